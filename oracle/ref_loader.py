@@ -1,0 +1,64 @@
+"""Import the reference's own ``operators`` package for pinning the oracle.
+
+TEST INFRASTRUCTURE ONLY.  The reference tree is present only on the
+development machine; ``load()`` returns ``None`` elsewhere, and callers skip.
+Nothing is copied: the modules are imported in place from the read-only tree.
+
+Two unused imports of the reference need stand-ins to import on a CPU box:
+``bitsandbytes.functional`` (operators/efficient_linear.py:2) and the
+``.cuda()`` calls on sentinel scalars (operators/compress_function.py:161-163,
+338), which are made no-ops while the reference runs on CPU tensors.
+"""
+from __future__ import annotations
+
+import contextlib
+import os
+import sys
+import types
+
+REFERENCE_ROOT = os.environ.get("HYC_REFERENCE_ROOT", "/root/reference")
+
+_cached = None
+
+
+def available() -> bool:
+    return os.path.isdir(os.path.join(REFERENCE_ROOT, "operators"))
+
+
+def load():
+    """Return the reference ``operators`` package, or None if absent."""
+    global _cached
+    if _cached is not None:
+        return _cached
+    if not available():
+        return None
+    for name in ("bitsandbytes", "bitsandbytes.functional"):
+        if name not in sys.modules:
+            sys.modules[name] = types.ModuleType(name)
+    sys.modules["bitsandbytes"].functional = sys.modules["bitsandbytes.functional"]
+    # the reference's ``operators`` directory has no __init__.py: register it
+    # as a package under a private name so its relative imports resolve
+    pkg = types.ModuleType("hyc_reference_operators")
+    pkg.__path__ = [os.path.join(REFERENCE_ROOT, "operators")]
+    sys.modules["hyc_reference_operators"] = pkg
+    import importlib
+
+    for sub in ("compress_function", "efficient_linear", "efficient_silu", "efficient_gelu",
+                "efficient_hadamard", "efficient_softmax", "efficient_gemm"):
+        setattr(pkg, sub, importlib.import_module(f"hyc_reference_operators.{sub}"))
+    _cached = pkg
+    return pkg
+
+
+@contextlib.contextmanager
+def cpu_cuda_noop():
+    """While active, ``Tensor.cuda()`` returns the tensor itself so the
+    reference's sentinel ``torch.tensor(1.).cuda()`` works without a GPU."""
+    import torch
+
+    saved = torch.Tensor.cuda
+    torch.Tensor.cuda = lambda self, *a, **k: self
+    try:
+        yield
+    finally:
+        torch.Tensor.cuda = saved
