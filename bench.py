@@ -1,0 +1,432 @@
+#!/usr/bin/env python
+"""Benchmark of the activation-compression hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--sweep]
+
+One "step" is one pass of the fused RMSNorm + compress kernel over one batch of
+synthetic activations (configuration 5 of the baseline: bf16 [65536, 4096],
+Student-t values, 1 % outlier channels x50, INT4, one dynamic absmax scale per
+token).  The metric is algorithmic HBM GB/s: bytes the operation must move
+(read x, write y, codes, outlier values, scales, rstd) per second, summed over
+all ranks.  With N > 1 every rank owns its own rows (weak scaling; the path
+has no data-path collective).
+
+The JSON line also carries
+  roofline      achieved / measured HBM peak for that kernel (CUDA-event time)
+  e2e           the same metric through the C ABI with HOST buffers: pinned
+                host -> device copy of the rows, kernel, device -> host copy of
+                everything the kernel produced, all inside the timed region
+  cpu_baseline  the CPU oracle (a PyTorch port of the reference's eager chain)
+                timed on this box's host cores on a bounded sample
+  clocks        SM clocks / throttle reasons sampled during the timed region
+``--impl reference`` times that CPU path alone, as its own arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, COLS, BITS, FRACTION, GROUP, ROTATE = 65536, 4096, 4, 0.01, 0, 0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes_per_row(cols: int, bits: int, k: int, groups: int, norm: bool = True, ln: bool = False) -> int:
+    """Bytes one row must move: read x (bf16) [+ write y] + codes + bf16 outlier values + fp32 scales
+    [+ rstd (+ mean)]."""
+    b = 2 * cols + cols * bits // 8 + 2 * k + 4 * groups
+    if norm:
+        b += 2 * cols + 4 + (4 if ln else 0)
+    return b
+
+
+def workload_name() -> str:
+    return (f"config5: fused RMSNorm+compress, bf16 [{ROWS},{COLS}] per GPU, INT{BITS}, "
+            f"{FRACTION:.0%} outlier channels, per-token absmax scale, rotation off")
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def committed_traffic():
+    """DRAM bytes per launch of the benchmarked kernel from the committed ncu summary, if any."""
+    path = os.path.join(ROOT, "profiles", "norm_compress_traffic.json")
+    if os.path.exists(path):
+        try:
+            return json.load(open(path)).get("dram_bytes_per_launch")
+        except Exception:
+            return None
+    return None
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 100 ms while active."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.rows:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            inside = t0 - 0.05 <= ts <= t1 + 0.15
+            try:
+                if inside:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            if inside:
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU arm
+
+def cpu_arm(sample_rows: int, repeats: int):
+    """The oracle's norm + channel-outlier compression on the host cores (all threads)."""
+    import torch
+    from hyc_lora_b200 import synthetic
+    from oracle import hyc_oracle as oc
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x, _ = synthetic.sweep_activation(sample_rows, COLS, FRACTION)
+    w = synthetic.norm_weight(COLS)
+    k = oc.n_outlier_count(COLS, FRACTION)
+    ch = oc.n_select_channels(oc.n_channel_scores(x), k)
+    groups = 1 if GROUP == 0 else COLS // GROUP
+    nbytes = algorithmic_bytes_per_row(COLS, BITS, k, groups) * sample_rows
+
+    def one():
+        oc.norm_forward(x, w, None, 1e-5, "rms")
+        oc.n_compress(x, ch, BITS, GROUP, ROTATE)
+
+    one()
+    times = []
+    for _ in range(repeats):
+        t = time.perf_counter()
+        one()
+        times.append(time.perf_counter() - t)
+    return nbytes, times, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 2048
+    nbytes, times, cores = cpu_arm(sample, args.warmup + args.steps)
+    times = times[args.warmup:]
+    total = sum(times)
+    value = nbytes * len(times) / total / 1e9
+    line = {
+        "impl": "reference", "metric": "fused norm+compress HBM GB/s", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload_name(), "sample": f"{sample} of {ROWS} rows per step"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample} rows x {len(times)} steps of the same workload; PyTorch CPU port of the "
+                                   "reference's eager norm + compress chain (the reference tree is not on this box)"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ GPU arm
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from hyc_lora_b200 import packed, synthetic
+    from oracle import hyc_oracle as oc
+
+    k = oc.n_outlier_count(COLS, FRACTION)
+    groups = 1 if GROUP == 0 else COLS // GROUP
+    # seeded rows of this rank (different salt per rank); generated in 8192-row pieces
+    pieces = [synthetic.sweep_activation(8192, COLS, FRACTION, salt=1000 * rank + i)[0] for i in range(ROWS // 8192)]
+    x_host = torch.cat(pieces).pin_memory()
+    del pieces
+    channels_host = synthetic.sweep_activation(8192, COLS, FRACTION, salt=1000 * rank)[1].to(torch.int32)
+    x = x_host.to(dev, non_blocking=True)
+    w = synthetic.norm_weight(COLS).to(dev)
+    # calibration (not timed): column absmax + top-k on the GPU; the planted set must come back
+    channels = packed.select_channels(packed.channel_absmax(x), k)
+    norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
+    bytes_per_step = algorithmic_bytes_per_row(COLS, BITS, k, groups) * ROWS
+
+    def step():
+        return packed.compress_n(x, channels, BITS, GROUP, ROTATE, norm=norm)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    start.record()
+    for _ in range(args.steps):
+        out = step()
+    stop.record()
+    barrier()
+    t1 = time.time()
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    # keep the GPU busy a little longer so that the clock samples are under load
+    if rank == 0:
+        t_end = time.time() + 0.6
+        while time.time() < t_end:
+            step()
+        torch.cuda.synchronize()
+        clocks = sampler.stop(t0, time.time())
+    p, y, rstd, _ = out
+
+    # ---- end to end through the C ABI with host buffers ----
+    y_host = torch.empty_like(x_host).pin_memory()
+    codes_host = torch.empty(p.codes.shape, dtype=p.codes.dtype).pin_memory()
+    oval_host = torch.empty(p.out_value.shape, dtype=p.out_value.dtype).pin_memory()
+    scales_host = torch.empty(p.scales.shape, dtype=p.scales.dtype).pin_memory()
+    rstd_host = torch.empty(rstd.shape, dtype=rstd.dtype).pin_memory()
+    h2d = x_host.numel() * 2
+    d2h = y_host.numel() * 2 + codes_host.numel() + oval_host.numel() * 2 + scales_host.numel() * 4 + rstd_host.numel() * 4
+    xin = torch.empty_like(x)
+
+    def e2e_step():
+        xin.copy_(x_host, non_blocking=True)
+        pp, yy, rr, _ = packed.compress_n(xin, channels, BITS, GROUP, ROTATE, norm=norm)
+        y_host.copy_(yy, non_blocking=True)
+        codes_host.copy_(pp.codes, non_blocking=True)
+        oval_host.copy_(pp.out_value, non_blocking=True)
+        scales_host.copy_(pp.scales, non_blocking=True)
+        rstd_host.copy_(rr, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    stop.record()
+    barrier()
+    e2e_ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+
+    if rank == 0:
+        peak, which = hbm_peak()
+        per_launch_s = ms / 1e3 / args.steps
+        achieved = bytes_per_step / per_launch_s / 1e9
+        value = achieved * world
+        line = {
+            "metric": "fused norm+compress HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": workload_name(), "rows_per_gpu": ROWS, "cols": COLS, "bits": BITS,
+                       "outlier_channels": k, "scale": "per-token absmax", "l2": "inputs (537 MB per step) exceed the 126 MB L2",
+                       "algorithmic_bytes_per_row": bytes_per_step // ROWS},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": committed_traffic(), "peak_source": f"of {which}",
+                         "kernel": "hyc::fwd_kernel<bf16, N, 4, norm>"},
+            "e2e": {"value": (bytes_per_step * e2e_steps * world) / (e2e_ms / 1e3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        # bounded CPU sample of the same workload (about 10-20 s)
+        nbytes, times, cores = cpu_arm(2048, 5)
+        line["cpu_baseline"] = {"value": nbytes / statistics.median(times) / 1e9, "unit": "GB/s", "cores": cores,
+                                "kind": "port", "sample": "2048 of 65536 rows, median of 5 runs, PyTorch CPU port of the "
+                                                          "reference's eager norm + compress chain"}
+        if args.sweep:
+            line["sweep"] = sweep(packed, synthetic, oc, x, w, peak)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def sweep(packed, synthetic, oc, x, w, peak):
+    """Per-kernel GB/s for the operator sweep of configuration 5 (informational)."""
+    import torch
+    rows_all, d = x.shape
+    out = []
+
+    def timed(fn, nbytes, name, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        out.append({"kernel": name, "ms": round(ms, 4), "GBps": round(nbytes / ms / 1e6, 1),
+                    "frac": round(nbytes / ms / 1e6 / peak, 3)})
+
+    norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
+    score = packed.channel_absmax(x)
+    dy = torch.randn(16384, d, device=x.device, dtype=torch.bfloat16)
+    for rows in (4096, 16384, 65536):
+        xs = x[:rows]
+        for frac in (0.005, 0.01, 0.02):
+            k = oc.n_outlier_count(d, frac)
+            ch = packed.select_channels(score, k)
+            for bits in (2, 4, 8):
+                for group in (0, 128):
+                    for rotate in (0, 256):
+                        if rows != 65536 and (frac != 0.01 or group or bits != 4):
+                            continue
+                        g = 1 if group == 0 else d // group
+                        tag = f"T={rows} f={frac} b={bits} g={group} rot={rotate}"
+                        timed(lambda: packed.compress_n(xs, ch, bits, group, rotate, norm=norm),
+                              algorithmic_bytes_per_row(d, bits, k, g) * rows, "norm+compress " + tag)
+                        if frac == 0.01:
+                            p = packed.compress_n(xs, ch, bits, group, rotate)
+                            base = d * bits // 8 + 2 * k + 4 * g
+                            timed(lambda: packed.decompress(p), (base + 2 * d) * rows, "decompress " + tag)
+                            if rows == 16384:
+                                rstd = torch.ones(rows, device=x.device)
+                                timed(lambda: packed.norm_bwd(p, dy, w, rstd, None, "rms"), (base + 4 + 4 * d) * rows,
+                                      "norm_bwd " + tag)
+                                timed(lambda: packed.act_bwd("silu", p, dy), (base + 4 * d) * rows, "silu_bwd " + tag)
+    # reference mode, one line per bit width (static per-channel scales)
+    xs = x[:16384]
+    xc = xs.float().cpu()[:512].to(torch.bfloat16).reshape(1, 512, d)
+    for bits in (2, 4, 8):
+        thr, L, R, scale = oc.r_calibrate(xc, 0.01, 1.0, bits, "per-channel", 0)
+        thr, scale = thr.to(x.device), scale.to(x.device)
+        nb = (2 * d + d * bits // 8 + 8) * 16384 + int(0.02 * 16384 * d) * 4
+        timed(lambda: packed.compress_r(xs, thr, scale, bits), nb, f"R-mode compress T=16384 b={bits} per-channel")
+        timed(lambda: packed.compress_r(xs, thr, scale, bits, norm=norm), nb + (2 * d + 4) * 16384,
+              f"R-mode norm+compress T=16384 b={bits} per-channel")
+    return out
+
+
+def run_case(args):
+    """A few launches of one kernel on a small case (inputs still larger than L2), for profilers."""
+    import torch
+    from hyc_lora_b200 import packed, synthetic
+    from oracle import hyc_oracle as oc
+    torch.cuda.set_device(0)
+    rows = args.rows
+    x = synthetic.sweep_activation(rows, COLS, FRACTION)[0].to("cuda")
+    w = synthetic.norm_weight(COLS).to("cuda")
+    k = oc.n_outlier_count(COLS, FRACTION)
+    ch = packed.select_channels(packed.channel_absmax(x), k)
+    norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
+    dy = torch.randn(rows, COLS, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(rows, device="cuda")
+    p = packed.compress_n(x, ch, BITS, args.group, args.rotate)
+    fns = {
+        "norm_compress": lambda: packed.compress_n(x, ch, BITS, args.group, args.rotate, norm=norm),
+        "compress": lambda: packed.compress_n(x, ch, BITS, args.group, args.rotate),
+        "decompress": lambda: packed.decompress(p),
+        "norm_bwd": lambda: packed.norm_bwd(p, dy, w, rstd, None, "rms"),
+        "silu_bwd": lambda: packed.act_bwd("silu", p, dy),
+    }
+    for _ in range(args.launches):
+        fns[args.case]()
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "rows": rows, "launches": args.launches, "status": int(p.status.item())}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sweep", action="store_true", help="add per-kernel numbers for the operator sweep")
+    ap.add_argument("--case", default=None, help="profiling aid: run only this kernel (see run_case)")
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--group", type=int, default=GROUP)
+    ap.add_argument("--rotate", type=int, default=ROTATE)
+    args = ap.parse_args()
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

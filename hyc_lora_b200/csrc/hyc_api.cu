@@ -1,0 +1,92 @@
+// Library-wide state, error strings, tuning knobs and the forward entry points
+// (argument checks + launch planning; the kernels are instantiated elsewhere).
+#include "hyc_fwd.cuh"
+
+namespace hyc {
+
+thread_local char g_cuda_error[256] = "";
+int g_tune_threads = 0, g_tune_stages = 0, g_tune_ctas = 0;
+
+static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, cudaStream_t stream) {
+  int rc = check_packed(out, true);
+  if (rc) return rc;
+  rc = check_dense(x, out->cols, norm != nullptr);
+  if (rc) return rc;
+  if (norm) {
+    if (!norm->weight || !norm->y || !norm->rstd) return HYC_ERR_NULL;
+    if (norm->kind < HYC_NORM_RMS || norm->kind > HYC_NORM_LAYER) return HYC_ERR_MODE;
+    if (norm->kind == HYC_NORM_LAYER && (!norm->bias || !norm->mean)) return HYC_ERR_NULL;
+    if (norm->param_dtype != HYC_F32 && norm->param_dtype != HYC_BF16) return HYC_ERR_DTYPE;
+    if (!aligned16(norm->weight) || !aligned16(norm->y) || (norm->bias && !aligned16(norm->bias))) return HYC_ERR_ALIGN;
+  }
+  if (out->rows == 0) return HYC_OK;
+  const int es = x->dtype == HYC_BF16 ? 2 : 4;
+  LayoutReq req;
+  fill_req_packed(&req, out, true);
+  req.slot_bytes = static_cast<uint32_t>(out->cols) * es;
+  LaunchPlan plan;
+  rc = plan_launch(req, out->rows, &plan);
+  if (rc) return rc;
+  FwdArgs a;
+  memset(&a, 0, sizeof(a));
+  a.p = to_dev(out);
+  a.x = static_cast<const unsigned char*>(x->base);
+  a.row_stride = x->row_stride; a.batch_stride = x->batch_stride; a.chunk_stride = x->chunk_stride;
+  a.chunks = x->chunks;
+  if (norm) {
+    a.kind = norm->kind; a.eps = norm->eps; a.weight = norm->weight; a.bias = norm->bias;
+    a.param_bf16 = norm->param_dtype == HYC_BF16;
+    a.y = norm->y; a.rstd = norm->rstd; a.mean = norm->mean;
+  }
+  a.L = plan.L;
+  if (out->mode == HYC_MODE_R) {
+    cudaError_t e = cudaMemsetAsync(out->pool_used, 0, sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(pool_used)");
+  }
+  return x->dtype == HYC_BF16 ? launch_fwd_bf16(a, plan, norm != nullptr, stream)
+                              : launch_fwd_f32(a, plan, norm != nullptr, stream);
+}
+
+}  // namespace hyc
+
+using namespace hyc;
+
+extern "C" {
+
+const char* hyc_strerror(int code) {
+  switch (code) {
+    case HYC_OK: return "ok";
+    case HYC_ERR_NULL: return "a required pointer is NULL";
+    case HYC_ERR_SHAPE: return "unsupported shape (cols must be a multiple of 128; group 0 or 128; rotate block must divide cols)";
+    case HYC_ERR_BITS: return "unsupported bit width";
+    case HYC_ERR_DTYPE: return "unsupported dtype";
+    case HYC_ERR_MODE: return "unknown mode, scale kind, norm kind or op";
+    case HYC_ERR_ALIGN: return "pointer or stride not 16-byte aligned";
+    case HYC_ERR_CAPACITY: return "size exceeds a stated maximum";
+    case HYC_ERR_CUDA: return "CUDA runtime error";
+    case HYC_ERR_SMEM: return "row too large for shared-memory staging";
+    default: return "unknown error code";
+  }
+}
+
+const char* hyc_last_cuda_error(void) { return g_cuda_error; }
+
+int hyc_version(void) { return 100; }
+
+int hyc_set_tuning(int threads, int stages, int ctas_per_sm) {
+  if (threads != 0 && (threads < 32 || threads > 256 || threads % 32 != 0)) return HYC_ERR_SHAPE;
+  if (stages < 0 || stages > kMaxStages || ctas_per_sm < 0 || ctas_per_sm > 16) return HYC_ERR_SHAPE;
+  g_tune_threads = threads; g_tune_stages = stages; g_tune_ctas = ctas_per_sm;
+  return HYC_OK;
+}
+
+int hyc_compress(const hyc_dense* x, const hyc_packed* out, void* stream) {
+  return run_fwd(x, nullptr, out, static_cast<cudaStream_t>(stream));
+}
+
+int hyc_norm_compress(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, void* stream) {
+  if (!norm) return HYC_ERR_NULL;
+  return run_fwd(x, norm, out, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

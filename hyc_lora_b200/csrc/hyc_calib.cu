@@ -1,0 +1,127 @@
+// Calibration kernels for the channel-outlier mode: column absmax of an
+// activation and deterministic top-k channel selection (ties to the lower
+// index, ascending output).  They run on the first calls of a site only.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/hyc_b200.h"
+#include "hyc_common.cuh"
+
+namespace hyc {
+
+// Each CTA walks rows blockIdx.x, +gridDim.x, ...; thread t owns the 8-channel
+// vectors t, t+blockDim, ... of every row and keeps their running maxima in
+// shared memory (one owner per column, so no atomics there).  The CTA's maxima
+// are merged into the global score with integer atomicMax, which orders
+// non-negative floats correctly.
+template <typename XT>
+__global__ void __launch_bounds__(256) channel_absmax_kernel(const XT* x, long long rows, int D, int seq, int chunks,
+                                                             long long row_stride, long long batch_stride,
+                                                             long long chunk_stride, float* score) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* acc = reinterpret_cast<float*>(smem_raw);
+  const int nvec = D >> 3;
+  const int clen = D / chunks;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) acc[c] = 0.f;
+  __syncthreads();  // columns are re-partitioned by 8-channel vector below
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const XT* src = chunks == 1 ? x + row * row_stride : x + (row / seq) * batch_stride + (row % seq) * row_stride;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const int col = v << 3;
+      const int c = col / clen;
+      float f[8];
+      load8<XT>(src + c * chunk_stride, col - c * clen, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[col + e] = fmaxf(acc[col + e], fabsf(f[e]));
+    }
+  }
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int col = (v << 3) + e;
+      atomicMax(reinterpret_cast<unsigned int*>(score) + col, __float_as_uint(acc[col]));
+    }
+  }
+}
+
+// rank[c] = number of channels that come before c when ordering by
+// (score descending, index ascending)
+__global__ void __launch_bounds__(256) channel_rank_kernel(const float* score, int D, int* rank) {
+  __shared__ float tile[1024];
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const float mine = c < D ? score[c] : 0.f;
+  int before = 0;
+  for (int j0 = 0; j0 < D; j0 += 1024) {
+    __syncthreads();
+    for (int j = threadIdx.x; j < 1024; j += blockDim.x) tile[j] = (j0 + j < D) ? score[j0 + j] : -1.f;
+    __syncthreads();
+    const int n = min(1024, D - j0);
+    for (int j = 0; j < n; ++j) {
+      const float s = tile[j];
+      before += (s > mine || (s == mine && (j0 + j) < c)) ? 1 : 0;
+    }
+  }
+  if (c < D) rank[c] = before;
+}
+
+// ascending list of the channels whose rank is below k
+__global__ void __launch_bounds__(256) channel_gather_kernel(const int* rank, int D, int k, int* channels) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D || rank[c] >= k) return;
+  int pos = 0;
+  for (int j = 0; j < c; ++j) pos += rank[j] < k ? 1 : 0;
+  channels[pos] = c;
+}
+
+}  // namespace hyc
+
+using namespace hyc;
+
+extern "C" {
+
+int hyc_channel_absmax(const hyc_dense* x, int64_t rows, int32_t cols, int32_t seq, float* score, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!x || !x->base || !score) return HYC_ERR_NULL;
+  if (rows < 0 || cols <= 0 || cols % 128 != 0 || cols > 65408 || seq < 1) return HYC_ERR_SHAPE;
+  if (x->dtype != HYC_F32 && x->dtype != HYC_BF16) return HYC_ERR_DTYPE;
+  if (x->chunks < 1 || cols % x->chunks != 0 || (cols / x->chunks) % 8 != 0) return HYC_ERR_SHAPE;
+  const int es = x->dtype == HYC_BF16 ? 2 : 4;
+  if ((reinterpret_cast<uintptr_t>(x->base) & 15u) || (x->row_stride * es) % 16 != 0 ||
+      (x->chunks > 1 && ((x->batch_stride * es) % 16 != 0 || (x->chunk_stride * es) % 16 != 0)))
+    return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  long long grid = static_cast<long long>(sms) * 4;
+  if (grid > rows) grid = rows;
+  const size_t smem = static_cast<size_t>(cols) * 4;
+  if (x->dtype == HYC_BF16) {
+    auto kern = channel_absmax_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<static_cast<int>(grid), 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(x->base), rows, cols, seq,
+                                                        x->chunks, x->row_stride, x->batch_stride, x->chunk_stride,
+                                                        score);
+  } else {
+    auto kern = channel_absmax_kernel<float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<static_cast<int>(grid), 256, smem, stream>>>(static_cast<const float*>(x->base), rows, cols, seq, x->chunks,
+                                                        x->row_stride, x->batch_stride, x->chunk_stride, score);
+  }
+  return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
+}
+
+int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* channels, int32_t* rank_scratch,
+                        void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!score || !rank_scratch || (k > 0 && !channels)) return HYC_ERR_NULL;
+  if (cols <= 0 || k < 0 || k > cols) return HYC_ERR_SHAPE;
+  if (k == 0) return HYC_OK;
+  const int blocks = (cols + 255) / 256;
+  channel_rank_kernel<<<blocks, 256, 0, stream>>>(score, cols, rank_scratch);
+  channel_gather_kernel<<<blocks, 256, 0, stream>>>(rank_scratch, cols, k, channels);
+  return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
+}
+
+}  // extern "C"

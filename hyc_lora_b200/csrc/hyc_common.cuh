@@ -1,0 +1,206 @@
+// Shared device helpers for the row-streaming kernels (sm_100a).
+//
+// Every kernel in this library walks rows of an activation.  A CTA owns a set
+// of rows (row = blockIdx.x + i*gridDim.x), stages each row -- and whatever
+// else the row needs (gradient row, packed codes) -- in shared memory with 1-D
+// bulk asynchronous copies (cp.async.bulk, completion on an mbarrier), several
+// stages deep, and makes a few cheap passes over the staged data.  No kernel
+// waits on another CTA; the only waits are on a CTA's own copies and they are
+// bounded.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hyc {
+
+constexpr int kMaxStages = 4;
+constexpr uint32_t kStatusPoolOverflow = 1u;
+constexpr uint32_t kStatusWaitExpired = 2u;
+
+// ---------------------------------------------------------------- PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+// make the initialised barriers visible to the asynchronous proxy
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// order this thread's generic-proxy shared-memory accesses before later
+// asynchronous-proxy (bulk copy) accesses to the same locations
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+// 1-D bulk copy global -> this CTA's shared memory; both addresses 16-byte
+// aligned, bytes a multiple of 16.  No multicast.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst_smem)),
+      "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: gives up after about a second of SM clocks and reports false.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - start > 2000000000LL) return false;
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------- bf16 helpers
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+
+// round-to-nearest-even to bf16, returned as fp32
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ uint32_t float_to_bf16_bits(float x) {
+  return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x)));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& w, float (&f)[8]) {
+  f[0] = __uint_as_float(w.x << 16);
+  f[1] = __uint_as_float(w.x & 0xffff0000u);
+  f[2] = __uint_as_float(w.y << 16);
+  f[3] = __uint_as_float(w.y & 0xffff0000u);
+  f[4] = __uint_as_float(w.z << 16);
+  f[5] = __uint_as_float(w.z & 0xffff0000u);
+  f[6] = __uint_as_float(w.w << 16);
+  f[7] = __uint_as_float(w.w & 0xffff0000u);
+}
+
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
+  uint4 w;
+  w.x = pack_bf16x2(f[0], f[1]);
+  w.y = pack_bf16x2(f[2], f[3]);
+  w.z = pack_bf16x2(f[4], f[5]);
+  w.w = pack_bf16x2(f[6], f[7]);
+  return w;
+}
+
+// Load 8 consecutive elements (column `col`, multiple of 8) of a row as fp32.
+// Works for shared or global rows (generic addressing), 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ void load8(const T* row, int col, float (&f)[8]);
+
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* row, int col, float (&f)[8]) {
+  const uint4 w = *reinterpret_cast<const uint4*>(row + col);
+  unpack_bf16x8(w, f);
+}
+
+template <>
+__device__ __forceinline__ void load8<float>(const float* row, int col, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(row + col);
+  const float4 b = *reinterpret_cast<const float4*>(row + col + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+template <typename T>
+__device__ __forceinline__ void store8(T* row, int col, const float (&f)[8]);
+
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* row, int col, const float (&f)[8]) {
+  *reinterpret_cast<uint4*>(row + col) = pack_bf16x8(f);
+}
+
+template <>
+__device__ __forceinline__ void store8<float>(float* row, int col, const float (&f)[8]) {
+  *reinterpret_cast<float4*>(row + col) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(row + col + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+
+// ---------------------------------------------------------------- reductions
+
+struct OpSum {
+  __device__ __forceinline__ float operator()(float a, float b) const { return a + b; }
+};
+struct OpMax {
+  __device__ __forceinline__ float operator()(float a, float b) const { return fmaxf(a, b); }
+};
+
+// CTA-wide reduction of N values; every thread gets the result.  `slot` is a
+// private shared array of N*32 floats for this call site; the same slot may be
+// reused once per row because at least one __syncthreads separates the uses.
+template <int N, class Op>
+__device__ __forceinline__ void block_reduce(float (&v)[N], float* slot, Op op) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v[i] = op(v[i], __shfl_xor_sync(0xffffffffu, v[i], m));
+  }
+  if (nwarps == 1) return;
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) slot[i * 32 + warp] = v[i];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    float r = slot[i * 32];
+    for (int w = 1; w < nwarps; ++w) r = op(r, slot[i * 32 + w]);
+    v[i] = r;
+  }
+}
+
+// ---------------------------------------------------------------- staged rows
+
+// Shared-memory ring of `stages` slots, one mbarrier per slot.  Thread 0 issues
+// the copies of a row into a slot; everybody waits on the slot's barrier.
+struct RowRing {
+  uint64_t* bars;        // [stages]
+  unsigned char* slots;  // stages * slot_bytes, 128-byte aligned
+  uint32_t slot_bytes;
+  int stages;
+
+  __device__ __forceinline__ unsigned char* slot(int s) const { return slots + static_cast<size_t>(s) * slot_bytes; }
+
+  __device__ __forceinline__ void init() {
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < stages; ++s) mbar_init(&bars[s], 1);
+      fence_barrier_init();
+    }
+    __syncthreads();
+  }
+};
+
+}  // namespace hyc

@@ -1,0 +1,103 @@
+// Packed activation -> bf16 rows.
+#include "hyc_host.cuh"
+
+namespace hyc {
+
+// ------------------------------------------------------------------ decompress to bf16 rows
+
+struct DecArgs {
+  PackedDev p;
+  __nv_bfloat16* out;
+  long long row_stride, batch_stride, chunk_stride;
+  int chunks;
+  SmemLayout L;
+};
+
+template <int MODE, int BITS>
+__global__ void __launch_bounds__(256) decompress_kernel(const __grid_constant__ DecArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const PackedDev& p = a.p;
+  const int D = p.cols;
+  const uint32_t cb = static_cast<uint32_t>(D) * BITS / 8;
+  RowRing ring{reinterpret_cast<uint64_t*>(smem), smem + a.L.off_slots, a.L.slot_bytes, a.L.stages};
+  ring.init();
+  const Work w = make_work(smem, a.L);
+  setup_packed(p, w);
+  const long long rows = p.rows, stride = gridDim.x;
+  long long row = blockIdx.x;
+  auto issue = [&](int s, long long r) {
+    mbar_expect_tx(&ring.bars[s], cb);
+    issue_bytes(ring, s, 0, p.codes + r * cb, cb);
+  };
+  if (threadIdx.x == 0)
+    for (int s = 0; s < ring.stages; ++s)
+      if (row + s * stride < rows) issue(s, row + s * stride);
+  for (int i = 0; row < rows; ++i, row += stride) {
+    const int st = i % ring.stages;
+    if (!mbar_wait_bounded(&ring.bars[st], (i / ring.stages) & 1)) w.misc[2] = 1;
+    dequant_row<MODE, BITS>(p, w, ring.slot(st), row);
+    __nv_bfloat16* orow;
+    const int clen = D / a.chunks;
+    if (a.chunks == 1) orow = a.out + row * a.row_stride;
+    else orow = a.out + (row / p.seq) * a.batch_stride + (row % p.seq) * a.row_stride;
+    for (int v = threadIdx.x; v < (D >> 3); v += blockDim.x) {
+      const int col = v << 3;
+      const uint4 val = *reinterpret_cast<const uint4*>(w.xr + col);
+      const int c = col / clen;
+      *reinterpret_cast<uint4*>(orow + c * a.chunk_stride + (col - c * clen)) = val;
+    }
+    __syncthreads();
+    if (w.misc[2]) {
+      if (threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
+      drain_ring(ring, i, row + stride, rows, stride);
+      return;
+    }
+    if (threadIdx.x == 0) {
+      const long long next = row + ring.stages * stride;
+      if (next < rows) { fence_proxy_async(); issue(st, next); }
+    }
+  }
+}
+
+}  // namespace hyc
+
+using namespace hyc;
+
+extern "C" {
+
+int hyc_decompress(const hyc_packed* in, const hyc_dense* o, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int rc = check_packed(in, false);
+  if (rc) return rc;
+  rc = check_dense(o, in->cols, false);
+  if (rc) return rc;
+  if (o->dtype != HYC_BF16) return HYC_ERR_DTYPE;
+  if (in->rows == 0) return HYC_OK;
+  LayoutReq req;
+  fill_req_packed(&req, in, false);
+  req.xr = true;
+  req.slot_bytes = static_cast<uint32_t>(in->cols) * in->bits / 8;
+  LaunchPlan plan;
+  rc = plan_launch(req, in->rows, &plan);
+  if (rc) return rc;
+  DecArgs a;
+  memset(&a, 0, sizeof(a));
+  a.p = to_dev(in);
+  a.out = static_cast<__nv_bfloat16*>(o->base);
+  a.row_stride = o->row_stride; a.batch_stride = o->batch_stride; a.chunk_stride = o->chunk_stride;
+  a.chunks = o->chunks;
+  a.L = plan.L;
+#define HYC_DEC_CASE(MODE, BITS)                                            \
+  {                                                                         \
+    auto kern = decompress_kernel<MODE, BITS>;                              \
+    rc = set_smem(kern, plan.L.total);                                      \
+    if (rc) return rc;                                                      \
+    kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a);             \
+  }
+  HYC_DISPATCH_MODE_BITS(a.p.mode, a.p.bits, HYC_DEC_CASE)
+#undef HYC_DEC_CASE
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? HYC_OK : cuda_fail(e, "decompress_kernel launch");
+}
+
+}  // extern "C"

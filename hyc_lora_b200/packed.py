@@ -1,0 +1,334 @@
+"""Packed activations and thin Python callers of the C ABI.
+
+A :class:`Packed` owns the device buffers of one compressed activation (all
+of them ordinary torch tensors, so PyTorch's caching allocator manages their
+lifetime) and knows how to describe itself as the ``hyc_packed`` record the
+kernels take.  The functions below allocate outputs, fill the records and
+enqueue the kernel on the current CUDA stream; none of them synchronises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import HycDense, HycNormBwdArgs, HycNormFwd, HycPacked, check, lib
+
+_SCALE_KIND = {"per-tensor": _lib.HYC_SCALE_TENSOR, "per-channel": _lib.HYC_SCALE_CHANNEL,
+               "per-token": _lib.HYC_SCALE_TOKEN}
+_NORM_KIND = {"rms": _lib.HYC_NORM_RMS, "rms_gemma": _lib.HYC_NORM_RMS_GEMMA, "ln": _lib.HYC_NORM_LAYER}
+_ACT_OP = {"silu": _lib.HYC_ACT_SILU, "gelu": _lib.HYC_ACT_GELU_TANH, "product": _lib.HYC_ACT_PRODUCT}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.HYC_BF16
+    if t.dtype == torch.float32:
+        return _lib.HYC_F32
+    raise TypeError(f"unsupported dtype {t.dtype}: the kernels take float32 or bfloat16")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("hyc_lora_b200 operators run on CUDA tensors only (there is no CPU path)")
+
+
+@dataclass
+class Packed:
+    """One compressed activation (rows x cols, rows = batch * seq)."""
+    mode: str                    # "R" or "N"
+    bits: int
+    rows: int
+    cols: int
+    seq: int
+    codes: torch.Tensor          # uint8 [rows, cols*bits/8]
+    status: torch.Tensor         # int32 [1]
+    shape: tuple                 # logical [B, S, D] shape of the activation
+    # reference mode
+    scale: Optional[torch.Tensor] = None
+    scale_kind: str = "per-tensor"
+    thr: Optional[torch.Tensor] = None
+    lowrank: Optional[torch.Tensor] = None   # bf16 [seq, cols]
+    pool: Optional[torch.Tensor] = None      # int32 [capacity]
+    pool_used: Optional[torch.Tensor] = None  # int32 [1]
+    row_meta: Optional[torch.Tensor] = None  # int32 [rows, 2]
+    # north-star mode
+    channels: Optional[torch.Tensor] = None  # int32 [k]
+    group: int = 0
+    rotate: int = 0
+    out_value: Optional[torch.Tensor] = None  # bf16 [rows, k]
+    scales: Optional[torch.Tensor] = None     # f32 [rows, G]
+    _keep: list = field(default_factory=list, repr=False)
+
+    def record(self) -> HycPacked:
+        r = HycPacked()
+        r.mode = _lib.HYC_MODE_R if self.mode == "R" else _lib.HYC_MODE_N
+        r.bits, r.rows, r.cols, r.seq = self.bits, self.rows, self.cols, self.seq
+        r.codes = self.codes.data_ptr()
+        r.status = self.status.data_ptr()
+        if self.mode == "R":
+            r.scale_kind = _SCALE_KIND[self.scale_kind]
+            r.scale_dtype = _dtype_code(self.scale)
+            r.scale = self.scale.data_ptr()
+            r.thr = self.thr.data_ptr() if self.thr is not None else None
+            r.lowrank = self.lowrank.data_ptr() if self.lowrank is not None else None
+            r.pool = self.pool.data_ptr()
+            r.pool_cap = self.pool.numel()
+            r.pool_used = self.pool_used.data_ptr()
+            r.row_meta = self.row_meta.data_ptr()
+        else:
+            k = 0 if self.channels is None else self.channels.numel()
+            r.channels = self.channels.data_ptr() if k else None
+            r.n_channels = k
+            r.group, r.rotate = self.group, self.rotate
+            r.out_value = self.out_value.data_ptr() if k else None
+            r.scales = self.scales.data_ptr()
+        return r
+
+    def nbytes(self) -> int:
+        """Bytes this activation keeps alive for backward."""
+        n = self.codes.numel()
+        if self.mode == "R":
+            n += self.pool.numel() * 4 + self.row_meta.numel() * 4
+        else:
+            n += self.scales.numel() * 4 + (0 if self.out_value is None else self.out_value.numel() * 2)
+        return n
+
+    # ---- helpers for checks (synchronise; not used on the training path) ----
+    def overflowed(self) -> bool:
+        return bool(int(self.status.item()) & _lib.HYC_STATUS_POOL_OVERFLOW)
+
+    def wait_expired(self) -> bool:
+        return bool(int(self.status.item()) & _lib.HYC_STATUS_WAIT_EXPIRED)
+
+    def outlier_coo(self):
+        """Reference-mode outliers as (flat element index int64 [nnz] sorted, bf16 values) -- the
+        content of the reference's sparse COO tensor, for parity checks."""
+        meta = self.row_meta.cpu().long()
+        pool = self.pool.cpu()
+        first, cnt = meta[:, 0], meta[:, 1]
+        rows = torch.repeat_interleave(torch.arange(self.rows), cnt)
+        starts = torch.repeat_interleave(first, cnt)
+        within = torch.arange(int(cnt.sum())) - torch.repeat_interleave(torch.cumsum(cnt, 0) - cnt, cnt)
+        entry = pool[(starts + within)].long() & 0xFFFFFFFF
+        col = entry & 0xFFFF
+        hi = (entry >> 16) & 0xFFFF
+        val = torch.where(hi >= 32768, hi - 65536, hi).to(torch.int16).view(torch.bfloat16)
+        flat = rows * self.cols + col
+        order = torch.argsort(flat)
+        return flat[order], val[order]
+
+
+def _dense_record(x: torch.Tensor, cols: int):
+    """Describe ``x`` ([..., D] contiguous rows, or a [B,H,S,hd] head tensor that is
+    seen as [B,S,H*hd]) as an hyc_dense.  Returns (record, rows, seq, logical_shape, keepalive)."""
+    d = HycDense()
+    d.dtype = _dtype_code(x)
+    if x.dim() == 4:
+        b, h, s, hd = x.shape
+        if x.stride(3) != 1:
+            x = x.contiguous()
+        d.base = x.data_ptr()
+        d.chunks = h
+        d.batch_stride, d.chunk_stride, d.row_stride = x.stride(0), x.stride(1), x.stride(2)
+        if h * hd != cols:
+            raise ValueError("head tensor does not match cols")
+        return d, b * s, s, (b, s, h * hd), x
+    if x.shape[-1] != cols:
+        raise ValueError("last dimension does not match cols")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    d.base = x.data_ptr()
+    d.chunks = 1
+    d.row_stride = cols
+    rows = x.numel() // cols
+    seq = x.shape[-2] if x.dim() >= 2 else 1
+    shape = tuple(x.shape) if x.dim() == 3 else (1, rows, cols) if x.dim() <= 2 else (rows // seq, seq, cols)
+    return d, rows, seq, shape, x
+
+
+def default_pool_entries(rows: int, cols: int, outlier_ratio: float) -> int:
+    """Capacity of the element-outlier pool: four times the calibrated two-sided
+    density (the reference's signed quantile keeps about 2 * ratio of the
+    elements), at least 1/64 of the tensor."""
+    frac = max(8.0 * outlier_ratio, 1.0 / 64.0)
+    return min(int(math.ceil(rows * cols * min(frac, 1.0))) + 1024, 2 ** 32 - 2)
+
+
+def _alloc_common(rows, cols, bits, device):
+    codes = torch.empty((rows, cols * bits // 8), dtype=torch.uint8, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    return codes, status
+
+
+def _new_r(x, rows, cols, seq, shape, thr, scale, scale_kind, bits, lowrank, pool_entries) -> Packed:
+    dev = x.device
+    codes, status = _alloc_common(rows, cols, bits, dev)
+    return Packed(mode="R", bits=bits, rows=rows, cols=cols, seq=seq, codes=codes, status=status, shape=shape,
+                  scale=scale.contiguous(), scale_kind=scale_kind,
+                  thr=thr.reshape(1).to(device=dev, dtype=torch.float32), lowrank=lowrank,
+                  pool=torch.empty(pool_entries, dtype=torch.int32, device=dev),
+                  pool_used=torch.empty(1, dtype=torch.int32, device=dev),
+                  row_meta=torch.empty((rows, 2), dtype=torch.int32, device=dev))
+
+
+def _new_n(x, rows, cols, seq, shape, channels, bits, group, rotate) -> Packed:
+    dev = x.device
+    codes, status = _alloc_common(rows, cols, bits, dev)
+    k = 0 if channels is None else channels.numel()
+    g = 1 if group == 0 else cols // group
+    return Packed(mode="N", bits=bits, rows=rows, cols=cols, seq=seq, codes=codes, status=status, shape=shape,
+                  channels=channels, group=group, rotate=rotate,
+                  out_value=torch.empty((rows, k), dtype=torch.bfloat16, device=dev) if k else None,
+                  scales=torch.empty((rows, g), dtype=torch.float32, device=dev))
+
+
+def scale_kind_of(scale: torch.Tensor) -> str:
+    """The reference tells its three scale layouts apart by shape: 0-dim,
+    [1, D] (per-channel) and [S, 1] (per-token)."""
+    if scale.dim() == 0 or scale.numel() == 1 and scale.dim() < 2:
+        return "per-tensor"
+    if scale.dim() == 2 and scale.shape[0] == 1:
+        return "per-channel" if scale.shape[1] > 1 else "per-tensor"
+    return "per-token"
+
+
+def compress_r(x: torch.Tensor, thr: torch.Tensor, scale: torch.Tensor, bits: int,
+               lowrank: Optional[torch.Tensor] = None, pool_entries: Optional[int] = None,
+               outlier_ratio: float = 0.01, norm: Optional[dict] = None):
+    """Reference-mode compression of ``x`` ([B,S,D] or [B,H,S,hd]).  With
+    ``norm`` (keys kind, weight, bias, eps) the norm forward is fused and
+    ``(packed, y, rstd, mean)`` is returned, else ``packed``."""
+    _require_cuda(x, thr, scale)
+    cols = x.shape[-1] if x.dim() != 4 else x.shape[1] * x.shape[3]
+    d, rows, seq, shape, keep = _dense_record(x, cols)
+    if scale.dtype != torch.bfloat16:
+        scale = scale.to(torch.bfloat16)
+    kind = scale_kind_of(scale)
+    if kind == "per-token" and scale.numel() != seq:
+        raise ValueError(f"per-token scale has {scale.numel()} positions, the activation has {seq}")
+    if pool_entries is None:
+        pool_entries = default_pool_entries(rows, cols, outlier_ratio)
+    p = _new_r(keep, rows, cols, seq, shape, thr, scale, kind, bits, lowrank, pool_entries)
+    return _run_fwd(d, keep, p, norm)
+
+
+def compress_n(x: torch.Tensor, channels: Optional[torch.Tensor], bits: int, group: int = 0, rotate: int = 0,
+               norm: Optional[dict] = None):
+    """North-star-mode compression (channel outliers, dynamic absmax scales,
+    optional block Hadamard rotation)."""
+    _require_cuda(x, channels)
+    cols = x.shape[-1] if x.dim() != 4 else x.shape[1] * x.shape[3]
+    d, rows, seq, shape, keep = _dense_record(x, cols)
+    p = _new_n(keep, rows, cols, seq, shape, channels, bits, group, rotate)
+    return _run_fwd(d, keep, p, norm)
+
+
+def _run_fwd(d, x, p: Packed, norm):
+    rec = p.record()
+    if norm is None:
+        check(lib.hyc_compress(C.byref(d), C.byref(rec), _stream()), "hyc_compress")
+        return p
+    kind = norm["kind"]
+    w, b = norm["weight"], norm.get("bias")
+    _require_cuda(w, b)
+    if b is not None and b.dtype != w.dtype:
+        b = b.to(w.dtype)
+    n = HycNormFwd()
+    n.kind = _NORM_KIND[kind]
+    n.eps = float(norm["eps"])
+    n.weight, n.bias = w.data_ptr(), (b.data_ptr() if (b is not None and kind == "ln") else None)
+    n.param_dtype = _dtype_code(w)
+    y = torch.empty_like(x)
+    rstd = torch.empty(p.rows, dtype=torch.float32, device=x.device)
+    mean = torch.empty(p.rows, dtype=torch.float32, device=x.device) if kind == "ln" else None
+    n.y, n.rstd, n.mean = y.data_ptr(), rstd.data_ptr(), (mean.data_ptr() if mean is not None else None)
+    check(lib.hyc_norm_compress(C.byref(d), C.byref(n), C.byref(rec), _stream()), "hyc_norm_compress")
+    return p, y, rstd, mean
+
+
+def decompress(p: Packed, num_heads: int = 0) -> torch.Tensor:
+    """bf16 reconstruction, [B,S,D] or (``num_heads``) a [B,H,S,hd] view of it."""
+    b, s, dcols = p.shape
+    out = torch.empty((b, s, dcols), dtype=torch.bfloat16, device=p.codes.device)
+    d = HycDense()
+    d.base, d.dtype, d.chunks, d.row_stride = out.data_ptr(), _lib.HYC_BF16, 1, dcols
+    rec = p.record()
+    check(lib.hyc_decompress(C.byref(rec), C.byref(d), _stream()), "hyc_decompress")
+    if num_heads:
+        return out.reshape(b, s, num_heads, dcols // num_heads).transpose(1, 2)
+    return out
+
+
+def norm_bwd(p: Packed, dy: torch.Tensor, weight: torch.Tensor, rstd: torch.Tensor, mean: Optional[torch.Tensor],
+             kind: str, ref_compat_c2: bool = True, need_dweight: bool = False, need_dbias: bool = False):
+    """Returns ``(dx bf16, dweight fp32 | None, dbias fp32 | None)``."""
+    _require_cuda(dy, weight, rstd)
+    if not dy.is_contiguous():
+        dy = dy.contiguous()
+    dx = torch.empty(dy.shape, dtype=torch.bfloat16, device=dy.device)
+    a = HycNormBwdArgs()
+    a.kind, a.ref_compat_c2 = _NORM_KIND[kind], int(ref_compat_c2)
+    a.weight, a.param_dtype = weight.data_ptr(), _dtype_code(weight)
+    a.dy, a.dy_dtype = dy.data_ptr(), _dtype_code(dy)
+    a.rstd, a.mean = rstd.data_ptr(), (mean.data_ptr() if mean is not None else None)
+    a.dx = dx.data_ptr()
+    dw = db = partials = None
+    if need_dweight:
+        nparts = lib.hyc_norm_bwd_partial_rows()
+        dw = torch.empty(p.cols, dtype=torch.float32, device=dy.device)
+        db = torch.empty(p.cols, dtype=torch.float32, device=dy.device) if need_dbias else None
+        partials = torch.empty((2 if need_dbias else 1) * nparts * p.cols, dtype=torch.float32, device=dy.device)
+        a.dweight, a.dbias, a.partials = dw.data_ptr(), (db.data_ptr() if db is not None else None), partials.data_ptr()
+    rec = p.record()
+    check(lib.hyc_norm_bwd(C.byref(rec), C.byref(a), _stream()), "hyc_norm_bwd")
+    return dx, dw, db
+
+
+def act_bwd(op: str, p1: Packed, g: torch.Tensor, p2: Optional[Packed] = None):
+    """``op`` in {"silu", "gelu", "product"}; returns dx (and dx2 for product) in g's dtype."""
+    _require_cuda(g)
+    if not g.is_contiguous():
+        g = g.contiguous()
+    dx1 = torch.empty_like(g)
+    dx2 = torch.empty_like(g) if op == "product" else None
+    r1 = p1.record()
+    r2 = p2.record() if p2 is not None else None
+    check(lib.hyc_act_bwd(_ACT_OP[op], C.byref(r1), C.byref(r2) if r2 is not None else None, _ptr(g),
+                          _dtype_code(g), _ptr(dx1), _ptr(dx2), _stream()), "hyc_act_bwd")
+    return (dx1, dx2) if op == "product" else dx1
+
+
+def channel_absmax(x: torch.Tensor, score: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 column absmax of ``x`` merged (max) into ``score`` [D]."""
+    _require_cuda(x)
+    cols = x.shape[-1] if x.dim() != 4 else x.shape[1] * x.shape[3]
+    d, rows, seq, _, keep = _dense_record(x, cols)
+    if score is None:
+        score = torch.zeros(cols, dtype=torch.float32, device=x.device)
+    check(lib.hyc_channel_absmax(C.byref(d), rows, cols, seq, _ptr(score), _stream()), "hyc_channel_absmax")
+    return score
+
+
+def select_channels(score: torch.Tensor, k: int) -> torch.Tensor:
+    """Ascending int32 list of the k channels of largest score (ties to the lower index)."""
+    _require_cuda(score)
+    cols = score.numel()
+    channels = torch.empty(k, dtype=torch.int32, device=score.device)
+    scratch = torch.empty(cols, dtype=torch.int32, device=score.device)
+    check(lib.hyc_select_channels(_ptr(score), cols, k, _ptr(channels), _ptr(scratch), _stream()),
+          "hyc_select_channels")
+    return channels

@@ -1,0 +1,195 @@
+/*
+ * hyc_b200.h -- C ABI of the B200 (sm_100a) activation compress / decompress+grad
+ * kernels that stand behind the HyC-LoRA operator layer.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless
+ *     the comment says "host";
+ *   - the caller allocates every buffer (inputs, outputs, scratch); no entry
+ *     point allocates, frees or synchronises unless its comment says so;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it;
+ *   - the return value is HYC_OK (0) or a negative hyc_status; argument errors
+ *     are returned BEFORE anything is enqueued; hyc_strerror() names a code;
+ *   - conditions only the device can see (outlier pool overflow, an expired
+ *     wait) are OR-ed into the caller-owned `status` word of the hyc_packed
+ *     record, never trapped.
+ *
+ * Citations name the reference implementation each entry replaces
+ * (paths inside thu-ee-acts-lab/HyC-LoRA).
+ */
+#ifndef HYC_B200_H
+#define HYC_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  HYC_OK = 0,
+  HYC_ERR_NULL = -1,        /* a required pointer is NULL                         */
+  HYC_ERR_SHAPE = -2,       /* rows/cols/seq/group/rotate not supported           */
+  HYC_ERR_BITS = -3,        /* bits not in {1,2,4,8} (R) / {2,4,8} (N)            */
+  HYC_ERR_DTYPE = -4,       /* dtype enum out of range or combination unsupported */
+  HYC_ERR_MODE = -5,        /* unknown mode / scale kind / op                     */
+  HYC_ERR_ALIGN = -6,       /* a pointer or stride is not 16-byte aligned         */
+  HYC_ERR_CAPACITY = -7,    /* a size exceeds a stated maximum                    */
+  HYC_ERR_CUDA = -8,        /* a CUDA runtime call failed (see hyc_last_cuda_error) */
+  HYC_ERR_SMEM = -9         /* the row does not fit the shared-memory staging     */
+} hyc_status;
+
+typedef enum { HYC_F32 = 0, HYC_BF16 = 1 } hyc_dtype;
+
+/* Semantic mode of a packed activation.
+ *  HYC_MODE_R  the reference's arithmetic: optional low-rank subtraction, scalar
+ *              threshold on |x| selecting ELEMENT outliers, static calibrated
+ *              scale (per tensor / channel / sequence position), round-half-even
+ *              of x/scale, clamp, offset-binary segment packing
+ *              (operators/compress_function.py:136-200).
+ *  HYC_MODE_N  channel outliers (a fixed ascending channel list kept in bf16),
+ *              optional block Walsh-Hadamard rotation, dynamic absmax scale per
+ *              row or per 128-channel group; same rounding/clamp/packing.     */
+typedef enum { HYC_MODE_R = 0, HYC_MODE_N = 1 } hyc_mode;
+
+typedef enum { HYC_SCALE_TENSOR = 0, HYC_SCALE_CHANNEL = 1, HYC_SCALE_TOKEN = 2 } hyc_scale_kind;
+
+/* bits of the caller-owned status word */
+#define HYC_STATUS_POOL_OVERFLOW 1u /* some rows were stored without their element outliers */
+#define HYC_STATUS_WAIT_EXPIRED 2u  /* a bounded wait on a staged copy ran out              */
+
+/* The compressed form of one activation of `rows` x `cols` (rows = B*S tokens).
+ * Packed codes: byte j of a row holds channel j of each of the 8/bits contiguous
+ * row segments, segment s in bit field s*bits (compress_function.py:176-197);
+ * 8-bit codes are int8 without offset.  cols must be a multiple of 128.        */
+typedef struct {
+  int32_t mode;          /* hyc_mode */
+  int32_t bits;          /* 1,2,4,8 (R) ; 2,4,8 (N) */
+  int64_t rows;          /* T */
+  int32_t cols;          /* D, multiple of 128, <= 65408 */
+  int32_t seq;           /* rows per batch element: row t uses position t % seq of [seq,*] statics; >= 1 */
+  void* codes;           /* u8 [rows, cols*bits/8] */
+  uint32_t* status;      /* one word, OR-ed by kernels; may be NULL */
+
+  /* ---- HYC_MODE_R ---- */
+  int32_t scale_kind;    /* hyc_scale_kind */
+  int32_t scale_dtype;   /* hyc_dtype of `scale` */
+  const void* scale;     /* [] / [cols] / [seq] */
+  const float* thr;      /* one fp32 threshold (device memory) */
+  const void* lowrank;   /* bf16 [seq, cols] = L@R already multiplied, or NULL (rank 0) */
+  uint32_t* pool;        /* outlier entries: (bf16 value bits << 16) | column */
+  uint32_t pool_cap;     /* entries in pool */
+  uint32_t* pool_used;   /* one word: entries reserved so far (compress zeroes it) */
+  uint32_t* row_meta;    /* [rows, 2]: (first entry, count) of each row */
+
+  /* ---- HYC_MODE_N ---- */
+  const int32_t* channels; /* [n_channels] ascending outlier channels */
+  int32_t n_channels;
+  int32_t group;         /* 0: one scale per row; 128: one per 128 channels */
+  int32_t rotate;        /* 0 or the Hadamard block size in {16,64,256,1024,4096}, dividing cols */
+  int32_t _pad;
+  void* out_value;       /* bf16 [rows, n_channels] */
+  float* scales;         /* f32 [rows, cols/group or 1] */
+} hyc_packed;
+
+/* A dense activation as rows of `cols` elements.  chunks == 1: row t starts at
+ * base + t*row_stride.  chunks > 1 ([B,H,S,hd] head layout seen as [B,S,H*hd],
+ * compress_function.py:4-12): row t = (b,s) with b = t / seq, s = t % seq is the
+ * concatenation of `chunks` pieces of cols/chunks elements, piece c starting at
+ * base + b*batch_stride + s*row_stride + c*chunk_stride (strides in elements). */
+typedef struct {
+  void* base;
+  int32_t dtype;         /* hyc_dtype */
+  int32_t chunks;
+  int64_t row_stride;
+  int64_t batch_stride;
+  int64_t chunk_stride;
+} hyc_dense;
+
+typedef enum { HYC_NORM_RMS = 0, HYC_NORM_RMS_GEMMA = 1, HYC_NORM_LAYER = 2 } hyc_norm_kind;
+typedef enum { HYC_ACT_SILU = 0, HYC_ACT_GELU_TANH = 1, HYC_ACT_PRODUCT = 2 } hyc_act_op;
+
+const char* hyc_strerror(int code);
+/* text of the last CUDA error seen by this library on the calling thread */
+const char* hyc_last_cuda_error(void);
+int hyc_version(void);
+
+/* Optional launch tuning for experiments (0 = library default):
+ * threads per row-CTA, staging depth, resident CTAs per SM. */
+int hyc_set_tuning(int threads, int stages, int ctas_per_sm);
+
+/* Compress-only (the sites that are not norms: LoRA-A linear input, SiLU/GELU
+ * input, gate*up operands, Q/K/V).  Replaces the eager chain of
+ * true_divide_outlier_suboutlier_svd_compress, operators/compress_function.py:136-200,
+ * as called from efficient_linear.py:46, efficient_silu.py:35, efficient_gelu.py:35,
+ * efficient_hadamard.py:45-46, efficient_gemm.py:50-51,222. */
+int hyc_compress(const hyc_dense* x, const hyc_packed* out, void* stream);
+
+/* Standalone reconstruction to bf16 (for library-GEMM consumers).  Replaces
+ * true_divide_outlier_suboutlier_svd_decompress, compress_function.py:203-261. */
+int hyc_decompress(const hyc_packed* in, const hyc_dense* out_bf16, void* stream);
+
+/* Fused norm forward + compression of the norm INPUT, one pass over each row.
+ * Replaces _rms_norm_fwd_fused / _layer_norm_fwd_fused followed by the compress
+ * chain (efficient_rmsnorm.py:179-201, efficient_rmsnorm_gemma.py:59,
+ * efficient_layernorm.py:236-257).  y has x's dtype and layout (chunks == 1);
+ * rstd and mean are fp32 [rows] (mean only for HYC_NORM_LAYER). */
+typedef struct {
+  int32_t kind;          /* hyc_norm_kind */
+  float eps;
+  const void* weight;    /* [cols] */
+  const void* bias;      /* [cols] or NULL (required for HYC_NORM_LAYER) */
+  int32_t param_dtype;   /* hyc_dtype of weight/bias */
+  int32_t _pad;
+  void* y;
+  float* rstd;
+  float* mean;
+} hyc_norm_fwd;
+int hyc_norm_compress(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, void* stream);
+
+/* Decompress + norm backward.  Replaces the decompress chain followed by
+ * _rms_norm_bwd_dx_fused/_dwdb or _layer_norm_bwd_dx_fused/_dwdb
+ * (efficient_rmsnorm.py:214-269, efficient_layernorm.py:275-335).
+ * dy: [rows, cols] bf16 or fp32 (rounded to bf16 first, efficient_rmsnorm.py:216);
+ * dx: bf16 [rows, cols].  ref_compat_c2 != 0 keeps the reference's mean(w*dy)
+ * term in the RMSNorm formula (efficient_rmsnorm.py:103-104).  When dweight is
+ * not NULL, `partials` must hold hyc_norm_bwd_partial_rows() * cols floats
+ * (twice that when dbias is not NULL); dweight/dbias are fp32 [cols]. */
+typedef struct {
+  int32_t kind;
+  int32_t ref_compat_c2;
+  const void* weight;
+  int32_t param_dtype;
+  int32_t dy_dtype;
+  const void* dy;
+  const float* rstd;
+  const float* mean;     /* HYC_NORM_LAYER only */
+  void* dx;
+  float* dweight;        /* NULL: weight is frozen, skip */
+  float* dbias;          /* NULL: skip */
+  float* partials;       /* scratch, see above */
+} hyc_norm_bwd_args;
+int hyc_norm_bwd_partial_rows(void);
+int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* args, void* stream);
+
+/* Decompress + activation backward.  Replaces the decompress chain plus the
+ * eager gradient formulas of efficient_silu.py:44-53, efficient_gelu.py:44-64
+ * (tanh approximation) and efficient_hadamard.py:56-66 (g*x2, x1*g).
+ * g and the outputs share `g_dtype` (bf16 or fp32), contiguous [rows, cols].
+ * saved2/dx2 are used by HYC_ACT_PRODUCT only. */
+int hyc_act_bwd(int op, const hyc_packed* saved1, const hyc_packed* saved2, const void* g,
+                int g_dtype, void* dx1, void* dx2, void* stream);
+
+/* Calibration for HYC_MODE_N: fp32 column absmax of x accumulated into
+ * score[cols] (caller zeroes it first; repeated calls accumulate the max), then
+ * the k best channels, ties to the lower index, written ascending.  Plays the
+ * role get_statistics (compress_function.py:292-340) plays for the reference
+ * mode.  `rank_scratch` holds cols int32. */
+int hyc_channel_absmax(const hyc_dense* x, int64_t rows, int32_t cols, int32_t seq, float* score, void* stream);
+int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* channels,
+                        int32_t* rank_scratch, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HYC_B200_H */

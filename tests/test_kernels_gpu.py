@@ -1,0 +1,329 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU
+oracle and the committed golden fixtures.
+
+Bars: packed codes, outlier indices/values, scales and reconstructions are
+compared BIT-EXACTLY; norm outputs and gradients (floating point, different
+summation order) within 1e-2 relative of the row scale; weight gradients by
+cosine >= 0.999 as well."""
+import itertools
+
+import pytest
+import torch
+
+from hyc_lora_b200 import synthetic
+from oracle import hyc_oracle as oc
+from tests import golden_io
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def pk():
+    from hyc_lora_b200 import packed
+    return packed
+
+
+def _rel_err(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return ((a - b).abs().max() / b.abs().max().clamp_min(1e-20)).item()
+
+
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.float().cpu().flatten(), b.float().cpu().flatten(), dim=0).item()
+
+
+def _lowrank(case):
+    if not case.rank:
+        return None
+    return (oc.fit_rows(case.L, case.x.shape[-2]) @ case.R).to(torch.bfloat16)
+
+
+def _oracle_coo_flat(c: oc.RCompressed):
+    b, s, d = c.shape
+    return c.out_index[0] * (s * d) + c.out_index[1] * d + c.out_index[2], c.out_value
+
+
+# ------------------------------------------------------------------ reference mode vs golden fixtures
+
+@pytest.mark.parametrize("case", list(golden_io.small_cases()), ids=lambda c: c.name)
+def test_r_mode_small_fixture(pk, case):
+    lr = _lowrank(case)
+    p = pk.compress_r(case.x.to(DEV), case.thr.to(DEV), case.scale.to(DEV), case.bits,
+                      lowrank=None if lr is None else lr.to(DEV), outlier_ratio=0.02)
+    codes = p.codes.cpu().reshape(case.codes.shape)
+    assert torch.equal(codes.view(torch.uint8), case.codes.view(torch.uint8))
+    flat, val = p.outlier_coo()
+    b, s, d = case.x.shape
+    gold_flat = case.coo_index[0] * (s * d) + case.coo_index[1] * d + case.coo_index[2]
+    assert torch.equal(flat, gold_flat)
+    assert torch.equal(val.view(torch.int16), case.coo_value.view(torch.int16))
+    xh = pk.decompress(p).cpu()
+    assert torch.equal(xh, case.xhat)
+    assert not p.overflowed() and not p.wait_expired()
+
+
+def test_config1_layernorm_compress_roundtrip_and_lora_grads(pk):
+    g = golden_io.config1()
+    x, _ = synthetic.roundtrip_activation()
+    a, grad = synthetic.lora_a_problem()
+    w, b = torch.ones(768), torch.zeros(768)
+    p, y, rstd, mean = pk.compress_r(x.to(DEV), g.thr.to(DEV), g.scale.to(DEV), 4, outlier_ratio=0.01,
+                                     norm=dict(kind="ln", weight=w.to(DEV), bias=b.to(DEV), eps=1e-5))
+    y_o, mean_o, rstd_o = oc.norm_forward(x, w, b, 1e-5, "ln")
+    assert _rel_err(y, y_o) < 1e-4 and _rel_err(mean, mean_o) < 1e-4 and _rel_err(rstd, rstd_o) < 1e-5
+    assert torch.equal(p.codes.cpu().reshape(g.codes.shape), g.codes)
+    flat, val = p.outlier_coo()
+    assert torch.equal(flat.int(), g.coo_flat) and torch.equal(val, g.coo_value)
+    xh = pk.decompress(p)
+    assert golden_io.sha_bits(xh.cpu()) == g.xhat_sha256
+    # LoRA-A gradients from the reconstructed input (library GEMM on the decompressed rows)
+    dx = grad.to(DEV) @ a.to(DEV)
+    da = torch.einsum("bsr,bsd->rd", grad.to(DEV), xh.float())
+    assert _rel_err(dx[0, :8], g.dX0) < 1e-5
+    assert _cos(da, g.dA) > 0.99999 and _rel_err(da, g.dA) < 1e-3
+
+
+@pytest.mark.parametrize("dtype,bits,method", list(itertools.product(
+    [torch.bfloat16, torch.float32], [1, 2, 4, 8], ["per-tensor", "per-channel", "per-token"])))
+def test_r_mode_against_oracle_ragged_rows(pk, dtype, bits, method):
+    # 3*37 = 111 rows: not a multiple of anything; D = 768 is not a power of two
+    x, _ = synthetic.roundtrip_activation(3, 37, 768, planted=5, gain=20.0, dtype=dtype, salt=bits)
+    thr, L, R, scale = oc.r_calibrate(x, 0.01, 1.0, bits, method, 0)
+    c = oc.r_compress(x, thr, scale, bits, 1.0)
+    p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), bits)
+    assert torch.equal(p.codes.cpu().reshape(c.codes.shape).view(torch.uint8), c.codes.view(torch.uint8))
+    flat, val = p.outlier_coo()
+    o_flat, o_val = _oracle_coo_flat(c)
+    assert torch.equal(flat, o_flat) and torch.equal(val, o_val)
+    assert torch.equal(pk.decompress(p).cpu(), oc.r_decompress(c))
+
+
+def test_r_mode_head_layout(pk):
+    x, _ = synthetic.roundtrip_activation(2, 24, 768, planted=4, dtype=torch.bfloat16, salt=3)
+    heads = x.reshape(2, 24, 12, 64).permute(0, 2, 1, 3)        # [B,H,S,hd] view, as the attention code makes it
+    thr, L, R, scale = oc.r_calibrate(heads, 0.02, 1.0, 4, "per-channel", 0)
+    c = oc.r_compress(heads, thr, scale, 4, 1.0)
+    view = x.to(DEV).reshape(2, 24, 12, 64).permute(0, 2, 1, 3)   # strided head view
+    copy = view.contiguous()                                      # really transposed copy
+    for h in (view, copy):
+        p = pk.compress_r(h, thr.to(DEV), scale.to(DEV), 4, outlier_ratio=0.02)
+        assert torch.equal(p.codes.cpu().reshape(c.codes.shape), c.codes)
+        out = pk.decompress(p, num_heads=12)
+        assert out.shape == (2, 12, 24, 64)
+        assert torch.equal(out.cpu(), oc.r_decompress(c, num_heads=12))
+
+
+def test_r_mode_pool_overflow_degrades_to_quantised_rows(pk):
+    x, _ = synthetic.roundtrip_activation(2, 16, 256, planted=4, dtype=torch.bfloat16, salt=9)
+    thr, L, R, scale = oc.r_calibrate(x, 0.05, 1.0, 8, "per-channel", 0)
+    p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), 8, pool_entries=7)
+    assert p.overflowed()
+    meta = p.row_meta.cpu()
+    assert int(meta[:, 1].sum()) <= 7
+    # rows that lost their pool slot were quantised whole: identical to compressing with thr = +inf
+    c_inf = oc.r_compress(x, torch.tensor(float("inf")), scale, 8, 1.0)
+    lost = (meta[:, 1] == 0)
+    got = p.codes.cpu().reshape(32, 256).view(torch.int8)
+    want = c_inf.codes.reshape(32, 256)
+    c_thr = oc.r_compress(x, thr, scale, 8, 1.0).codes.reshape(32, 256)
+    had_outliers = (c_thr != want).any(dim=1)
+    sel = lost & had_outliers
+    assert sel.any() and torch.equal(got[sel], want[sel])
+
+
+# ------------------------------------------------------------------ north-star mode vs oracle
+
+N_CASES = [
+    # rows, D, dtype, bits, group, rotate, fraction
+    (64, 1024, torch.bfloat16, 4, 0, 0, 0.01),
+    (64, 1024, torch.bfloat16, 4, 128, 0, 0.01),
+    (37, 768, torch.float32, 4, 0, 0, 0.01),
+    (37, 768, torch.float32, 2, 128, 256, 0.02),
+    (50, 4096, torch.bfloat16, 2, 0, 256, 0.02),
+    (50, 4096, torch.bfloat16, 8, 128, 256, 0.005),
+    (50, 4096, torch.bfloat16, 4, 0, 4096, 0.01),
+    (33, 4096, torch.bfloat16, 4, 128, 1024, 0.01),
+    (33, 1024, torch.bfloat16, 4, 0, 64, 0.01),
+    (33, 1024, torch.float32, 8, 128, 16, 0.0),
+    (20, 11008, torch.bfloat16, 4, 0, 256, 0.01),
+    (20, 14336, torch.bfloat16, 2, 128, 0, 0.02),
+    (1, 4096, torch.bfloat16, 4, 0, 0, 0.01),
+    (2000, 4096, torch.bfloat16, 4, 0, 256, 0.01),
+]
+
+
+@pytest.mark.parametrize("rows,d,dtype,bits,group,rotate,frac", N_CASES)
+def test_n_mode_against_oracle(pk, rows, d, dtype, bits, group, rotate, frac):
+    x, _ = synthetic.sweep_activation(rows, d, max(frac, 0.005), dtype=dtype, salt=bits + group + rotate)
+    k = oc.n_outlier_count(d, frac)
+    xd = x.to(DEV)
+    score = pk.channel_absmax(xd)
+    assert torch.equal(score.cpu(), oc.n_channel_scores(x))
+    ch = pk.select_channels(score, k) if k else None
+    ch_o = oc.n_select_channels(oc.n_channel_scores(x), k)
+    if k:
+        assert torch.equal(ch.cpu(), ch_o)
+    c = oc.n_compress(x, ch_o, bits, group, rotate)
+    p = pk.compress_n(xd, ch, bits, group, rotate)
+    assert torch.equal(p.scales.cpu(), c.scales)
+    assert torch.equal(p.codes.cpu().view(torch.uint8), c.codes.view(torch.uint8))
+    if k:
+        assert torch.equal(p.out_value.cpu(), c.out_value)
+    xh = pk.decompress(p).cpu().reshape(rows, d)
+    assert torch.equal(xh, oc.n_decompress(c))
+    assert not p.wait_expired()
+
+
+def test_n_mode_ties_zero_rows_and_nonfinite_values(pk):
+    x = torch.zeros(16, 512, dtype=torch.bfloat16)
+    x[3, 5] = 2.0
+    x[7, 5] = -2.0
+    x[2, 100] = 2.0         # ties with channel 5
+    x[2, 101] = 2.0         # ties again: the lower index wins the last place
+    x[9, 300] = float("inf")
+    x[10, 301] = float("nan")   # NaN never wins a max: the channel scores 0
+    xd = x.to(DEV)
+    score = pk.channel_absmax(xd)
+    assert score.cpu()[301] == 0 and score.cpu()[300] == float("inf")
+    ch = pk.select_channels(score, 3)
+    assert ch.cpu().tolist() == [5, 100, 300]
+    p = pk.compress_n(xd, ch, 4, 128, 0)
+    xh = pk.decompress(p).cpu().reshape(16, 512)
+    keep = [c for c in range(512) if c not in (101, 301)]
+    assert torch.equal(xh[:, keep].float(), x[:, keep].float())
+    assert xh[2, 101] == 2.0 and xh[10, 301] == 0
+    assert torch.equal(p.scales.cpu()[0], torch.ones(4))
+    assert not p.wait_expired()
+
+
+# ------------------------------------------------------------------ fused norm forward
+
+@pytest.mark.parametrize("kind,dtype,d", [("rms", torch.bfloat16, 4096), ("rms_gemma", torch.bfloat16, 1024),
+                                          ("ln", torch.float32, 768), ("ln", torch.bfloat16, 3072),
+                                          ("rms", torch.float32, 768), ("rms", torch.bfloat16, 11008)])
+def test_norm_forward_matches_oracle(pk, kind, dtype, d):
+    rows = 45
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=dtype, salt=d)
+    w = synthetic.norm_weight(d, 0.1, dtype=dtype)
+    b = (0.05 * torch.randn(d, generator=torch.Generator().manual_seed(d))).to(dtype)
+    k = oc.n_outlier_count(d, 0.01)
+    ch = oc.n_select_channels(oc.n_channel_scores(x), k)
+    p, y, rstd, mean = pk.compress_n(x.to(DEV), ch.to(DEV), 4, 0, 0,
+                                     norm=dict(kind=kind, weight=w.to(DEV), bias=b.to(DEV), eps=1e-5))
+    y_o, mean_o, rstd_o = oc.norm_forward(x, w, b, 1e-5, kind)
+    assert y.dtype == x.dtype and y.shape == x.shape
+    # 1e-2 relative at bf16 (the output is rounded to bf16 once on both sides)
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-4
+    assert ((y.float().cpu() - y_o.float()).abs() <= tol * y_o.float().abs() + 1e-3).all()
+    assert _rel_err(rstd, rstd_o) < 1e-5
+    if kind == "ln":
+        assert (mean.cpu() - mean_o).abs().max() < 1e-4 * x.float().abs().max()
+    # the compressed copy is of the norm INPUT and is bit-exact
+    c = oc.n_compress(x, ch, 4, 0, 0)
+    assert torch.equal(p.codes.cpu(), c.codes) and torch.equal(p.scales.cpu(), c.scales)
+
+
+# ------------------------------------------------------------------ backward kernels
+
+def _packed_pair(pk, x, mode, bits, group=0, rotate=0):
+    """Compress on the GPU and with the oracle; returns (packed, oracle reconstruction)."""
+    if mode == "N":
+        d = x.shape[-1]
+        ch = oc.n_select_channels(oc.n_channel_scores(x), oc.n_outlier_count(d, 0.01))
+        p = pk.compress_n(x.to(DEV), ch.to(DEV), bits, group, rotate)
+        xh = oc.n_decompress(oc.n_compress(x.reshape(-1, d), ch, bits, group, rotate)).reshape(x.shape)
+    else:
+        thr, L, R, scale = oc.r_calibrate(x, 0.01, 1.0, bits, "per-channel", 0)
+        p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), bits)
+        xh = oc.r_decompress(oc.r_compress(x, thr, scale, bits, 1.0))
+    return p, xh
+
+
+@pytest.mark.parametrize("kind,mode,bits,gdtype,d,rotate", [
+    ("rms", "N", 4, torch.bfloat16, 4096, 256), ("rms", "R", 4, torch.bfloat16, 4096, 0),
+    ("rms_gemma", "N", 8, torch.bfloat16, 1024, 0), ("ln", "R", 4, torch.float32, 768, 0),
+    ("ln", "N", 2, torch.bfloat16, 3072, 0), ("rms", "N", 4, torch.float32, 768, 256)])
+def test_norm_backward_matches_oracle(pk, kind, mode, bits, gdtype, d, rotate):
+    b, s = 3, 41
+    x, _ = synthetic.roundtrip_activation(b, s, d, planted=6, gain=20.0, dtype=torch.bfloat16, salt=d + bits)
+    w = synthetic.norm_weight(d, 0.1, dtype=torch.float32)
+    dy = torch.randn(b, s, d, generator=torch.Generator().manual_seed(5)).to(gdtype)
+    p, xh = _packed_pair(pk, x, mode, bits, 0, rotate)
+    _, mean_o, rstd_o = oc.norm_forward(x, w, torch.zeros(d), 1e-5, kind)
+    for compat in (True, False):
+        dx_o, dw_o, db_o = oc.norm_backward(xh, dy, w, mean_o, rstd_o, kind, ref_compat_c2=compat)
+        dx, dw, db = pk.norm_bwd(p, dy.to(DEV), w.to(DEV), rstd_o.to(DEV),
+                                 None if mean_o is None else mean_o.to(DEV), kind, ref_compat_c2=compat,
+                                 need_dweight=True, need_dbias=(kind == "ln"))
+        assert dx.dtype == torch.bfloat16 and dx.shape == dy.shape
+        assert _rel_err(dx, dx_o) < 1e-2 and _cos(dx, dx_o) > 0.9999
+        assert _cos(dw, dw_o) > 0.9999 and _rel_err(dw, dw_o) < 1e-3
+        if kind == "ln":
+            assert _rel_err(db, db_o) < 1e-3
+    dx2, dw2, _ = pk.norm_bwd(p, dy.to(DEV), w.to(DEV), rstd_o.to(DEV),
+                              None if mean_o is None else mean_o.to(DEV), kind)
+    assert dw2 is None and _rel_err(dx2, oc.norm_backward(xh, dy, w, mean_o, rstd_o, kind)[0]) < 1e-2
+
+
+@pytest.mark.parametrize("op,mode,bits,gdtype,d,rotate", [
+    ("silu", "N", 4, torch.bfloat16, 11008, 256), ("silu", "R", 8, torch.bfloat16, 1024, 0),
+    ("gelu", "R", 4, torch.float32, 3072, 0), ("gelu", "N", 4, torch.bfloat16, 3072, 0),
+    ("product", "N", 4, torch.bfloat16, 11008, 0), ("product", "R", 4, torch.bfloat16, 1024, 0),
+    ("product", "N", 2, torch.float32, 1024, 256)])
+def test_activation_backward_matches_oracle(pk, op, mode, bits, gdtype, d, rotate):
+    b, s = 2, 23
+    x1, _ = synthetic.roundtrip_activation(b, s, d, planted=6, gain=4.0, dtype=torch.bfloat16, salt=d)
+    g = torch.randn(b, s, d, generator=torch.Generator().manual_seed(6)).to(gdtype)
+    p1, xh1 = _packed_pair(pk, x1, mode, bits, 0, rotate)
+    if op == "product":
+        x2, _ = synthetic.roundtrip_activation(b, s, d, planted=6, gain=4.0, dtype=torch.bfloat16, salt=d + 1)
+        p2, xh2 = _packed_pair(pk, x2, mode, bits, 0, rotate)
+        d1, d2 = pk.act_bwd("product", p1, g.to(DEV), p2)
+        o1, o2 = oc.product_backward(xh1, xh2, g)
+        assert d1.dtype == o1.dtype and torch.equal(d1.cpu(), o1) and torch.equal(d2.cpu(), o2)
+    else:
+        dx = pk.act_bwd(op, p1, g.to(DEV))
+        o = (oc.silu_backward if op == "silu" else oc.gelu_backward)(xh1, g)
+        assert dx.dtype == o.dtype
+        assert ((dx.float().cpu() - o.float()).abs() <= 1e-2 * o.float().abs() + 1e-4).all()
+
+
+# ------------------------------------------------------------------ full-size properties (configuration 5 shapes)
+
+@pytest.mark.parametrize("bits,group,rotate", [(4, 0, 0), (2, 128, 256), (8, 0, 256)])
+def test_full_size_roundtrip_properties(pk, bits, group, rotate):
+    rows, d = 16384, 4096
+    x, planted = synthetic.sweep_activation(rows, d, 0.01, salt=40 + bits)
+    xd = x.to(DEV)
+    ch = pk.select_channels(pk.channel_absmax(xd), oc.n_outlier_count(d, 0.01))
+    assert set(planted.tolist()) == set(ch.cpu().tolist())
+    w = synthetic.norm_weight(d, 0.1)
+    p, y, rstd, _ = pk.compress_n(xd, ch, bits, group, rotate,
+                                  norm=dict(kind="rms", weight=w.to(DEV), bias=None, eps=1e-5))
+    xh = pk.decompress(p).reshape(rows, d)
+    # outlier channels are carried exactly
+    assert torch.equal(xh[:, ch.long()], xd[:, ch.long()])
+    # a slice of rows against the oracle, bit for bit
+    sl = slice(5000, 5256)
+    c = oc.n_compress(x[sl], ch.cpu(), bits, group, rotate)
+    assert torch.equal(p.codes[sl].cpu().view(torch.uint8), c.codes.view(torch.uint8))
+    assert torch.equal(xh[sl].cpu(), oc.n_decompress(c))
+    # checksum of checksums over the whole tensor: recompressing the reconstruction
+    # keeps the scales within one bf16 rounding and the error bounded by half a step
+    body = xd.float()
+    body[:, ch.long()] = 0
+    err = (xh.float() - xd.float())
+    err[:, ch.long()] = 0
+    g = d if group == 0 else group
+    if not rotate:
+        step = p.scales.repeat_interleave(g, dim=1)
+        assert bool((err.abs() <= 0.5 * step * 1.01 + 0.008 * body.abs()).all())
+    # the rotation is orthogonal, so in either case the row error norm is bounded by
+    # half a quantisation step per element plus the bf16 rounding of the output
+    bound = (g * (0.5 * p.scales) ** 2).sum(dim=1).sqrt() * 1.01 + 0.008 * body.norm(dim=1) + 1e-3
+    assert bool((err.norm(dim=1) <= bound).all())
+    y_o, _, rstd_o = oc.norm_forward(x[sl], w, None, 1e-5, "rms")
+    assert ((y[sl].float().cpu() - y_o.float()).abs() <= 1e-2 * y_o.float().abs() + 1e-3).all()
+    assert _rel_err(rstd[sl], rstd_o) < 1e-5
+    assert not p.wait_expired()
