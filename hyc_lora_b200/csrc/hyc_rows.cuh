@@ -347,7 +347,9 @@ __device__ void r_quant_row(const PackedDev& p, const Work& w, const XT* xs, lon
         const float sc = per_channel ? w.cscale[col + e] : sc_row;
         float q = __fdiv_rn(x, sc);
         if (kBf16) q = bf16_round(q);
-        const int qi = clampi(__float2int_rn(q), C::kLo, C::kHi) + C::kOff;
+        // a NaN quotient (0/0 on a channel whose calibrated range is empty) is stored as
+        // byte value 0, which is what the eager float -> uint8 / int8 cast produces
+        const int qi = (q != q) ? 0 : clampi(__float2int_rn(q), C::kLo, C::kHi) + C::kOff;
         const uint32_t c = (static_cast<uint32_t>(qi) & 0xffu) << (s * BITS);
         if (e < 4) b0 |= c << (8 * e); else b1 |= c << (8 * (e - 4));
       }

