@@ -1,6 +1,6 @@
 // Library-wide state, error strings, tuning knobs and the forward entry points
 // (argument checks + launch planning; the kernels are instantiated elsewhere).
-#include "hyc_fwd.cuh"
+#include "hyc_fwd_fast.cuh"
 
 namespace hyc {
 
@@ -21,11 +21,18 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
   }
   if (out->rows == 0) return HYC_OK;
   const int es = x->dtype == HYC_BF16 ? 2 : 4;
+  const FastPlan fast = plan_fast(out, es);
   LayoutReq req;
   fill_req_packed(&req, out, true);
   req.slot_bytes = static_cast<uint32_t>(out->cols) * es;
+  if (fast.ok) {
+    req.rot = fast.rot;
+    req.osm = true;
+    req.wsm = norm != nullptr;
+    req.bsm = norm != nullptr && norm->kind == HYC_NORM_LAYER;
+  }
   LaunchPlan plan;
-  rc = plan_launch(req, out->rows, &plan);
+  rc = plan_launch(req, out->rows, &plan, 0, fast.ok ? fast.threads : 0);
   if (rc) return rc;
   FwdArgs a;
   memset(&a, 0, sizeof(a));
@@ -43,6 +50,9 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
     cudaError_t e = cudaMemsetAsync(out->pool_used, 0, sizeof(uint32_t), stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(pool_used)");
   }
+  if (fast.ok)
+    return x->dtype == HYC_BF16 ? launch_fwd_fast_bf16(a, plan, fast, norm != nullptr, stream)
+                                : launch_fwd_fast_f32(a, plan, fast, norm != nullptr, stream);
   return x->dtype == HYC_BF16 ? launch_fwd_bf16(a, plan, norm != nullptr, stream)
                               : launch_fwd_f32(a, plan, norm != nullptr, stream);
 }

@@ -42,7 +42,7 @@ struct SmemLayout {
   int stages;
   uint32_t slot_bytes;
   uint32_t off_slots, off_red, off_misc, off_omask, off_chan, off_gamax, off_ginv, off_rot, off_list, off_cscale,
-      off_xr, off_omask2, off_chan2, off_cscale2, off_xr2, off_acc;
+      off_xr, off_omask2, off_chan2, off_cscale2, off_xr2, off_acc, off_wsm, off_bsm, off_osm;
   uint32_t total;
 };
 
@@ -52,6 +52,8 @@ struct LayoutReq {
   int k = 0, k2 = 0;
   bool nmode = false, group = false, rot = false, list = false, cscale = false, xr = false;
   bool second = false, nmode2 = false, cscale2 = false;
+  bool wsm = false, bsm = false;  // fp32 norm weight / bias rows
+  bool osm = false;               // fp32 originals of the outlier channels, ring of 3 rows
   int acc_rows = 0;  // fp32 [acc_rows][D] accumulators
 };
 
@@ -61,11 +63,11 @@ inline SmemLayout make_layout(const LayoutReq& r, int stages) {
   SmemLayout L;
   memset(&L, 0, sizeof(L));
   uint32_t off = 64;  // mbarriers
-  L.off_red = off; off += 4 * 64 * 4;
+  L.off_red = off; off += 6 * 64 * 4;
   L.off_misc = off; off += 64;
   auto take = [&](uint32_t bytes) { uint32_t o = off; off = align_up(off + bytes, 16); return o; };
   if (r.nmode) { L.off_omask = take(r.D / 32 * 4); L.off_chan = take((r.k > 0 ? r.k : 1) * 4); }
-  if (r.group) { L.off_gamax = take(r.D / 128 * 4); L.off_ginv = take(r.D / 128 * 4); }
+  if (r.group) { L.off_gamax = take(r.D / 128 * 4 * 2); L.off_ginv = take(r.D / 128 * 4); }  // gamax: two row parities
   if (r.rot) L.off_rot = take(r.D * 4);
   if (r.list) L.off_list = take(r.D * 4);
   if (r.cscale) L.off_cscale = take(r.D * 4);
@@ -75,6 +77,9 @@ inline SmemLayout make_layout(const LayoutReq& r, int stages) {
     if (r.cscale2) L.off_cscale2 = take(r.D * 4);
     L.off_xr2 = take(r.D * 2);
   }
+  if (r.wsm) L.off_wsm = take(r.D * 4);
+  if (r.bsm) L.off_bsm = take(r.D * 4);
+  if (r.osm) L.off_osm = take(3u * (r.k > 0 ? r.k : 1) * 4);
   if (r.acc_rows) L.off_acc = take(static_cast<uint32_t>(r.acc_rows) * r.D * 4);
   off = align_up(off, 128);
   L.off_slots = off;
@@ -92,8 +97,8 @@ struct LaunchPlan {
 // Pick threads, staging depth and CTAs per SM so that the staging rings of the
 // resident CTAs fill most of an SM's shared memory; the grid is that many CTAs
 // on every SM (or one CTA per row when there are fewer rows).
-inline int plan_launch(const LayoutReq& r, long long rows, LaunchPlan* out, int grid_cap = 0) {
-  int threads = g_tune_threads ? g_tune_threads : (r.D <= 1024 ? 64 : r.D <= 4096 ? 128 : 256);
+inline int plan_launch(const LayoutReq& r, long long rows, LaunchPlan* out, int grid_cap = 0, int force_threads = 0) {
+  int threads = force_threads ? force_threads : g_tune_threads ? g_tune_threads : (r.D <= 1024 ? 64 : r.D <= 4096 ? 128 : 256);
   int stages = g_tune_stages ? g_tune_stages : 3;
   if (stages > kMaxStages) stages = kMaxStages;
   SmemLayout L = make_layout(r, stages);

@@ -64,6 +64,14 @@ struct CodeTraits {
 
 __device__ __forceinline__ int clampi(int v, int lo, int hi) { return max(lo, min(hi, v)); }
 
+// rint(x * inv) with a single rounding of the exact product: the fused multiply-add
+// against 1.5 * 2^23 leaves the integer in the low mantissa bits (|x * inv| < 2^22).
+constexpr float kRoundMagic = 12582912.f;
+constexpr uint32_t kRoundMagicBits = 0x4B400000u;
+__device__ __forceinline__ int round_product(float x, float inv) {
+  return __float_as_int(__fmaf_rn(x, inv, kRoundMagic)) - static_cast<int>(kRoundMagicBits);
+}
+
 __device__ __forceinline__ uint32_t mask8(const uint32_t* omask, int col) {
   return (omask[col >> 5] >> (col & 31)) & 0xffu;
 }
@@ -219,7 +227,7 @@ __device__ void n_quant_row(const Work& w, const ST* src, float inv_row, unsigne
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const float x = ((m >> e) & 1u) ? 0.f : f[e];
-        const int q = clampi(__float2int_rn(x * inv), C::kLo, C::kHi) + C::kOff;
+        const int q = clampi(round_product(x, inv), C::kLo, C::kHi) + C::kOff;
         const uint32_t c = (static_cast<uint32_t>(q) & 0xffu) << (s * BITS);
         if (e < 4) b0 |= c << (8 * e); else b1 |= c << (8 * (e - 4));
       }

@@ -294,9 +294,10 @@ def n_compress(x: torch.Tensor, channels: torch.Tensor, bits: int, group: int = 
     zeroed in place; the remainder is (optionally) rotated in fp32; the scale
     of a row / 128-channel group is ``absmax / qmax`` with
     ``qmax = 2^(bits-1) - 1`` and the code is
-    ``clamp(rint(x * (qmax / absmax)))`` -- one fp32 multiply per element by a
-    reciprocal that is itself one IEEE division, so CPU and GPU agree bit for
-    bit.  A zero absmax gives scale 1 and codes 0."""
+    ``clamp(rint(x * (qmax / absmax)))`` -- the reciprocal is one IEEE fp32
+    division and the product is rounded to an integer once, from its exact
+    value, so CPU and GPU agree bit for bit on finite inputs (codes of rows
+    holding inf/NaN are unspecified).  A zero absmax gives scale 1 and codes 0."""
     assert bits in (2, 4, 8) and x.dim() == 2
     t, d = x.shape
     half = 2 ** (bits - 1)
@@ -315,8 +316,11 @@ def n_compress(x: torch.Tensor, channels: torch.Tensor, bits: int, group: int = 
     one = torch.ones_like(amax)
     scales = torch.where(live, amax / qmax, one)
     inv = torch.where(live, torch.tensor(qmax) / amax, one)
-    q = torch.clamp(torch.round(vg * inv.unsqueeze(-1)), min=-half, max=half - 1).reshape(t, d)
-    q = torch.nan_to_num(q, nan=0.0)
+    # the product is rounded ONCE, from its exact value (fp32 x fp32 is exact in fp64),
+    # which is what a fused multiply-add against a rounding constant computes on the GPU
+    prod = vg.double() * inv.unsqueeze(-1).double()
+    q = torch.clamp(torch.round(prod), min=-half, max=half - 1).reshape(t, d)
+    q = torch.nan_to_num(q, nan=0.0).float()
     if bits == 8:
         codes = pack_codes(q, 8)
     else:
