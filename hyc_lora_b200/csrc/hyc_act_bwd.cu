@@ -1,5 +1,5 @@
 // Decompress + SiLU / GELU(tanh) / product backward.
-#include "hyc_host.cuh"
+#include "hyc_bwd_fast.cuh"
 
 namespace hyc {
 
@@ -123,6 +123,45 @@ int hyc_act_bwd(int op, const hyc_packed* s1, const hyc_packed* s2, const void* 
   }
   if (s1->rows == 0) return HYC_OK;
   const int D = s1->cols;
+  {
+    const BwdPlan bp = plan_bwd_fast(s1, prod ? s2 : nullptr, 4, false, 0, 512, 0,
+                                     align_up(static_cast<uint32_t>(D) * s1->bits / 8, 128) * (prod ? 2 : 1) +
+                                         static_cast<uint32_t>(D) * (g_dtype == HYC_BF16 ? 2 : 4));
+    if (bp.ok) {
+      ActFastArgs fa;
+      memset(&fa, 0, sizeof(fa));
+      fa.p1 = to_dev(s1);
+      if (prod) fa.p2 = to_dev(s2);
+      fa.g = static_cast<const unsigned char*>(g);
+      fa.dx1 = static_cast<unsigned char*>(dx1);
+      fa.dx2 = static_cast<unsigned char*>(dx2);
+      fa.L = bp.L;
+#define HYC_ACTF_OP(B, UP, RT, GT, OPV)                                                         \
+  {                                                                                             \
+    auto kern = act_bwd_n_fast_kernel<B, UP, RT, GT, OPV>;                                      \
+    rc = set_smem(kern, bp.L.total);                                                            \
+    if (rc) return rc;                                                                          \
+    kern<<<bp.grid, bp.threads, bp.L.total, stream>>>(fa);                                      \
+  }
+#define HYC_ACTF(B, UP, RT)                                                                     \
+  {                                                                                             \
+    if (g_dtype == HYC_BF16) {                                                                  \
+      if (op == HYC_ACT_SILU) HYC_ACTF_OP(B, UP, RT, __nv_bfloat16, HYC_ACT_SILU)               \
+      else if (op == HYC_ACT_GELU_TANH) HYC_ACTF_OP(B, UP, RT, __nv_bfloat16, HYC_ACT_GELU_TANH) \
+      else HYC_ACTF_OP(B, UP, RT, __nv_bfloat16, HYC_ACT_PRODUCT)                               \
+    } else {                                                                                    \
+      if (op == HYC_ACT_SILU) HYC_ACTF_OP(B, UP, RT, float, HYC_ACT_SILU)                       \
+      else if (op == HYC_ACT_GELU_TANH) HYC_ACTF_OP(B, UP, RT, float, HYC_ACT_GELU_TANH)        \
+      else HYC_ACTF_OP(B, UP, RT, float, HYC_ACT_PRODUCT)                                       \
+    }                                                                                           \
+  }
+      HYC_BWD_DISPATCH(bp, s1->bits, 4, HYC_ACTF)
+#undef HYC_ACTF
+#undef HYC_ACTF_OP
+      cudaError_t e = cudaGetLastError();
+      return e == cudaSuccess ? HYC_OK : cuda_fail(e, "act_bwd_n_fast_kernel launch");
+    }
+  }
   const uint32_t cb = static_cast<uint32_t>(D) * s1->bits / 8;
   LayoutReq req;
   fill_req_packed(&req, s1, false);

@@ -32,7 +32,9 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
     req.bsm = norm != nullptr && norm->kind == HYC_NORM_LAYER;
   }
   LaunchPlan plan;
-  rc = plan_launch(req, out->rows, &plan, 0, fast.ok ? fast.threads : 0);
+  // the register-resident kernel frees a slot right after pass 1: two stages suffice and
+  // leave room for more resident CTAs
+  rc = plan_launch(req, out->rows, &plan, 0, fast.ok ? fast.threads : 0, fast.ok ? 2 : 3);
   if (rc) return rc;
   FwdArgs a;
   memset(&a, 0, sizeof(a));

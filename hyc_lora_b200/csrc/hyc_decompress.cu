@@ -1,5 +1,5 @@
 // Packed activation -> bf16 rows.
-#include "hyc_host.cuh"
+#include "hyc_bwd_fast.cuh"
 
 namespace hyc {
 
@@ -73,6 +73,30 @@ int hyc_decompress(const hyc_packed* in, const hyc_dense* o, void* stream_) {
   if (rc) return rc;
   if (o->dtype != HYC_BF16) return HYC_ERR_DTYPE;
   if (in->rows == 0) return HYC_OK;
+  {
+    // register-resident kernel for the channel-outlier mode
+    const BwdPlan bp = plan_bwd_fast(in, nullptr, 4, false, 0, 512, 0, static_cast<uint32_t>(in->cols) * in->bits / 8);
+    if (bp.ok) {
+      DecFastArgs fa;
+      memset(&fa, 0, sizeof(fa));
+      fa.p = to_dev(in);
+      fa.out = static_cast<__nv_bfloat16*>(o->base);
+      fa.row_stride = o->row_stride; fa.batch_stride = o->batch_stride; fa.chunk_stride = o->chunk_stride;
+      fa.chunks = o->chunks;
+      fa.L = bp.L;
+#define HYC_DECF(B, UP, RT)                                                                     \
+  {                                                                                             \
+    auto kern = decompress_n_fast_kernel<B, UP, RT>;                                            \
+    rc = set_smem(kern, bp.L.total);                                                            \
+    if (rc) return rc;                                                                          \
+    kern<<<bp.grid, bp.threads, bp.L.total, stream>>>(fa);                                      \
+  }
+      HYC_BWD_DISPATCH(bp, in->bits, 4, HYC_DECF)
+#undef HYC_DECF
+      cudaError_t e = cudaGetLastError();
+      return e == cudaSuccess ? HYC_OK : cuda_fail(e, "decompress_n_fast_kernel launch");
+    }
+  }
   LayoutReq req;
   fill_req_packed(&req, in, false);
   req.xr = true;

@@ -97,9 +97,10 @@ struct LaunchPlan {
 // Pick threads, staging depth and CTAs per SM so that the staging rings of the
 // resident CTAs fill most of an SM's shared memory; the grid is that many CTAs
 // on every SM (or one CTA per row when there are fewer rows).
-inline int plan_launch(const LayoutReq& r, long long rows, LaunchPlan* out, int grid_cap = 0, int force_threads = 0) {
+inline int plan_launch(const LayoutReq& r, long long rows, LaunchPlan* out, int grid_cap = 0, int force_threads = 0,
+                       int default_stages = 3) {
   int threads = force_threads ? force_threads : g_tune_threads ? g_tune_threads : (r.D <= 1024 ? 64 : r.D <= 4096 ? 128 : 256);
-  int stages = g_tune_stages ? g_tune_stages : 3;
+  int stages = g_tune_stages ? g_tune_stages : default_stages;
   if (stages > kMaxStages) stages = kMaxStages;
   SmemLayout L = make_layout(r, stages);
   while (L.total > kSmemPerCtaMax && stages > 1) L = make_layout(r, --stages);

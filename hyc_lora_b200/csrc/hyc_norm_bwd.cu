@@ -1,5 +1,5 @@
 // Decompress + RMSNorm / LayerNorm backward, with the optional weight / bias gradient.
-#include "hyc_host.cuh"
+#include "hyc_bwd_fast.cuh"
 
 namespace hyc {
 
@@ -160,6 +160,45 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
     return HYC_OK;
   }
   const int D = saved->cols;
+  {
+    const BwdPlan bp = plan_bwd_fast(saved, nullptr, 4, true, g->dweight ? (g->dbias ? 2 : 1) : 0, 256, kPartialRowsMax,
+                                     align_up(static_cast<uint32_t>(D) * saved->bits / 8, 128) +
+                                         static_cast<uint32_t>(D) * (g->dy_dtype == HYC_BF16 ? 2 : 4));
+    if (bp.ok) {
+      NormBwdFastArgs fa;
+      memset(&fa, 0, sizeof(fa));
+      fa.p = to_dev(saved);
+      fa.kind = g->kind; fa.ref_compat_c2 = g->ref_compat_c2; fa.param_bf16 = g->param_dtype == HYC_BF16;
+      fa.weight = g->weight; fa.dy = static_cast<const unsigned char*>(g->dy);
+      fa.rstd = g->rstd; fa.mean = g->mean; fa.dx = static_cast<__nv_bfloat16*>(g->dx);
+      fa.partials = g->partials; fa.need_dw = g->dweight != nullptr; fa.need_db = g->dbias != nullptr;
+      fa.L = bp.L;
+#define HYC_NBF(B, UP, RT)                                                                      \
+  {                                                                                             \
+    if (g->dy_dtype == HYC_BF16) {                                                              \
+      auto kern = norm_bwd_n_fast_kernel<B, UP, RT, __nv_bfloat16>;                             \
+      rc = set_smem(kern, bp.L.total);                                                          \
+      if (rc) return rc;                                                                        \
+      kern<<<bp.grid, bp.threads, bp.L.total, stream>>>(fa);                                    \
+    } else {                                                                                    \
+      auto kern = norm_bwd_n_fast_kernel<B, UP, RT, float>;                                     \
+      rc = set_smem(kern, bp.L.total);                                                          \
+      if (rc) return rc;                                                                        \
+      kern<<<bp.grid, bp.threads, bp.L.total, stream>>>(fa);                                    \
+    }                                                                                           \
+  }
+      HYC_BWD_DISPATCH(bp, saved->bits, 4, HYC_NBF)
+#undef HYC_NBF
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return cuda_fail(e, "norm_bwd_n_fast_kernel launch");
+      if (g->dweight) {
+        reduce_partials_kernel<<<(D + 127) / 128, 128, 0, stream>>>(g->partials, bp.grid, D, g->dweight, g->dbias);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "reduce_partials_kernel launch");
+      }
+      return HYC_OK;
+    }
+  }
   const uint32_t cb = static_cast<uint32_t>(D) * saved->bits / 8;
   LayoutReq req;
   fill_req_packed(&req, saved, false);
