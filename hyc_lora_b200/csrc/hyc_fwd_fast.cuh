@@ -100,15 +100,8 @@ __device__ __forceinline__ void reduce_sum_max(float& s, float& m, float* buf) {
   const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   if ((threadIdx.x & 31) == 0) { buf[warp] = s; buf[32 + warp] = m; }
   __syncthreads();
-  // every warp folds the (at most 8) per-warp partials with three shuffle steps
-  const int l = threadIdx.x & 7;
-  s = l < nwarps ? buf[l] : 0.f;
-  m = l < nwarps ? buf[32 + l] : 0.f;
-#pragma unroll
-  for (int o = 4; o > 0; o >>= 1) {
-    s += __shfl_xor_sync(0xffffffffu, s, o);
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  }
+  s = buf[0]; m = buf[32];
+  for (int w = 1; w < nwarps; ++w) { s += buf[w]; m = fmaxf(m, buf[32 + w]); }
 }
 
 // Shared-memory helpers for the outlier channels of a staged row: save the original values
@@ -194,18 +187,6 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
   float rstd_prev = 0.f, mean_prev = 0.f;
   long long row_prev = -1;
   int i = 0;
-  // the columns of this thread's register groups never change; -1 marks an idle group
-  int colr[NR];
-#pragma unroll
-  for (int r = 0; r < NR; ++r) {
-    const int col = ROT ? (((warp + r * nwarps) << 8) + (lane << 3))
-                        : ((r % NSEG) * segw + ((threadIdx.x + (r / NSEG) * blockDim.x) << 3));
-    const bool ok = ROT ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
-    colr[r] = ok ? col : -1;
-  }
-  const long long y_stride = a.row_stride;
-  const int code_bytes = D * BITS / 8;
-  XT* const ybase = reinterpret_cast<XT*>(a.y);
   for (; row < rows; ++i, row += stride) {
     const int st = i % ring.stages;
     const int par = i & 1;
@@ -219,8 +200,9 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
       float s1 = 0.f, dummy = 0.f;
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
-        const int col = colr[r];
-        const bool ok = col >= 0;
+        const int col = ROT ? (((warp + r * nwarps) << 8) + (lane << 3))
+                            : ((r % NSEG) * segw + ((threadIdx.x + (r / NSEG) * blockDim.x) << 3));
+        const bool ok = ROT ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
         if (ok) {
           load8<XT>(xs, col, f[r]);
 #pragma unroll
@@ -234,8 +216,9 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     float ss = 0.f, amax = 0.f;
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
-      const int col = colr[r];
-      const bool ok = col >= 0;
+      const int col = ROT ? (((warp + r * nwarps) << 8) + (lane << 3))
+                          : ((r % NSEG) * segw + ((threadIdx.x + (r / NSEG) * blockDim.x) << 3));
+      const bool ok = ROT ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
       float a8 = 0.f;
       if (ok) {
         if (!ln) load8<XT>(xs, col, f[r]);
@@ -312,7 +295,7 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     // ---- norm output of the previous row at its outlier channels
     if (NORM && row_prev >= 0) {
       const float* o_prv = osm + ((i + 2) % 3) * k;
-      XT* yprev = ybase + row_prev * y_stride;
+      XT* yprev = reinterpret_cast<XT*>(a.y) + row_prev * a.row_stride;
       for (int j = threadIdx.x; j < k; j += blockDim.x) {
         const int c = w.chan[j];
         const float y = ln ? ((o_prv[j] - mean_prev) * rstd_prev * wsm[c] + bsm[c]) : (o_prv[j] * rstd_prev * wsm[c]);
@@ -334,13 +317,14 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
       if (threadIdx.x == 0) p.scales[row] = live ? __fdiv_rn(amax, qmax) : 1.f;
     }
     // ---- pass 2
-    unsigned char* codes_row = p.codes + row * code_bytes;
-    XT* yrow = NORM ? ybase + row * y_stride : nullptr;
+    unsigned char* codes_row = p.codes + row * (static_cast<long long>(D) * BITS / 8);
+    XT* yrow = NORM ? reinterpret_cast<XT*>(a.y) + row * a.row_stride : nullptr;
     if (NORM) {
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
-        const int col = colr[r];
-        const bool ok = col >= 0;
+        const int col = ROT ? (((warp + r * nwarps) << 8) + (lane << 3))
+                            : ((r % NSEG) * segw + ((threadIdx.x + (r / NSEG) * blockDim.x) << 3));
+        const bool ok = ROT ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
         if (ok) {
           float y[8], wv[8];
           load8<float>(wsm, col, wv);
@@ -360,12 +344,12 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     if (!ROT) {
 #pragma unroll
       for (int iu = 0; iu < UPT; ++iu) {
-        if (colr[iu * NSEG] >= 0) {
-          const int u = colr[iu * NSEG] >> 3;
+        const int u = threadIdx.x + iu * blockDim.x;
+        if (u < U) {
           PackAcc<BITS> acc;
 #pragma unroll
           for (int s = 0; s < NSEG; ++s) {
-            const int col = colr[iu * NSEG + s];
+            const int col = s * segw + (u << 3);
             float inv = inv_row;
             if (group) {
               const float ga = gamax[col >> 7];
@@ -406,7 +390,7 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
   if (NORM && row_prev >= 0) {
     __syncthreads();
     const float* o_prv = osm + ((i + 2) % 3) * k;
-    XT* yprev = ybase + row_prev * y_stride;
+    XT* yprev = reinterpret_cast<XT*>(a.y) + row_prev * a.row_stride;
     for (int j = threadIdx.x; j < k; j += blockDim.x) {
       const int c = w.chan[j];
       const float y = ln ? ((o_prv[j] - mean_prev) * rstd_prev * wsm[c] + bsm[c]) : (o_prv[j] * rstd_prev * wsm[c]);
