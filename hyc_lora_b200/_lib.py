@@ -85,6 +85,8 @@ SYMBOLS = {
                               C.c_void_p, C.c_void_p, C.c_void_p]),
     "hyc_channel_absmax": (C.c_int, [C.POINTER(HycDense), C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "hyc_select_channels": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "hyc_select_channels_static_max_cols": (C.c_int, []),
+    "hyc_select_channels_noalloc": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
 }
 
 

@@ -75,6 +75,11 @@ __global__ void __launch_bounds__(256) channel_gather_kernel(const int* rank, in
   channels[pos] = c;
 }
 
+// Scratch of the allocation-free selection entry point: one rank per channel.  The array
+// lives in every GPU context that loads this library, until the process exits.
+constexpr int kStaticSelectMaxCols = 16384;
+static __device__ __align__(256) int g_select_rank_scratch[kStaticSelectMaxCols];
+
 }  // namespace hyc
 
 using namespace hyc;
@@ -121,6 +126,33 @@ int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* ch
   const int blocks = (cols + 255) / 256;
   channel_rank_kernel<<<blocks, 256, 0, stream>>>(score, cols, rank_scratch);
   channel_gather_kernel<<<blocks, 256, 0, stream>>>(rank_scratch, cols, k, channels);
+  return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
+}
+
+int hyc_select_channels_static_max_cols(void) { return kStaticSelectMaxCols; }
+
+int hyc_select_channels_noalloc(const float* score, int32_t cols, int32_t k, int32_t* channels, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!score || (k > 0 && !channels)) return HYC_ERR_NULL;
+  if (cols <= 0 || k < 0 || k > cols) return HYC_ERR_SHAPE;
+  if (cols > kStaticSelectMaxCols) return HYC_ERR_CAPACITY;
+  if (k == 0) return HYC_OK;
+  // In host code the array's name is only a handle: the device address has to be asked for,
+  // once per device, with that device current.  The first call on a device does it.
+  static int* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HYC_ERR_CUDA;
+  if (!scratch_of_device[dev]) {
+    int* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_select_rank_scratch) != cudaSuccess || !ptr)
+      return HYC_ERR_CUDA;
+    scratch_of_device[dev] = ptr;
+  }
+  int* rank = scratch_of_device[dev];
+  const int blocks = (cols + 255) / 256;
+  // every rank in [0, cols) is rewritten by the first kernel, so nothing has to start at zero
+  channel_rank_kernel<<<blocks, 256, 0, stream>>>(score, cols, rank);
+  channel_gather_kernel<<<blocks, 256, 0, stream>>>(rank, cols, k, channels);
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
 

@@ -189,6 +189,24 @@ int hyc_channel_absmax(const hyc_dense* x, int64_t rows, int32_t cols, int32_t s
 int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* channels,
                         int32_t* rank_scratch, void* stream);
 
+/* Channel selection for callers that cannot allocate device memory.  (No counterpart in the
+ * reference; added for hosts that own no device allocator -- a foreign-language binding that
+ * only sees raw pointers handed to it, or a runtime whose memory plan is frozen once its
+ * buffers are reserved, so that asking for even a small rank buffer per call is not an
+ * option.)  Same result as hyc_select_channels, but the cols-sized rank scratch is a fixed
+ * array inside the library (hyc_select_channels_static_max_cols() entries of int32, 64 KiB,
+ * resident on every GPU that loads the library until the process exits).  The entry point
+ * calls no allocating routine.  Rules:
+ *   - cols above the maximum is refused with HYC_ERR_CAPACITY before anything is enqueued;
+ *   - the first call on a device looks the array's address up (one cudaGetSymbolAddress with
+ *     that device current); make that first call outside any stream capture;
+ *   - all calls on a device share the one array: two calls whose kernels can overlap on the
+ *     GPU (different streams) race; keep them on one stream or order them with events;
+ *   - the array keeps the previous call's ranks, which is harmless: every rank below cols is
+ *     rewritten before it is read. */
+int hyc_select_channels_static_max_cols(void);
+int hyc_select_channels_noalloc(const float* score, int32_t cols, int32_t k, int32_t* channels, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
