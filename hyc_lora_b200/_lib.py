@@ -70,6 +70,15 @@ class HycNormBwdArgs(C.Structure):
     ]
 
 
+class HycSparseRows(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int64), ("cols", C.c_int32), ("dtype", C.c_int32),
+        ("val", C.c_void_p), ("col", C.c_void_p),
+        ("cap", C.c_uint32), ("_pad", C.c_uint32),
+        ("used", C.c_void_p), ("row_meta", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
 # every symbol include/hyc_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "hyc_strerror": (C.c_char_p, [C.c_int]),
@@ -85,6 +94,9 @@ SYMBOLS = {
                               C.c_void_p, C.c_void_p, C.c_void_p]),
     "hyc_channel_absmax": (C.c_int, [C.POINTER(HycDense), C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "hyc_select_channels": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "hyc_softmax_compact": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(HycSparseRows), C.c_void_p]),
+    "hyc_softmax_expand": (C.c_int, [C.POINTER(HycSparseRows), C.c_void_p, C.c_void_p]),
+    "hyc_softmax_bwd": (C.c_int, [C.POINTER(HycSparseRows), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hyc_select_channels_static_max_cols": (C.c_int, []),
     "hyc_select_channels_noalloc": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
 }

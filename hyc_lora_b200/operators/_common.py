@@ -1,0 +1,87 @@
+"""Pieces shared by the ``EfficientMemory*`` modules: the calibration running
+mean of the reference, the options of the channel mode and the one helper that
+compresses an activation for backward in either mode."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import compress_function as cf
+from .compress_function import StaticList
+
+
+class SiteOptions:
+    """Options the reference does not have.  ``outlier_mode="element"`` (default)
+    is the reference's arithmetic; ``"channel"`` keeps the top ``outlier_ratio``
+    absmax channels in bf16, quantises the rest with a dynamic absmax scale per
+    token (``group_size=0``) or per 128 channels, optionally after a block
+    Walsh-Hadamard rotation (``rotate`` = block size)."""
+
+    def __init__(self, outlier_ratio: float, outlier_mode: str = "element", group_size: int = 0, rotate: int = 0):
+        if outlier_mode not in ("element", "channel"):
+            raise ValueError("outlier_mode must be 'element' or 'channel'")
+        if group_size not in (0, 128):
+            raise ValueError("group_size must be 0 (per token) or 128")
+        if rotate not in (0, 16, 64, 256, 1024, 4096):
+            raise ValueError("rotate must be 0 or a block size in {16, 64, 256, 1024, 4096}")
+        self.outlier_mode, self.group_size, self.rotate = outlier_mode, group_size, rotate
+        self.calib = cf.ChannelCalibration(outlier_ratio)
+        self._dummy = None
+
+    @property
+    def channel(self) -> bool:
+        return self.outlier_mode == "channel"
+
+    def dummy_stats(self, device):
+        """Placeholders for the four statistic outputs of a Function in channel mode."""
+        if self._dummy is None or self._dummy[0].device != device:
+            z = torch.zeros((), device=device)
+            self._dummy = (z, torch.zeros(1, 1, device=device, dtype=torch.bfloat16),
+                           torch.zeros(1, 1, device=device, dtype=torch.bfloat16),
+                           torch.ones((), device=device, dtype=torch.bfloat16))
+        return self._dummy
+
+
+def site_options(extra) -> Optional[SiteOptions]:
+    return extra[0] if extra else None
+
+
+@torch.no_grad()
+def compress_site(x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, method, rank, iteration, static_value,
+                  opts: Optional[SiteOptions], norm: Optional[dict] = None):
+    """Compress ``x`` for backward.  Returns ``(packed, (outlier, L, R, scale), norm_out)``
+    where ``norm_out`` is ``(y, rstd, mean)`` when ``norm`` is given."""
+    if not x.is_cuda:
+        raise RuntimeError("hyc_lora_b200 operators run on CUDA tensors only (there is no CPU path)")
+    if opts is not None and opts.channel:
+        channels = opts.calib.channels_for(x, iteration)
+        res = cf.channel_compress(x, channels, sub_outlier_bit, opts.group_size, opts.rotate, norm=norm)
+        stats = opts.dummy_stats(x.device)
+        if norm is None:
+            return res, stats, None
+        return res[0], stats, res[1:]
+    if iteration < 2:
+        outlier, L, R, scale = cf.get_statistics(x, iteration, outlier_ratio, sub_outlier_ratio, sub_outlier_bit,
+                                                 method, rank)
+        cache = None
+    else:
+        outlier, L, scale, R = static_value[0], static_value[1], static_value[2], static_value[3]
+        cache = static_value.cache if isinstance(static_value, StaticList) else None
+    res = cf.true_divide_outlier_suboutlier_svd_compress(x, outlier, scale, sub_outlier_bit, sub_outlier_ratio, L, R,
+                                                         rank=rank, cache=cache, outlier_ratio=outlier_ratio, norm=norm)
+    packed, _codes, scale_out = res[0], res[1], res[2]
+    return packed, (outlier, L, R, scale_out), (res[3:] if norm is not None else None)
+
+
+def update_static(static_value, iteration, outlier, L, scale, R):
+    """The reference's running mean over the first two calls (efficient_linear.py:122-146)."""
+    if iteration >= 2:
+        return
+    n = iteration
+    static_value[0] = outlier if static_value[0] is None else (n * static_value[0] + outlier) / (n + 1)
+    static_value[1] = L if static_value[1] is None else (n * static_value[1] + cf.pad_cut_L(L, static_value[1])) / (n + 1)
+    static_value[2] = scale if static_value[2] is None else (n * static_value[2] + scale) / (n + 1)
+    static_value[3] = R if static_value[3] is None else (n * static_value[3] + R) / (n + 1)
+    if isinstance(static_value, StaticList):
+        static_value.cache.clear()

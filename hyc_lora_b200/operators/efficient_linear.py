@@ -1,0 +1,68 @@
+"""LoRA-A linear with a compressed saved input (reference: operators/efficient_linear.py).
+
+Forward ``y = x W^T (+ b)`` and ``dX = dY W`` stay library GEMMs.  The weight
+gradient ``dW = sum_b dY_b^T X_b`` consumes the packed activation: through the
+dequant-fused tensor-core kernel when the library has it for the site's format,
+else through a bf16 reconstruction and a library GEMM, as the reference does
+(efficient_linear.py:61-67)."""
+import torch
+
+from .. import packed as _pk
+from ._common import SiteOptions, compress_site, site_options, update_static
+from .compress_function import StaticList
+
+
+class EfficientMemoryLinearFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, use_bias, outlier_ratio, sub_outlier_ratio, sub_outlier_bit,
+                sub_outlier_quantize_method, rank, iteration, static_value, *extra):
+        ctx.use_bias = use_bias
+        ctx.n_extra = len(extra)
+        output = x @ w.transpose(0, 1) + b[None, ...] if use_bias else x @ w.transpose(0, 1)
+        packed, (outlier, L, R, scale), _ = compress_site(
+            x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, sub_outlier_quantize_method, rank, iteration,
+            static_value, site_options(extra))
+        ctx.mark_non_differentiable(outlier, L, R, scale)
+        ctx.x_outlier_compressed = packed
+        ctx.save_for_backward(w)
+        return output, outlier, L, R, scale
+
+    @staticmethod
+    def backward(ctx, grad_output, grad_outlier, grad_L, grad_R, grad_scale):
+        (w,) = ctx.saved_tensors
+        packed = ctx.x_outlier_compressed
+        grad_input = grad_weight = grad_bias = None
+        if ctx.needs_input_grad[0]:
+            grad_input = grad_output.to(w.dtype) @ w
+        if ctx.needs_input_grad[1]:
+            grad_weight = _pk.lora_wgrad(packed, grad_output).to(w.dtype)
+        if ctx.use_bias and ctx.needs_input_grad[2]:
+            grad_bias = grad_output.to(torch.bfloat16).sum(0)
+        ctx.x_outlier_compressed = None
+        return (grad_input, grad_weight, grad_bias) + (None,) * (8 + ctx.n_extra)
+
+
+class EfficientMemoryLinear(torch.nn.Linear):
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, outlier_ratio: float = 0.01,
+                 sub_outlier_ratio: float = 0.2, sub_outlier_bit: int = 8,
+                 sub_outlier_quantize_method: str = "per-tensor", rank: int = 16, *,
+                 outlier_mode: str = "element", group_size: int = 0, rotate: int = 0):
+        super().__init__(in_features, out_features, bias)
+        self.outlier_ratio = outlier_ratio
+        self.sub_outlier_ratio = sub_outlier_ratio
+        self.sub_outlier_bit = sub_outlier_bit
+        self.sub_outlier_quantize_method = sub_outlier_quantize_method
+        self.rank = rank
+        self.iteration = 0
+        self.static_value = StaticList()
+        self.site = SiteOptions(outlier_ratio, outlier_mode, group_size, rotate)
+
+    def forward(self, input: torch.Tensor):
+        result, outlier, L, R, scale = EfficientMemoryLinearFunc.apply(
+            input, self.weight, self.bias, self.bias is not None, self.outlier_ratio, self.sub_outlier_ratio,
+            self.sub_outlier_bit, self.sub_outlier_quantize_method, self.rank, self.iteration, self.static_value,
+            self.site)
+        if not self.site.channel:
+            update_static(self.static_value, self.iteration, outlier, L, scale, R)
+        self.iteration += 1
+        return result

@@ -16,7 +16,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import HycDense, HycNormBwdArgs, HycNormFwd, HycPacked, check, lib
+from ._lib import HycDense, HycNormBwdArgs, HycNormFwd, HycPacked, HycSparseRows, check, lib
 
 _SCALE_KIND = {"per-tensor": _lib.HYC_SCALE_TENSOR, "per-channel": _lib.HYC_SCALE_CHANNEL,
                "per-token": _lib.HYC_SCALE_TOKEN}
@@ -332,3 +332,84 @@ def select_channels(score: torch.Tensor, k: int) -> torch.Tensor:
     check(lib.hyc_select_channels(_ptr(score), cols, k, _ptr(channels), _ptr(scratch), _stream()),
           "hyc_select_channels")
     return channels
+
+
+# ---------------------------------------------------------------------------
+# LoRA-A weight gradient from a packed activation
+# ---------------------------------------------------------------------------
+
+
+def lora_wgrad(p: Packed, grad_output: torch.Tensor) -> torch.Tensor:
+    """``dW[r, D] = sum_t G[t, r] * X_hat[t, d]`` in fp32.  The saved input is
+    rebuilt by the decompress kernel and contracted by a library GEMM in bf16
+    with fp32 accumulation, which is the arithmetic of the reference
+    (efficient_linear.py:61-67) followed by the autograd engine's sum over the batch."""
+    _require_cuda(grad_output)
+    xh = decompress(p).reshape(p.rows, p.cols)
+    g = grad_output.reshape(p.rows, -1).to(torch.bfloat16)
+    return (g.t() @ xh).float()
+
+
+# ---------------------------------------------------------------------------
+# thresholded copy of attention probabilities
+# ---------------------------------------------------------------------------
+
+
+@dataclass
+class SparseRows:
+    rows: int
+    cols: int
+    shape: tuple
+    val: torch.Tensor        # [cap], dtype of the probabilities
+    col: torch.Tensor        # int16 storage of uint16 columns [cap]
+    used: torch.Tensor       # int32 [1]
+    row_meta: torch.Tensor   # int32 [rows, 2]
+    status: torch.Tensor     # int32 [1]
+
+    def record(self) -> HycSparseRows:
+        r = HycSparseRows()
+        r.rows, r.cols, r.dtype = self.rows, self.cols, _dtype_code(self.val)
+        r.val, r.col, r.cap = self.val.data_ptr(), self.col.data_ptr(), self.val.numel()
+        r.used, r.row_meta, r.status = self.used.data_ptr(), self.row_meta.data_ptr(), self.status.data_ptr()
+        return r
+
+    def overflowed(self) -> bool:
+        return bool(int(self.status.item()) & _lib.HYC_STATUS_POOL_OVERFLOW)
+
+
+def softmax_compact(y: torch.Tensor, thr: torch.Tensor, capacity_ratio: float = 0.125) -> SparseRows:
+    """Keep ``y > thr`` of a [..., C] probability tensor as per-row lists."""
+    _require_cuda(y, thr)
+    if not y.is_contiguous():
+        y = y.contiguous()
+    cols = y.shape[-1]
+    rows = y.numel() // cols
+    cap = min(int(math.ceil(rows * cols * min(max(capacity_ratio, 1.0 / 64.0), 1.0))) + 1024, 2 ** 32 - 2)
+    dev = y.device
+    s = SparseRows(rows=rows, cols=cols, shape=tuple(y.shape),
+                   val=torch.empty(cap, dtype=y.dtype, device=dev), col=torch.empty(cap, dtype=torch.int16, device=dev),
+                   used=torch.empty(1, dtype=torch.int32, device=dev),
+                   row_meta=torch.empty((rows, 2), dtype=torch.int32, device=dev),
+                   status=torch.zeros(1, dtype=torch.int32, device=dev))
+    thr32 = thr.reshape(1).to(device=dev, dtype=torch.float32)
+    rec = s.record()
+    check(lib.hyc_softmax_compact(_ptr(y), _ptr(thr32), C.byref(rec), _stream()), "hyc_softmax_compact")
+    return s
+
+
+def softmax_expand(s: SparseRows) -> torch.Tensor:
+    out = torch.empty(s.shape, dtype=s.val.dtype, device=s.val.device)
+    rec = s.record()
+    check(lib.hyc_softmax_expand(C.byref(rec), _ptr(out), _stream()), "hyc_softmax_expand")
+    return out
+
+
+def softmax_bwd(s: SparseRows, g: torch.Tensor) -> torch.Tensor:
+    _require_cuda(g)
+    if not g.is_contiguous():
+        g = g.contiguous()
+    out_dtype = torch.bfloat16 if (g.dtype == torch.bfloat16 and s.val.dtype == torch.bfloat16) else torch.float32
+    dx = torch.empty(s.shape, dtype=out_dtype, device=g.device)
+    rec = s.record()
+    check(lib.hyc_softmax_bwd(C.byref(rec), _ptr(g), _dtype_code(g), _ptr(dx), _stream()), "hyc_softmax_bwd")
+    return dx

@@ -189,6 +189,31 @@ int hyc_channel_absmax(const hyc_dense* x, int64_t rows, int32_t cols, int32_t s
 int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* channels,
                         int32_t* rank_scratch, void* stream);
 
+/* Thresholded ("sparse") copy of attention probabilities, rows x cols with cols <= 65535.
+ * Replaces true_compress_softmax / true_decompress_softmax (compress_function.py:264-275: a
+ * torch sparse COO tensor built with a host sync) and the backward of
+ * EfficientMemorySoftmaxFunc (efficient_softmax.py:35-45).  Entries of a row sit contiguously in
+ * `val`/`col` in ascending column order; row_meta[row] = (first entry, count).  A row that does
+ * not fit the pool keeps nothing and raises HYC_STATUS_POOL_OVERFLOW. */
+typedef struct {
+  int64_t rows;
+  int32_t cols;
+  int32_t dtype;         /* hyc_dtype of the probabilities / of `val` */
+  void* val;             /* [cap] */
+  uint16_t* col;         /* [cap] */
+  uint32_t cap;
+  uint32_t _pad;
+  uint32_t* used;        /* one word (compact zeroes it) */
+  uint32_t* row_meta;    /* [rows, 2] */
+  uint32_t* status;      /* may be NULL */
+} hyc_sparse_rows;
+/* keep p > *thr (compared in p's dtype) */
+int hyc_softmax_compact(const void* p, const float* thr, const hyc_sparse_rows* out, void* stream);
+/* dense [rows, cols] of the list's dtype, zeros where nothing was kept */
+int hyc_softmax_expand(const hyc_sparse_rows* in, void* dense, void* stream);
+/* dx = (g - sum(g * y_kept)) * y_kept; dx is fp32 unless both the list and g are bf16 */
+int hyc_softmax_bwd(const hyc_sparse_rows* in, const void* g, int g_dtype, void* dx, void* stream);
+
 /* Channel selection for callers that cannot allocate device memory.  (No counterpart in the
  * reference; added for hosts that own no device allocator -- a foreign-language binding that
  * only sees raw pointers handed to it, or a runtime whose memory plan is frozen once its

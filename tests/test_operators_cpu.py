@@ -1,0 +1,83 @@
+"""No-GPU checks of the operator layer: the drop-in names exist, and constructor and
+Function signatures match the reference's (when its tree is present)."""
+import inspect
+
+import pytest
+
+import hyc_lora_b200
+from oracle import ref_loader
+
+PAIRS = [
+    ("efficient_linear", "EfficientMemoryLinear", "EfficientMemoryLinearFunc"),
+    ("efficient_silu", "EfficientMemorySiLU", "EfficientMemorySiLUFunc"),
+    ("efficient_gelu", "EfficientMemoryGELU", "EfficientMemoryGELUFunc"),
+    ("efficient_hadamard", "EfficientMemoryHadamard", "EfficientMemoryHadamardFunc"),
+    ("efficient_softmax", "EfficientMemorySoftmax", "EfficientMemorySoftmaxFunc"),
+    ("efficient_gemm", "EfficientMemoryGEMM", "EfficientMemoryGEMMFunc"),
+    ("efficient_gemm", "EfficientMemoryGEMMWithSoftmax", "EfficientMemoryGEMMWithSoftmaxFunc"),
+]
+EXTRA_KW = {"outlier_mode", "group_size", "rotate", "ref_compat_c2"}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from hyc_lora_b200 import build
+    build.build()
+    return hyc_lora_b200.install_as_operators()
+
+
+def test_reference_import_lines_resolve(ops):
+    from operators.efficient_linear import EfficientMemoryLinear          # noqa: F401
+    from operators.efficient_gelu import EfficientMemoryGELU              # noqa: F401
+    from operators.efficient_silu import EfficientMemorySiLU              # noqa: F401
+    from operators.efficient_layernorm import EfficientMemoryLayerNorm    # noqa: F401
+    from operators.efficient_rmsnorm import EfficientMemoryRMSNorm        # noqa: F401
+    from operators.efficient_rmsnorm_gemma import EfficientMemoryRMSNormGemma  # noqa: F401
+    from operators.efficient_dropout import EfficientMemoryDropout        # noqa: F401
+    from operators.efficient_hadamard import EfficientMemoryHadamard      # noqa: F401
+    from operators.efficient_gemm import EfficientMemoryGEMM, EfficientMemoryGEMMWithSoftmax  # noqa: F401
+    from operators.efficient_softmax import EfficientMemorySoftmax        # noqa: F401
+    from operators.compress_function import (get_statistics, pad_cut_L,   # noqa: F401
+                                             true_divide_outlier_suboutlier_svd_compress,
+                                             true_divide_outlier_suboutlier_svd_decompress)
+
+
+def test_modules_keep_reference_state_attributes(ops):
+    from operators.efficient_linear import EfficientMemoryLinear
+    from operators.efficient_rmsnorm import EfficientMemoryRMSNorm
+    import torch
+    m = EfficientMemoryLinear(768, 16, bias=False, outlier_ratio=0.01, sub_outlier_ratio=1.0, sub_outlier_bit=4,
+                              sub_outlier_quantize_method="per-token", rank=0)
+    assert isinstance(m, torch.nn.Linear) and m.iteration == 0 and list(m.static_value) == [None] * 4
+    n = EfficientMemoryRMSNorm(4096, eps=1e-6)
+    assert isinstance(n, torch.nn.LayerNorm) and n.weight.shape == (4096,) and n.eps == 1e-6
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        m(torch.zeros(1, 4, 768))
+
+
+@pytest.mark.skipif(ref_loader.load() is None, reason="reference tree not present")
+@pytest.mark.parametrize("mod,cls,fn", PAIRS)
+def test_signatures_match_reference(ops, mod, cls, fn):
+    ref = ref_loader.load()
+    ours = getattr(__import__(f"operators.{mod}", fromlist=[cls]), cls)
+    theirs = getattr(getattr(ref, mod), cls)
+    po = [p for p in inspect.signature(ours.__init__).parameters.values() if p.name not in EXTRA_KW]
+    pt = list(inspect.signature(theirs.__init__).parameters.values())
+    assert [(p.name, p.default) for p in po] == [(p.name, p.default) for p in pt]
+    fo = getattr(__import__(f"operators.{mod}", fromlist=[fn]), fn)
+    ft = getattr(getattr(ref, mod), fn)
+    names_o = [n for n in inspect.signature(fo.forward).parameters if n != "extra"]
+    assert names_o == list(inspect.signature(ft.forward).parameters)
+
+
+def test_norm_signatures_match_reference_text():
+    # the reference's norm modules import Triton kernels that need a GPU to build, so their
+    # signatures are compared by name against the documented list instead of by import
+    from hyc_lora_b200.operators.efficient_rmsnorm import EfficientMemoryRMSNorm, EfficientMemoryRMSNormFunc
+    want = ["self", "normalized_shape", "eps", "elementwise_affine", "bias", "outlier_ratio", "sub_outlier_ratio",
+            "sub_outlier_bit", "sub_outlier_quantize_method", "rank"]
+    got = [n for n in inspect.signature(EfficientMemoryRMSNorm.__init__).parameters if n not in EXTRA_KW]
+    assert got == want
+    fwd = [n for n in inspect.signature(EfficientMemoryRMSNormFunc.forward).parameters if n != "extra"]
+    assert fwd == ["ctx", "x", "normalized_shape", "outlier_ratio", "sub_outlier_ratio", "sub_outlier_bit",
+                   "sub_outlier_quantize_method", "rank", "weight", "bias", "eps", "iteration", "static_value"]
