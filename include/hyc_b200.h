@@ -189,6 +189,18 @@ int hyc_channel_absmax(const hyc_dense* x, int64_t rows, int32_t cols, int32_t s
 int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* channels,
                         int32_t* rank_scratch, void* stream);
 
+/* LoRA-A weight gradient from a packed activation (channel mode), on the tcgen05 tensor cores:
+ *     out[n, d] = sum_t grad[t, n] * X_hat[t, d],   fp32 [rank, cols].
+ * Replaces the decompress + batched GEMM + batch sum of efficient_linear.py:61,66-67 without
+ * writing X_hat to memory.  grad is bf16 [rows, rank] (contiguous, 16-byte aligned), rank a
+ * multiple of 8 in [8, 64]; cols*bits/8 must be a multiple of 128.  `partials` is scratch of
+ * hyc_lora_wgrad_splits(rows, cols, bits) * rank * cols floats.  The columns of the outlier
+ * channels are NOT filled in by this call (their codes are the zero code): the caller sets
+ * out[:, channels] = grad^T * out_value (a [rank, k] product).  With rotation the result
+ * already includes the inverse rotation. */
+int hyc_lora_wgrad_splits(int64_t rows, int32_t cols, int32_t bits);
+int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, float* out, float* partials, void* stream);
+
 /* Thresholded ("sparse") copy of attention probabilities, rows x cols with cols <= 65535.
  * Replaces true_compress_softmax / true_decompress_softmax (compress_function.py:264-275: a
  * torch sparse COO tensor built with a host sync) and the backward of

@@ -296,6 +296,27 @@ def test_activation_backward_matches_oracle(pk, op, mode, bits, gdtype, d, rotat
         assert ((dx.float().cpu() - o.float()).abs() <= 1e-2 * o.float().abs() + 1e-4).all()
 
 
+# ------------------------------------------------------------------ tensor-core weight gradient
+
+@pytest.mark.parametrize("rows,d,bits,group,rotate,rank", [
+    (512, 4096, 4, 0, 0, 64), (2048, 4096, 4, 0, 256, 64), (300, 768, 4, 0, 0, 16), (1000, 4096, 2, 128, 0, 64),
+    (777, 4096, 8, 0, 256, 16), (64, 11008, 4, 0, 0, 64), (4096, 1024, 4, 128, 64, 32), (70, 4096, 4, 0, 0, 8)])
+def test_lora_weight_gradient_from_codes(pk, rows, d, bits, group, rotate, rank):
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, salt=rank + bits)
+    g = torch.randn(rows, rank, generator=torch.Generator().manual_seed(rank)).to(torch.bfloat16)
+    ch = oc.n_select_channels(oc.n_channel_scores(x), oc.n_outlier_count(d, 0.01))
+    p = pk.compress_n(x.to(DEV), ch.to(DEV), bits, group, rotate)
+    assert pk.lora_wgrad_supported(p, rank)
+    dw = pk.lora_wgrad(p, g.to(DEV))
+    xh = oc.n_decompress(oc.n_compress(x, ch, bits, group, rotate))
+    want = g.float().T @ xh.float()
+    assert dw.shape == (rank, d) and dw.dtype == torch.float32
+    assert _cos(dw, want) > 0.9999 and _rel_err(dw, want) < 1e-2
+    lib_path = pk.lora_wgrad(p, g.to(DEV), force_library=True)
+    assert _cos(dw, lib_path) > 0.9999
+    assert not p.wait_expired()
+
+
 # ------------------------------------------------------------------ full-size properties (configuration 5 shapes)
 
 @pytest.mark.parametrize("bits,group,rotate", [(4, 0, 0), (2, 128, 256), (8, 0, 256)])
