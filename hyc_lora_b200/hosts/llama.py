@@ -1,0 +1,145 @@
+"""LLaMA / Mistral-shaped decoder host (RMSNorm, RoPE, SiLU-gated MLP, optional GQA).
+
+Swap points carry the names the reference's model file gives them
+(models/modeling_llama.py:103-125, 293, 817, 833, 1109): ``input_layernorm``,
+``post_attention_layernorm``, ``norm`` (class name contains "RMSNorm"), ``act_fn`` (class name
+contains "SiLU"), ``hadamard`` (class ``LlamaHadamard``).  Attention runs on the library's fused
+causal attention (``F.scaled_dot_product_attention``), which stands in for the flash-attn call of
+the reference and is not part of the compression path."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .lora import FrozenLinear, LoRALinear
+
+
+@dataclass
+class DecoderConfig:
+    hidden: int = 4096
+    layers: int = 32
+    heads: int = 32
+    kv_heads: int = 32
+    ffn: int = 11008
+    vocab: int = 32000
+    eps: float = 1e-5
+    rope_theta: float = 10000.0
+    lora_r: int = 64
+    lora_alpha: float = 16.0
+    base_quant: str = "nf4"
+
+    @staticmethod
+    def llama2_7b(**kw):
+        return DecoderConfig(**kw)
+
+    @staticmethod
+    def mistral_7b(**kw):
+        return DecoderConfig(kv_heads=8, ffn=14336, **kw)
+
+
+class LlamaRMSNorm(nn.Module):
+    def __init__(self, hidden, eps, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden, device=device), requires_grad=False)
+        self.variance_epsilon = eps
+
+    def forward(self, x):
+        v = x.float().pow(2).mean(-1, keepdim=True)
+        return (self.weight * (x.float() * torch.rsqrt(v + self.variance_epsilon))).to(x.dtype)
+
+
+class LlamaSiLU(nn.Module):
+    def forward(self, x):
+        return F.silu(x)
+
+
+class LlamaHadamard(nn.Module):
+    def forward(self, x1, x2):
+        return x1 * x2
+
+
+def _rope(q, k, theta):
+    b, h, s, d = q.shape
+    pos = torch.arange(s, device=q.device, dtype=torch.float32)
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=q.device, dtype=torch.float32) / d))
+    ang = torch.outer(pos, inv)
+    cos, sin = torch.cat((ang.cos(), ang.cos()), -1).to(q.dtype), torch.cat((ang.sin(), ang.sin()), -1).to(q.dtype)
+
+    def rot(x):
+        x1, x2 = x[..., : d // 2], x[..., d // 2:]
+        return torch.cat((-x2, x1), dim=-1)
+
+    return q * cos + rot(q) * sin, k * cos + rot(k) * sin
+
+
+class Attention(nn.Module):
+    def __init__(self, c: DecoderConfig, device, gen):
+        super().__init__()
+        self.c = c
+        hd = c.hidden // c.heads
+        mk = lambda i, o: LoRALinear(i, o, c.lora_r, c.lora_alpha, c.base_quant, device=device, generator=gen)
+        self.q_proj, self.k_proj = mk(c.hidden, c.heads * hd), mk(c.hidden, c.kv_heads * hd)
+        self.v_proj, self.o_proj = mk(c.hidden, c.kv_heads * hd), mk(c.heads * hd, c.hidden)
+
+    def forward(self, x):
+        b, s, _ = x.shape
+        c = self.c
+        hd = c.hidden // c.heads
+        q = self.q_proj(x).view(b, s, c.heads, hd).transpose(1, 2)
+        k = self.k_proj(x).view(b, s, c.kv_heads, hd).transpose(1, 2)
+        v = self.v_proj(x).view(b, s, c.kv_heads, hd).transpose(1, 2)
+        q, k = _rope(q, k, c.rope_theta)
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=c.kv_heads != c.heads)
+        return self.o_proj(o.transpose(1, 2).reshape(b, s, c.heads * hd))
+
+
+class MLP(nn.Module):
+    def __init__(self, c: DecoderConfig, device, gen):
+        super().__init__()
+        mk = lambda i, o: LoRALinear(i, o, c.lora_r, c.lora_alpha, c.base_quant, device=device, generator=gen)
+        self.gate_proj, self.up_proj, self.down_proj = mk(c.hidden, c.ffn), mk(c.hidden, c.ffn), mk(c.ffn, c.hidden)
+        self.act_fn = LlamaSiLU()
+        self.hadamard = LlamaHadamard()
+
+    def forward(self, x):
+        return self.down_proj(self.hadamard(self.act_fn(self.gate_proj(x)), self.up_proj(x)))
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, c, device, gen):
+        super().__init__()
+        self.input_layernorm = LlamaRMSNorm(c.hidden, c.eps, device)
+        self.self_attn = Attention(c, device, gen)
+        self.post_attention_layernorm = LlamaRMSNorm(c.hidden, c.eps, device)
+        self.mlp = MLP(c, device, gen)
+
+    def forward(self, x):
+        x = x + self.self_attn(self.input_layernorm(x))
+        return x + self.mlp(self.post_attention_layernorm(x))
+
+
+class DecoderLM(nn.Module):
+    """Causal LM host; ``forward(ids)`` returns the mean next-token cross-entropy with labels = ids."""
+
+    def __init__(self, c: DecoderConfig, device="cuda", seed: int = 0):
+        super().__init__()
+        gen = torch.Generator(device=device)
+        gen.manual_seed(seed)
+        self.config = c
+        self.embed_tokens = nn.Embedding(c.vocab, c.hidden, device=device, dtype=torch.bfloat16)
+        self.embed_tokens.weight.requires_grad_(False)
+        self.layers = nn.ModuleList(DecoderLayer(c, device, gen) for _ in range(c.layers))
+        self.norm = LlamaRMSNorm(c.hidden, c.eps, device)
+        self.lm_head = FrozenLinear(c.hidden, c.vocab, "bf16", device=device, generator=gen)
+
+    def forward(self, ids):
+        x = self.embed_tokens(ids)
+        # the first activation has no trainable producer; it must require grad for the LoRA chain rule
+        x = x.requires_grad_(True) if not x.requires_grad else x
+        for layer in self.layers:
+            x = layer(x)
+        logits = self.lm_head(self.norm(x))
+        return F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), ids[:, 1:].reshape(-1))

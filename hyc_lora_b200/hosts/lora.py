@@ -1,0 +1,123 @@
+"""LoRA adapter around a frozen base linear.
+
+The arithmetic is the published LoRA forward ``base(x) + B(A(x)) * (alpha / r)`` (what the
+peft wrapper used by the reference computes, train_gsm8k.py:698-722).  ``lora_A`` is a
+trainable ``nn.Linear`` with ``in_features > 100`` and is therefore the module the
+replacement rules turn into ``EfficientMemoryLinear``; ``lora_B`` (``in_features = r``)
+is left alone, as in the reference (train_gsm8k.py:428-451).
+
+The base weight is frozen and either bf16 or held as blockwise 4-bit codebook weights.
+Either way the base layer keeps NO activation for backward -- the behaviour the
+reference's bitsandbytes patch exists for (bitsandbytes_fix/_function.py:515-518).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+import torch.nn as nn
+
+_CODEBOOK = None
+
+
+def nf4_codebook() -> torch.Tensor:
+    """The 16 levels of the 4-bit NormalFloat codebook, built from its published
+    construction: 8 positive and 7 negative quantiles of N(0,1) taken at evenly spaced
+    probabilities between 0.5 and an offset close to 1, plus an exact zero, normalised
+    to [-1, 1]."""
+    global _CODEBOOK
+    if _CODEBOOK is None:
+        from scipy.stats import norm
+        offset = 0.5 * (1 - 1 / 32 + 1 - 1 / 30)          # midway between the two tail conventions
+        pos = norm.ppf(torch.linspace(offset, 0.5, 9)[:-1].double().numpy())
+        neg = -norm.ppf(torch.linspace(offset, 0.5, 8)[:-1].double().numpy())
+        vals = torch.tensor(sorted(list(pos) + [0.0] + list(neg)), dtype=torch.float64)
+        _CODEBOOK = (vals / vals.abs().max()).float()
+    return _CODEBOOK
+
+
+@torch.no_grad()
+def nf4_quantize(w: torch.Tensor, block: int = 64):
+    """Blockwise absmax quantisation to the codebook.  Returns (codes uint8 [n/2], absmax fp32 [n/block])."""
+    flat = w.reshape(-1, block).float()
+    absmax = flat.abs().amax(dim=1).clamp_min(1e-12)
+    book = nf4_codebook().to(w.device)
+    idx = torch.empty(flat.shape, dtype=torch.uint8, device=w.device)
+    step = max(1, (1 << 24) // block)
+    for i in range(0, flat.shape[0], step):                    # chunked: the distance tensor is 16x the weight
+        norm = flat[i:i + step] / absmax[i:i + step, None]
+        idx[i:i + step] = (norm.unsqueeze(-1) - book).abs().argmin(dim=-1).to(torch.uint8)
+    idx = idx.reshape(-1, 2)
+    return ((idx[:, 0] << 4) | idx[:, 1]).contiguous(), absmax.contiguous()
+
+
+def nf4_dequantize(codes: torch.Tensor, absmax: torch.Tensor, shape) -> torch.Tensor:
+    from .. import _lib
+    n = codes.numel() * 2
+    out = torch.empty(n, dtype=torch.bfloat16, device=codes.device)
+    book = nf4_codebook().to(codes.device)
+    _lib.check(_lib.lib.hyc_nf4_dequant(C.c_void_p(codes.data_ptr()), C.c_void_p(absmax.data_ptr()),
+                                        C.c_void_p(book.data_ptr()), n, C.c_void_p(out.data_ptr()),
+                                        C.c_void_p(torch.cuda.current_stream().cuda_stream)), "hyc_nf4_dequant")
+    return out.view(shape)
+
+
+class _FrozenNF4LinearFunc(torch.autograd.Function):
+    """y = x W^T with W rebuilt from 4-bit storage; backward rebuilds W again and returns dX only."""
+
+    @staticmethod
+    def forward(ctx, x, layer):
+        ctx.layer = layer
+        return x @ layer.dequantized().t()
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        return grad_out @ ctx.layer.dequantized(), None
+
+
+class FrozenLinear(nn.Module):
+    """Frozen base projection (no bias).  ``quant="nf4"`` stores 4-bit codes; ``"bf16"`` a frozen
+    bf16 parameter (autograd keeps no input for a weight that does not train)."""
+
+    def __init__(self, in_features: int, out_features: int, quant: str = "bf16", device=None, std: float = 0.02,
+                 generator=None):
+        super().__init__()
+        self.in_features, self.out_features, self.quant = in_features, out_features, quant
+        w = torch.empty(out_features, in_features, device=device, dtype=torch.bfloat16)
+        w.normal_(0.0, std, generator=generator)
+        if quant == "nf4":
+            codes, absmax = nf4_quantize(w)
+            self.register_buffer("codes", codes)
+            self.register_buffer("absmax", absmax)
+        else:
+            self.weight = nn.Parameter(w, requires_grad=False)
+
+    def dequantized(self) -> torch.Tensor:
+        return nf4_dequantize(self.codes, self.absmax, (self.out_features, self.in_features))
+
+    def forward(self, x):
+        if self.quant == "nf4":
+            return _FrozenNF4LinearFunc.apply(x, self)
+        return nn.functional.linear(x, self.weight)
+
+
+class LoRALinear(nn.Module):
+    """``base(x) + lora_B(lora_A(x)) * scaling`` with B initialised to zero."""
+
+    def __init__(self, in_features: int, out_features: int, r: int = 64, alpha: float = 16.0, quant: str = "bf16",
+                 device=None, dtype=torch.bfloat16, generator=None):
+        super().__init__()
+        self.base_layer = FrozenLinear(in_features, out_features, quant, device=device, generator=generator)
+        self.lora_A = nn.Linear(in_features, r, bias=False, device=device, dtype=dtype)
+        self.lora_B = nn.Linear(r, out_features, bias=False, device=device, dtype=dtype)
+        nn.init.kaiming_uniform_(self.lora_A.weight, a=math.sqrt(5))
+        nn.init.zeros_(self.lora_B.weight)
+        self.scaling = alpha / r
+
+    def forward(self, x):
+        return self.base_layer(x) + self.lora_B(self.lora_A(x)) * self.scaling
+
+
+def lora_parameters(model: nn.Module):
+    return [p for n, p in model.named_parameters() if p.requires_grad]

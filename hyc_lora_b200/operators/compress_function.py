@@ -169,9 +169,12 @@ def get_statistics_softmax(x: torch.Tensor, iteration: int, outlier_ratio: float
 
 
 @torch.no_grad()
-def true_compress_softmax(x: torch.Tensor, outlier):
-    """Keep the probabilities above the threshold as a compact per-row list."""
-    return _pk.softmax_compact(x, outlier)
+def true_compress_softmax(x: torch.Tensor, outlier, outlier_ratio: Optional[float] = None):
+    """Keep the probabilities above the threshold as a compact per-row list.  The list's
+    capacity is twice the calibrated fraction (plus slack); rows that do not fit keep
+    nothing and raise the overflow flag of the record."""
+    cap = 0.125 if outlier_ratio is None else min(1.0, 2.0 * outlier_ratio + 0.02)
+    return _pk.softmax_compact(x, outlier, capacity_ratio=cap)
 
 
 @torch.no_grad()

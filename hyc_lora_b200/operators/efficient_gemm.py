@@ -81,7 +81,7 @@ class EfficientMemoryGEMMWithSoftmaxFunc(torch.autograd.Function):
         result = x1 @ x2
         ctx.num_heads = x1.shape[1]
         outlier_1 = get_statistics_softmax(x1, iteration, outlier_ratio_1) if iteration < 2 else static_value_1
-        ctx.x_sparse = true_compress_softmax(x1, outlier_1)
+        ctx.x_sparse = true_compress_softmax(x1, outlier_1, outlier_ratio_1)
         p2, (outlier_2, L_2, R_2, scale_2), _ = compress_site(
             x2, outlier_ratio_2, sub_outlier_ratio_2, sub_outlier_bit_2, sub_outlier_quantize_method_2, rank,
             iteration, static_value_2, extra[0] if extra else None)

@@ -14,7 +14,7 @@ class EfficientMemorySoftmaxFunc(torch.autograd.Function):
     def forward(ctx, x, outlier_ratio, iteration, static_value):
         y_return = F.softmax(x, dim=-1)
         outlier = get_statistics_softmax(y_return, iteration, outlier_ratio) if iteration < 2 else static_value
-        ctx.y_sparse = true_compress_softmax(y_return, outlier)
+        ctx.y_sparse = true_compress_softmax(y_return, outlier, outlier_ratio)
         ctx.mark_non_differentiable(outlier)
         return y_return, outlier
 

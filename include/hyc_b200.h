@@ -226,6 +226,13 @@ int hyc_softmax_expand(const hyc_sparse_rows* in, void* dense, void* stream);
 /* dx = (g - sum(g * y_kept)) * y_kept; dx is fp32 unless both the list and g are bf16 */
 int hyc_softmax_bwd(const hyc_sparse_rows* in, const void* g, int g_dtype, void* dx, void* stream);
 
+/* Frozen base weights of the host models: blockwise 4-bit codebook storage (64 values per fp32
+ * absmax, two 4-bit indices per byte, high nibble first) -> bf16.  `n` values, n % 64 == 0;
+ * `codebook` is 16 floats on the device.  The reference relies on bitsandbytes for this
+ * (bitsandbytes_fix/_function.py:509,540); it is not part of the compression path. */
+int hyc_nf4_dequant(const void* codes, const float* absmax, const float* codebook, int64_t n, void* out_bf16,
+                    void* stream);
+
 /* Channel selection for callers that cannot allocate device memory.  (No counterpart in the
  * reference; added for hosts that own no device allocator -- a foreign-language binding that
  * only sees raw pointers handed to it, or a runtime whose memory plan is frozen once its

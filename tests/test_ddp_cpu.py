@@ -1,0 +1,72 @@
+"""world_size-2 gloo test (CPU) of the LoRA-gradient exchange: the batch is sharded across
+ranks, each rank back-propagates its shard, one flat all-reduce averages the trainable
+gradients, and the result equals the single-process gradient of the whole batch."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class _Tiny(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        g = torch.Generator().manual_seed(5)
+        self.base = torch.nn.Parameter(torch.randn(24, 24, generator=g), requires_grad=False)
+        self.lora_A = torch.nn.Parameter(0.1 * torch.randn(4, 24, generator=g))
+        self.lora_B = torch.nn.Parameter(0.1 * torch.randn(24, 4, generator=g))
+
+    def forward(self, x):
+        return ((x @ self.base.t() + x @ self.lora_A.t() @ self.lora_B.t()) ** 2).mean()
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from hyc_lora_b200.ddp import FlatGradSync
+    model = _Tiny()
+    sync = FlatGradSync(model.parameters())
+    assert sync.numel() == 4 * 24 * 2
+    x = torch.randn(8, 24, generator=torch.Generator().manual_seed(9))
+    for step in range(2):                       # second step: the flat buffer is reused after zero()
+        sync.zero()
+        model(x[rank * 4:(rank + 1) * 4]).backward()
+        sync.sync()
+    if rank == 0:
+        out.put((model.lora_A.grad.clone(), model.lora_B.grad.clone()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_flat_gradient_allreduce_matches_single_process():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    ga, gb = out.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    ref = _Tiny()
+    x = torch.randn(8, 24, generator=torch.Generator().manual_seed(9))
+    # each rank's loss is the mean over ITS shard; averaging the ranks gives the mean over the batch
+    (0.5 * ref(x[:4]) + 0.5 * ref(x[4:])).backward()
+    assert torch.allclose(ga, ref.lora_A.grad, atol=1e-6) and torch.allclose(gb, ref.lora_B.grad, atol=1e-6)
+
+
+def test_flat_buffer_views_and_single_process_noop():
+    from hyc_lora_b200.ddp import FlatGradSync
+    m = _Tiny()
+    sync = FlatGradSync(m.parameters())
+    m(torch.ones(2, 24)).backward()
+    assert m.lora_A.grad.data_ptr() == sync.flat.data_ptr()          # gradients accumulate straight into the flat buffer
+    assert sync.flat.abs().sum() > 0 and sync.sync() is None
