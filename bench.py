@@ -314,10 +314,68 @@ def run_ours(args):
                                                           "reference's eager norm + compress chain"}
         if args.sweep:
             line["sweep"] = sweep(packed, synthetic, oc, x, w, peak)
+    # free the operator benchmark's buffers before the model is built
+    del x, xin, out, p, y, rstd, x_host, y_host, codes_host
+    torch.cuda.empty_cache()
+    step = None
+    if not args.no_step:
+        try:
+            step = train_step_bench(args, world, rank, dev, barrier)
+        except Exception as e:  # the operator line must still be printed
+            step = {"metric": "7B HyC-LoRA train tokens/s", "error": f"{type(e).__name__}: {e}"[:300]}
+    if rank == 0:
+        if step is not None:
+            line["train_step"] = step
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def train_step_bench(args, world, rank, dev, barrier):
+    """Configuration 3: LLaMA-2-7B-shaped LoRA step (32 layers, hidden 4096, FFN 11008, 4-bit frozen base,
+    LoRA r=64 on the seven projections, bf16), batch 4 x 512 tokens per GPU, INT4 activations with 1 % outlier
+    channels and a 256-wide Hadamard rotation, data-parallel with one all-reduce of the LoRA gradients."""
+    import torch
+    import torch.distributed as dist
+    from hyc_lora_b200 import synthetic
+    from hyc_lora_b200.hosts.step import build_trainer
+
+    batch, seq, vocab = 4, 512, 32000
+    trainer = build_trainer("llama2_7b", layers=args.step_layers, bits=4, outlier_ratio=0.01, rotate=256, device=dev)
+    ids_host = synthetic.token_ids(3, batch, seq, vocab, salt=rank).pin_memory()
+    ids = torch.empty_like(ids_host, device=dev)
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def one():
+        ids.copy_(ids_host, non_blocking=True)            # host -> device copy of the step's inputs
+        loss = trainer.step(ids)
+        loss_host.copy_(loss.float(), non_blocking=True)  # device -> host read of the step's result
+
+    for _ in range(3):                                     # includes the two calibration calls of every site
+        one()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = args.step_steps
+    start.record()
+    for _ in range(steps):
+        one()
+    stop.record()
+    barrier()
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    tokens = batch * seq * world * steps
+    return {"metric": "7B HyC-LoRA train tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s",
+            "ms_per_step": ms / steps, "steps": steps, "loss": float(loss_host.item()),
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
+            "config": {"model": "LLaMA-2-7B shape, random init, 4-bit codebook base (block 64)",
+                       "layers": trainer.model.config.layers, "lora_r": 64, "trainable_params": trainer.trainable(),
+                       "batch_per_gpu": batch, "seq_len": seq, "activations": "INT4, 1% outlier channels, rotate 256",
+                       "parallelism": f"dp{world}", "attention": "torch scaled_dot_product_attention (causal)",
+                       "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": 4}}
 
 
 def sweep(packed, synthetic, oc, x, w, peak):
@@ -366,6 +424,20 @@ def sweep(packed, synthetic, oc, x, w, peak):
                                 timed(lambda: packed.norm_bwd(p, dy, w, rstd, None, "rms"), (base + 4 + 4 * d) * rows,
                                       "norm_bwd " + tag)
                                 timed(lambda: packed.act_bwd("silu", p, dy), (base + 4 * d) * rows, "silu_bwd " + tag)
+    # dequant-fused tensor-core weight gradient vs. decompress + library GEMM
+    for rows, bits, rank in ((65536, 4, 64), (65536, 4, 16), (65536, 2, 64), (65536, 8, 64), (2048, 4, 64)):
+        xs = x[:rows]
+        k = oc.n_outlier_count(d, 0.01)
+        ch = packed.select_channels(score, k)
+        p = packed.compress_n(xs, ch, bits, 0, 0)
+        g = torch.randn(rows, rank, device=x.device, dtype=torch.bfloat16)
+        nbytes = rows * (d * bits // 8 + 2 * rank + 4 + 2 * k) + 4 * rank * d
+        before = len(out)
+        timed(lambda: packed.lora_wgrad(p, g), nbytes, f"lora_wgrad tcgen05 T={rows} b={bits} r={rank}")
+        timed(lambda: packed.lora_wgrad(p, g, force_library=True), nbytes,
+              f"lora_wgrad decompress+library GEMM T={rows} b={bits} r={rank}")
+        for rec in out[before:]:
+            rec["TFLOPs"] = round(2.0 * rows * rank * d / (rec["ms"] * 1e-3) / 1e12, 1)
     # reference mode, one line per bit width (static per-channel scales)
     xs = x[:16384]
     xc = xs.float().cpu()[:512].to(torch.bfloat16).reshape(1, 512, d)
@@ -394,7 +466,9 @@ def run_case(args):
     dy = torch.randn(rows, COLS, device="cuda", dtype=torch.bfloat16)
     rstd = torch.ones(rows, device="cuda")
     p = packed.compress_n(x, ch, BITS, args.group, args.rotate)
+    g64 = torch.randn(rows, 64, device="cuda", dtype=torch.bfloat16)
     fns = {
+        "lora_wgrad": lambda: packed.lora_wgrad(p, g64),
         "norm_compress": lambda: packed.compress_n(x, ch, BITS, args.group, args.rotate, norm=norm),
         "compress": lambda: packed.compress_n(x, ch, BITS, args.group, args.rotate),
         "decompress": lambda: packed.decompress(p),
@@ -414,6 +488,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", action="store_true", help="add per-kernel numbers for the operator sweep")
+    ap.add_argument("--no-step", action="store_true", help="skip the 7B-shaped training step")
+    ap.add_argument("--step-layers", type=int, default=None, help="decoder layers of the step model (default 32)")
+    ap.add_argument("--step-steps", type=int, default=5)
     ap.add_argument("--case", default=None, help="profiling aid: run only this kernel (see run_case)")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--launches", type=int, default=4)
