@@ -103,7 +103,7 @@ constexpr uint32_t kASbo = 128, kALbo = 16 * 128, kAStage = (kChunk / 8) * kALbo
 constexpr uint32_t kBSbo = 128;
 
 template <int BITS>
-__global__ void __launch_bounds__(kWgThreads, 1) lora_wgrad_kernel(const __grid_constant__ WgradArgs a) {
+__global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_constant__ WgradArgs a) {
   constexpr int NSEG = 8 / BITS;
   extern __shared__ __align__(1024) unsigned char smem[];
   const PackedDev& p = a.p;
@@ -142,8 +142,50 @@ __global__ void __launch_bounds__(kWgThreads, 1) lora_wgrad_kernel(const __grid_
   const uint32_t idesc = instr_desc(npad);
   // conversion mapping: lane = token-in-group (k0) + 8 * (unit & 3); a warp item = (token group, unit >> 2)
   const int k0 = lane & 7, u_lo = lane >> 3;
+  constexpr int kAItems = (kChunk / 8) * 4 / (kWgThreads / 32);   // A items per warp and chunk (4)
+  constexpr int kBItems = 2;                                      // B items per warp and chunk (at most)
+  const int b_per_tg = (npad / 8 + 3) / 4;
+  // The packed bytes, scales and gradient vectors of chunk c+1 are loaded into registers before
+  // chunk c is converted, so their latency hides behind the conversion and the MMAs.
+  uint2 cb_reg[kAItems];
+  float sc_reg[kAItems];
+  uint4 g_reg[kBItems];
+  auto fetch = [&](int c) {
+    const long long t0 = t_begin + static_cast<long long>(c) * kChunk;
+#pragma unroll
+    for (int i = 0; i < kAItems; ++i) {
+      const int item = warp + i * (kWgThreads / 32);
+      const int tg = item >> 2, unit = ((item & 3) << 2) + u_lo;
+      const long long t = t0 + tg * 8 + k0;
+      cb_reg[i] = make_uint2(0, 0);
+      sc_reg[i] = 0.f;
+      if (t < t_end) {
+        cb_reg[i] = ld_stream_u2(p.codes + t * cb + byte0 + (unit << 3));
+        if (!p.group) sc_reg[i] = __ldg(p.scales + t);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kBItems; ++i) {
+      const int item = warp + i * (kWgThreads / 32);
+      const int tg = item / b_per_tg, n1 = (item % b_per_tg) * 4 + u_lo;
+      const long long t = t0 + tg * 8 + k0;
+      g_reg[i] = make_uint4(0, 0, 0, 0);
+      if (item < (kChunk / 8) * b_per_tg && n1 < npad / 8 && t < t_end && (n1 << 3) < a.rank)
+        g_reg[i] = *reinterpret_cast<const uint4*>(a.grad + t * a.rank + (n1 << 3));
+    }
+  };
+  if (nchunks > 0) fetch(0);
   for (int c = 0; c < nchunks; ++c) {
     const int buf = c & 1;
+    // move this chunk's registers aside and start the next chunk's loads
+    uint2 cb_cur[kAItems];
+    float sc_cur[kAItems];
+    uint4 g_cur[kBItems];
+#pragma unroll
+    for (int i = 0; i < kAItems; ++i) { cb_cur[i] = cb_reg[i]; sc_cur[i] = sc_reg[i]; }
+#pragma unroll
+    for (int i = 0; i < kBItems; ++i) g_cur[i] = g_reg[i];
+    if (c + 1 < nchunks) fetch(c + 1);
     if (c >= 2) {
       if (!mbar_wait_bounded(&bar_done[buf], ((c >> 1) - 1) & 1)) *fail = 1;
       tc_fence_after();
@@ -152,35 +194,32 @@ __global__ void __launch_bounds__(kWgThreads, 1) lora_wgrad_kernel(const __grid_
     unsigned char* abase = a_buf + static_cast<uint32_t>(buf) * NSEG * kAStage;
     unsigned char* bbase = b_buf + static_cast<uint32_t>(buf) * b_stage;
     // ---- A: codes -> bf16 values
-    for (int item = warp; item < (kChunk / 8) * 4; item += kWgThreads / 32) {
+#pragma unroll
+    for (int i = 0; i < kAItems; ++i) {
+      const int item = warp + i * (kWgThreads / 32);
       const int tg = item >> 2, unit = ((item & 3) << 2) + u_lo;
       const long long t = t0 + tg * 8 + k0;
-      uint2 cbits = make_uint2(0, 0);
       const bool live = t < t_end;
-      if (live) cbits = ld_stream_u2(p.codes + t * cb + byte0 + (unit << 3));
 #pragma unroll
       for (int s = 0; s < NSEG; ++s) {
-        float f[8];
         uint4 packed_vals = make_uint4(0, 0, 0, 0);
         if (live) {
+          float f[8];
           const int col = s * segw + byte0 + (unit << 3);
-          const float sc = __ldg(p.scales + t * G + (p.group ? (col >> 7) : 0));
-          dequant8<BITS>(cbits, s, sc, f);
+          const float sc = p.group ? __ldg(p.scales + t * G + (col >> 7)) : sc_cur[i];
+          dequant8<BITS>(cb_cur[i], s, sc, f);
           packed_vals = pack_bf16x8(f);
         }
         *reinterpret_cast<uint4*>(abase + s * kAStage + tg * kALbo + unit * kASbo + k0 * 16) = packed_vals;
       }
     }
     // ---- B: gradient rows
-    for (int item = warp; item < (kChunk / 8) * ((npad / 8 + 3) / 4); item += kWgThreads / 32) {
-      const int per_tg = (npad / 8 + 3) / 4;
-      const int tg = item / per_tg, n1 = (item % per_tg) * 4 + u_lo;
-      const long long t = t0 + tg * 8 + k0;
-      if (n1 < npad / 8) {
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (t < t_end && (n1 << 3) < a.rank) v = *reinterpret_cast<const uint4*>(a.grad + t * a.rank + (n1 << 3));
-        *reinterpret_cast<uint4*>(bbase + tg * b_lbo + n1 * kBSbo + k0 * 16) = v;
-      }
+#pragma unroll
+    for (int i = 0; i < kBItems; ++i) {
+      const int item = warp + i * (kWgThreads / 32);
+      const int tg = item / b_per_tg, n1 = (item % b_per_tg) * 4 + u_lo;
+      if (item < (kChunk / 8) * b_per_tg && n1 < npad / 8)
+        *reinterpret_cast<uint4*>(bbase + tg * b_lbo + n1 * kBSbo + k0 * 16) = g_cur[i];
     }
     fence_proxy_async();          // generic-proxy stores -> visible to the tensor-core (async) proxy
     tc_fence_before();
@@ -263,7 +302,7 @@ static int wgrad_splits(long long rows, int cols, int bits) {
   if (tiles <= 0) return 1;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  long long splits = (sms + tiles - 1) / tiles;
+  long long splits = (2 * sms + tiles - 1) / tiles;  // two CTAs per SM
   const long long max_splits = (rows + kChunk - 1) / kChunk;
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;
