@@ -354,6 +354,9 @@ def train_step_bench(args, world, rank, dev, barrier):
 
     for _ in range(3):                                     # includes the two calibration calls of every site
         one()
+    graphed = trainer.capture(ids) if not args.no_graph else False
+    for _ in range(2):
+        one()
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     steps = args.step_steps
@@ -369,7 +372,7 @@ def train_step_bench(args, world, rank, dev, barrier):
         ms = float(t.item())
     tokens = batch * seq * world * steps
     return {"metric": "7B HyC-LoRA train tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s",
-            "ms_per_step": ms / steps, "steps": steps, "loss": float(loss_host.item()),
+            "ms_per_step": ms / steps, "steps": steps, "loss": float(loss_host.item()), "cuda_graph": bool(graphed),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
             "config": {"model": "LLaMA-2-7B shape, random init, 4-bit codebook base (block 64)",
                        "layers": trainer.model.config.layers, "lora_r": 64, "trainable_params": trainer.trainable(),
@@ -491,6 +494,7 @@ def main():
     ap.add_argument("--no-step", action="store_true", help="skip the 7B-shaped training step")
     ap.add_argument("--step-layers", type=int, default=None, help="decoder layers of the step model (default 32)")
     ap.add_argument("--step-steps", type=int, default=5)
+    ap.add_argument("--no-graph", action="store_true", help="run the training step eagerly instead of from a CUDA graph")
     ap.add_argument("--case", default=None, help="profiling aid: run only this kernel (see run_case)")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--launches", type=int, default=4)

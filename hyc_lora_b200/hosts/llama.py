@@ -30,6 +30,7 @@ class DecoderConfig:
     lora_r: int = 64
     lora_alpha: float = 16.0
     base_quant: str = "nf4"
+    dtype: torch.dtype = torch.bfloat16
 
     @staticmethod
     def llama2_7b(**kw):
@@ -80,7 +81,8 @@ class Attention(nn.Module):
         super().__init__()
         self.c = c
         hd = c.hidden // c.heads
-        mk = lambda i, o: LoRALinear(i, o, c.lora_r, c.lora_alpha, c.base_quant, device=device, generator=gen)
+        mk = lambda i, o: LoRALinear(i, o, c.lora_r, c.lora_alpha, c.base_quant, device=device, dtype=c.dtype,
+                                     generator=gen)
         self.q_proj, self.k_proj = mk(c.hidden, c.heads * hd), mk(c.hidden, c.kv_heads * hd)
         self.v_proj, self.o_proj = mk(c.hidden, c.kv_heads * hd), mk(c.heads * hd, c.hidden)
 
@@ -99,7 +101,8 @@ class Attention(nn.Module):
 class MLP(nn.Module):
     def __init__(self, c: DecoderConfig, device, gen):
         super().__init__()
-        mk = lambda i, o: LoRALinear(i, o, c.lora_r, c.lora_alpha, c.base_quant, device=device, generator=gen)
+        mk = lambda i, o: LoRALinear(i, o, c.lora_r, c.lora_alpha, c.base_quant, device=device, dtype=c.dtype,
+                                     generator=gen)
         self.gate_proj, self.up_proj, self.down_proj = mk(c.hidden, c.ffn), mk(c.hidden, c.ffn), mk(c.ffn, c.hidden)
         self.act_fn = LlamaSiLU()
         self.hadamard = LlamaHadamard()
@@ -124,16 +127,19 @@ class DecoderLayer(nn.Module):
 class DecoderLM(nn.Module):
     """Causal LM host; ``forward(ids)`` returns the mean next-token cross-entropy with labels = ids."""
 
-    def __init__(self, c: DecoderConfig, device="cuda", seed: int = 0):
+    def __init__(self, c: DecoderConfig, device="cuda", seed: int = 0, init_on_cpu: bool = False):
         super().__init__()
-        gen = torch.Generator(device=device)
+        # init_on_cpu draws every weight from a CPU generator (identical on any machine) and moves it
+        gen = torch.Generator(device="cpu" if init_on_cpu else device)
         gen.manual_seed(seed)
         self.config = c
-        self.embed_tokens = nn.Embedding(c.vocab, c.hidden, device=device, dtype=torch.bfloat16)
+        self.embed_tokens = nn.Embedding(c.vocab, c.hidden, device=device, dtype=c.dtype)
+        emb = torch.empty(c.vocab, c.hidden, device=gen.device, dtype=torch.float32).normal_(0, 1, generator=gen)
+        self.embed_tokens.weight.data.copy_(emb)
         self.embed_tokens.weight.requires_grad_(False)
         self.layers = nn.ModuleList(DecoderLayer(c, device, gen) for _ in range(c.layers))
         self.norm = LlamaRMSNorm(c.hidden, c.eps, device)
-        self.lm_head = FrozenLinear(c.hidden, c.vocab, "bf16", device=device, generator=gen)
+        self.lm_head = FrozenLinear(c.hidden, c.vocab, "bf16", device=device, generator=gen, dtype=c.dtype)
 
     def forward(self, ids):
         x = self.embed_tokens(ids)

@@ -37,6 +37,17 @@ def nf4_codebook() -> torch.Tensor:
     return _CODEBOOK
 
 
+_CODEBOOK_DEV = {}
+
+
+def _codebook_on(device) -> torch.Tensor:
+    """Device copy of the codebook, made once per device (no host->device copy per call)."""
+    key = str(device)
+    if key not in _CODEBOOK_DEV:
+        _CODEBOOK_DEV[key] = nf4_codebook().to(device)
+    return _CODEBOOK_DEV[key]
+
+
 @torch.no_grad()
 def nf4_quantize(w: torch.Tensor, block: int = 64):
     """Blockwise absmax quantisation to the codebook.  Returns (codes uint8 [n/2], absmax fp32 [n/block])."""
@@ -56,7 +67,7 @@ def nf4_dequantize(codes: torch.Tensor, absmax: torch.Tensor, shape) -> torch.Te
     from .. import _lib
     n = codes.numel() * 2
     out = torch.empty(n, dtype=torch.bfloat16, device=codes.device)
-    book = nf4_codebook().to(codes.device)
+    book = _codebook_on(codes.device)
     _lib.check(_lib.lib.hyc_nf4_dequant(C.c_void_p(codes.data_ptr()), C.c_void_p(absmax.data_ptr()),
                                         C.c_void_p(book.data_ptr()), n, C.c_void_p(out.data_ptr()),
                                         C.c_void_p(torch.cuda.current_stream().cuda_stream)), "hyc_nf4_dequant")
@@ -81,11 +92,14 @@ class FrozenLinear(nn.Module):
     bf16 parameter (autograd keeps no input for a weight that does not train)."""
 
     def __init__(self, in_features: int, out_features: int, quant: str = "bf16", device=None, std: float = 0.02,
-                 generator=None):
+                 generator=None, dtype=torch.bfloat16):
         super().__init__()
         self.in_features, self.out_features, self.quant = in_features, out_features, quant
-        w = torch.empty(out_features, in_features, device=device, dtype=torch.bfloat16)
+        # drawn on the generator's device (CPU for reproducible small models), then moved
+        gdev = generator.device if generator is not None else device
+        w = torch.empty(out_features, in_features, device=gdev, dtype=torch.float32)
         w.normal_(0.0, std, generator=generator)
+        w = w.to(device=device, dtype=dtype)
         if quant == "nf4":
             codes, absmax = nf4_quantize(w)
             self.register_buffer("codes", codes)
@@ -108,10 +122,14 @@ class LoRALinear(nn.Module):
     def __init__(self, in_features: int, out_features: int, r: int = 64, alpha: float = 16.0, quant: str = "bf16",
                  device=None, dtype=torch.bfloat16, generator=None):
         super().__init__()
-        self.base_layer = FrozenLinear(in_features, out_features, quant, device=device, generator=generator)
+        self.base_layer = FrozenLinear(in_features, out_features, quant, device=device, generator=generator,
+                                       dtype=dtype)
         self.lora_A = nn.Linear(in_features, r, bias=False, device=device, dtype=dtype)
         self.lora_B = nn.Linear(r, out_features, bias=False, device=device, dtype=dtype)
-        nn.init.kaiming_uniform_(self.lora_A.weight, a=math.sqrt(5))
+        gdev = generator.device if generator is not None else device
+        bound = 1.0 / math.sqrt(in_features)           # kaiming-uniform with a = sqrt(5)
+        a = torch.empty(r, in_features, device=gdev, dtype=torch.float32).uniform_(-bound, bound, generator=generator)
+        self.lora_A.weight.data.copy_(a)
         nn.init.zeros_(self.lora_B.weight)
         self.scaling = alpha / r
 

@@ -14,22 +14,61 @@ from .replace import replace_module, uniform_config
 
 
 class Trainer:
+    """Forward, backward, LoRA-gradient exchange and AdamW update of one step.
+
+    ``capture()`` records the whole step into a CUDA graph once every site has finished
+    calibrating (three eager steps): the step launches a few thousand small kernels, and
+    replaying them from a graph removes the host-side launch cost that otherwise leaves the
+    GPU idle between them.  Calibration state lives in Python and is frozen by then, and no
+    steady-state operator call synchronises with the host, so the recorded step is the
+    steady-state step."""
+
     def __init__(self, model, lr: float = 1e-4):
         self.model = model
         self.params = lora_parameters(model)
         self.sync = FlatGradSync(self.params)
-        self.opt = torch.optim.AdamW(self.params, lr=lr, fused=True)
+        self.opt = torch.optim.AdamW(self.params, lr=lr, fused=True, capturable=True)
+        self.graph = None
+        self.static_ids = None
+        self.static_loss = None
+        self.eager_steps = 0
 
     def trainable(self) -> int:
         return self.sync.numel()
 
-    def step(self, ids: torch.Tensor) -> torch.Tensor:
+    def _step(self, ids: torch.Tensor) -> torch.Tensor:
         self.sync.zero()
         loss = self.model(ids)
         loss.backward()
         self.sync.sync()
         self.opt.step()
         return loss.detach()
+
+    def capture(self, ids: torch.Tensor) -> bool:
+        """Record the step for ``ids``' shape.  Returns False (and stays eager) if capture fails."""
+        while self.eager_steps < 3:          # calibration calls and optimizer state first
+            self.step(ids)
+        try:
+            torch.cuda.synchronize()
+            self.static_ids = ids.clone()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.static_loss = self._step(self.static_ids)
+            torch.cuda.synchronize()
+            self.graph = graph
+            return True
+        except Exception:
+            self.graph = None
+            torch.cuda.synchronize()
+            return False
+
+    def step(self, ids: torch.Tensor) -> torch.Tensor:
+        if self.graph is not None:
+            self.static_ids.copy_(ids, non_blocking=True)
+            self.graph.replay()
+            return self.static_loss
+        self.eager_steps += 1
+        return self._step(ids)
 
 
 def build_trainer(arch: str = "llama2_7b", layers: int | None = None, bits: int = 4, outlier_ratio: float = 0.01,

@@ -112,3 +112,22 @@ def test_encoder_host_with_the_reference_preset_sparsity():
         loss.backward()
     grads = _lora_grads(model)
     assert torch.isfinite(loss) and all(torch.isfinite(g).all() for g in grads.values())
+
+
+def test_graph_captured_step_matches_eager_step():
+    from hyc_lora_b200.hosts.step import build_trainer
+    ids = synthetic.token_ids(3, 2, 128, 32000).cuda()
+    losses = {}
+    for mode in ("eager", "graph"):
+        tr = build_trainer("llama2_7b", layers=2, seed=5)
+        for _ in range(3):
+            tr.step(ids)
+        if mode == "graph":
+            assert tr.capture(ids)
+        out = []
+        for _ in range(4):
+            out.append(float(tr.step(ids).item()))
+        losses[mode] = out
+    assert losses["graph"][-1] < losses["graph"][0]                 # it trains
+    for a, b in zip(losses["eager"], losses["graph"]):
+        assert abs(a - b) < 2e-2 * abs(a)
