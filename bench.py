@@ -222,7 +222,8 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 10)              # clocks and caches settle within the first few launches
+    for _ in range(warm):
         out = step()
     barrier()
     sampler = ClockSampler(local)
@@ -261,15 +262,36 @@ def run_ours(args):
     h2d = x_host.numel() * 2
     d2h = y_host.numel() * 2 + codes_host.numel() + oval_host.numel() * 2 + scales_host.numel() * 4 + rstd_host.numel() * 4
     xin = torch.empty_like(x)
+    # The rows go through in pieces so that the copy of piece i+1 to the device, the kernel on piece i
+    # and the copy of piece i-1 back to the host overlap (PCIe is full duplex): three streams, events.
+    piece = 8192
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    pieces = [(r0, min(ROWS, r0 + piece)) for r0 in range(0, ROWS, piece)]
 
     def e2e_step():
-        xin.copy_(x_host, non_blocking=True)
-        pp, yy, rr, _ = packed.compress_n(xin, channels, BITS, GROUP, ROTATE, norm=norm)
-        y_host.copy_(yy, non_blocking=True)
-        codes_host.copy_(pp.codes, non_blocking=True)
-        oval_host.copy_(pp.out_value, non_blocking=True)
-        scales_host.copy_(pp.scales, non_blocking=True)
-        rstd_host.copy_(rr, non_blocking=True)
+        cur = torch.cuda.current_stream()
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        keep = []
+        for r0, r1 in pieces:
+            with torch.cuda.stream(s_in):
+                xin[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            cur.wait_event(ev_in)
+            pp, yy, rr, _ = packed.compress_n(xin[r0:r1], channels, BITS, GROUP, ROTATE, norm=norm)
+            ev_k = torch.cuda.Event()
+            ev_k.record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_k)
+                y_host[r0:r1].copy_(yy, non_blocking=True)
+                codes_host[r0:r1].copy_(pp.codes, non_blocking=True)
+                oval_host[r0:r1].copy_(pp.out_value, non_blocking=True)
+                scales_host[r0:r1].copy_(pp.scales, non_blocking=True)
+                rstd_host[r0:r1].copy_(rr, non_blocking=True)
+            keep.append((pp, yy, rr))
+        cur.wait_stream(s_out)          # the step ends when its last result is on the host
+        return keep
 
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(2):
@@ -293,7 +315,7 @@ def run_ours(args):
         value = achieved * world
         line = {
             "metric": "fused norm+compress HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": workload_name(), "rows_per_gpu": ROWS, "cols": COLS, "bits": BITS,
@@ -303,7 +325,8 @@ def run_ours(args):
                          "traffic": committed_traffic(), "peak_source": f"of {which}",
                          "kernel": "hyc::fwd_kernel<bf16, N, 4, norm>"},
             "e2e": {"value": (bytes_per_step * e2e_steps * world) / (e2e_ms / 1e3) / 1e9, "unit": "GB/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "pipeline": "8 pieces of 8192 rows; H2D, kernel and D2H on three streams"},
             "gpu_launches": args.steps,
             "clocks": clocks,
         }

@@ -126,7 +126,8 @@ int hyc_act_bwd(int op, const hyc_packed* s1, const hyc_packed* s2, const void* 
   {
     const BwdPlan bp = plan_bwd_fast(s1, prod ? s2 : nullptr, 4, false, 0, 512, 0,
                                      align_up(static_cast<uint32_t>(D) * s1->bits / 8, 128) * (prod ? 2 : 1) +
-                                         static_cast<uint32_t>(D) * (g_dtype == HYC_BF16 ? 2 : 4));
+                                         static_cast<uint32_t>(D) * (g_dtype == HYC_BF16 ? 2 : 4),
+                                     256, 2);
     if (bp.ok) {
       ActFastArgs fa;
       memset(&fa, 0, sizeof(fa));

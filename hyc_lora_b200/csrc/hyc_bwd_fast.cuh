@@ -582,13 +582,16 @@ struct BwdPlan {
 // reg_groups: cap on 8-channel register groups per thread for the kernel at hand;
 // slot_bytes: bytes one staged row needs (codes, gradient row, ...)
 inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_groups, bool want_w, int acc_rows,
-                             int max_threads, int grid_cap, uint32_t slot_bytes) {
+                             int max_threads, int grid_cap, uint32_t slot_bytes, int min_threads = 0,
+                             int default_stages = 3) {
   BwdPlan b;
   memset(&b, 0, sizeof(b));
   if (q->mode != HYC_MODE_N || q->rotate > 256) return b;
   const int D = q->cols, nseg = 8 / q->bits;
   b.rot = q->rotate != 0;
   int threads = g_tune_threads ? g_tune_threads : (D <= 1024 ? 64 : D <= 4096 ? 128 : 256);
+  // kernels that hold two operands per element in registers run better with fewer elements per thread
+  if (!g_tune_threads && min_threads && threads < min_threads && D >= 8 * min_threads) threads = min_threads;
   if (b.rot) {
     const int chunks = (D + 255) / 256;
     for (; threads <= max_threads; threads *= 2) {
@@ -618,7 +621,7 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
   off = align_up(off, 128);
   b.L.off_slots = off;
   b.L.slot_bytes = align_up(slot_bytes, 128);
-  b.L.stages = g_tune_stages ? g_tune_stages : 3;
+  b.L.stages = g_tune_stages ? g_tune_stages : default_stages;
   if (b.L.stages > kMaxStages) b.L.stages = kMaxStages;
   while (b.L.stages > 2 && off + b.L.slot_bytes * b.L.stages > 64 * 1024) --b.L.stages;
   b.L.total = off + b.L.slot_bytes * b.L.stages;

@@ -75,7 +75,7 @@ int hyc_decompress(const hyc_packed* in, const hyc_dense* o, void* stream_) {
   if (in->rows == 0) return HYC_OK;
   {
     // register-resident kernel for the channel-outlier mode
-    const BwdPlan bp = plan_bwd_fast(in, nullptr, 4, false, 0, 512, 0, static_cast<uint32_t>(in->cols) * in->bits / 8);
+    const BwdPlan bp = plan_bwd_fast(in, nullptr, 4, false, 0, 512, 0, static_cast<uint32_t>(in->cols) * in->bits / 8, 0, 2);
     if (bp.ok) {
       DecFastArgs fa;
       memset(&fa, 0, sizeof(fa));

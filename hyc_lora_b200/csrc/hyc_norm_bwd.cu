@@ -163,7 +163,8 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
   {
     const BwdPlan bp = plan_bwd_fast(saved, nullptr, 4, true, g->dweight ? (g->dbias ? 2 : 1) : 0, 256, kPartialRowsMax,
                                      align_up(static_cast<uint32_t>(D) * saved->bits / 8, 128) +
-                                         static_cast<uint32_t>(D) * (g->dy_dtype == HYC_BF16 ? 2 : 4));
+                                         static_cast<uint32_t>(D) * (g->dy_dtype == HYC_BF16 ? 2 : 4),
+                                     256, 4);
     if (bp.ok) {
       NormBwdFastArgs fa;
       memset(&fa, 0, sizeof(fa));

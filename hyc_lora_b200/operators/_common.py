@@ -85,3 +85,33 @@ def update_static(static_value, iteration, outlier, L, scale, R):
     static_value[3] = R if static_value[3] is None else (n * static_value[3] + R) / (n + 1)
     if isinstance(static_value, StaticList):
         static_value.cache.clear()
+
+
+def calibration_state_dict(module) -> dict:
+    """Calibration state of one ``EfficientMemory*`` module as plain tensors / numbers, so that a
+    resumed run does not recalibrate (in the reference this state is Python attributes only and is
+    lost on resume)."""
+    out = {"iteration": module.iteration}
+    for name in ("static_value", "static_value_1", "static_value_2"):
+        if hasattr(module, name):
+            v = getattr(module, name)
+            out[name] = [None if t is None else t.detach().clone() for t in v] if isinstance(v, list) else (
+                None if v is None else v.detach().clone())
+    for name in ("site", "site_1", "site_2"):
+        if hasattr(module, name):
+            c = getattr(module, name).calib
+            out[name] = {"score": None if c.score is None else c.score.clone(),
+                         "channels": None if c.channels is None else c.channels.clone()}
+    return out
+
+
+def load_calibration_state_dict(module, state: dict) -> None:
+    module.iteration = int(state["iteration"])
+    for name in ("static_value", "static_value_1", "static_value_2"):
+        if name in state:
+            v = state[name]
+            setattr(module, name, StaticList(v) if isinstance(v, list) else v)
+    for name in ("site", "site_1", "site_2"):
+        if name in state and hasattr(module, name):
+            c = getattr(module, name).calib
+            c.score, c.channels = state[name]["score"], state[name]["channels"]
