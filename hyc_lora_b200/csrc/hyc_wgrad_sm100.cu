@@ -4,21 +4,25 @@
 //
 // X_hat is never written to HBM.  A CTA owns 128 packed byte columns of the code rows (that is
 // 8/bits tiles of 128 channels, one per row segment) and a slice of the tokens.  For every
-// chunk of 64 tokens all threads rebuild the bf16 values from the codes (integer -> float
-// through the mantissa of 2^23, times the token / group scale, one rounding to bf16 -- the
-// same values the decompress kernel produces) and store them, 16 bytes per token and 8
-// channels, into shared memory in the MN-major no-swizzle core-matrix layout tcgen05 reads;
-// the gradient rows are copied into the same layout.  One thread then issues
+// chunk of 64 tokens all threads turn the packed fields into exact bf16 integers (code minus
+// offset: one byte permute drops a field pair into the mantissas of 128.0, one packed subtract
+// removes 128 + offset) and store them, 16 bytes per token and 8 channels, into shared memory
+// in the MN-major no-swizzle core-matrix layout tcgen05 reads; the scale of the token (or of
+// the token and the 128-channel tile) is folded into the gradient rows, which are rounded to
+// bf16 and stored in the same layout:  sum_t G[t,n] * (q[t,d] * s[t])  =  sum_t (G[t,n] s[t]) * q[t,d].
+// (8-bit codes are dequantised on the A side instead.)  One thread then issues
 // tcgen05.mma (M = 128 channels, N = rank, K = 16 tokens per instruction) with the
 // accumulators in tensor memory, and commits to an mbarrier that tells everybody when the
-// staging buffer may be overwritten (two buffers, so conversion of chunk c+1 overlaps the
-// MMAs of chunk c).  At the end four warps read the accumulators back with tcgen05.ld and
-// store one partial [rank, D] slab per token slice; a second kernel adds the slabs.
+// staging buffer may be overwritten (two buffers; the packed bytes of chunk c+1 are already in
+// registers while chunk c is converted).  At the end four warps read the accumulators back
+// with tcgen05.ld and store one partial [rank, D] slab per token slice; a second kernel adds
+// the slabs.
 //
 // Channel-outlier mode only.  Outlier channels carry the zero code, so their columns come out
 // as zero here; the caller adds G^T * out_value there.  With rotation the kernel contracts the
 // un-rotated codes and the rotation is applied to the `rank` output rows afterwards
 // (X_hat = Q H  =>  G^T X_hat = (G^T Q) H).
+#include <mutex>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -31,7 +35,7 @@ namespace hyc {
 
 constexpr int kChunk = 64;          // tokens per staging buffer
 constexpr int kTileM = 128;         // channels per accumulator tile
-constexpr int kWgThreads = 256;
+constexpr int kWgThreads = 512;
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------
 
@@ -48,14 +52,17 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// D[tmem] (+)= A[smem] * B[smem], bf16 x bf16 -> fp32, issued by one thread
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
+// D[tmem] (+)= A[smem] * B[smem], bf16 x bf16 -> fp32, issued by one thread.  The two shared-memory
+// descriptors arrive as (low, high) words.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -74,13 +81,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_u4(uint32_t saddr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 
 // Shared-memory matrix descriptor, no swizzle.  Core matrix = 8 rows of 16 bytes; `lbo` is the
-// byte distance between core matrices along K, `sbo` along M/N (MN-major operands).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo >> 4) << 16) |
-         (static_cast<uint64_t>(sbo >> 4) << 32) | (1ull << 46);
+// byte distance between core matrices along K, `sbo` along M/N (MN-major operands).  Low word:
+// address >> 4 (14 bits) and lbo >> 4 at bit 16; high word: sbo >> 4 and the version bit (bit 46).
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo) {
+  return ((saddr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16);
 }
+__device__ __forceinline__ constexpr uint32_t desc_hi(uint32_t sbo) { return (sbo >> 4) | (1u << 14); }
 
 // instruction descriptor: fp32 accumulate, bf16 A and B, both MN-major, M = 128, N = n
 __host__ __device__ constexpr uint32_t instr_desc(int n) {
@@ -119,7 +130,7 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 16);
   uint32_t* fail = reinterpret_cast<uint32_t*>(smem + 20);
   unsigned char* a_buf = smem + 1024;                              // [2][NSEG][kAStage]
-  unsigned char* b_buf = a_buf + 2u * NSEG * kAStage;              // [2][b_stage]
+  unsigned char* b_buf = a_buf + 2u * NSEG * kAStage;              // [2][B tiles][b_stage]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) {
     mbar_init(&bar_done[0], 1);
@@ -142,84 +153,138 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
   const uint32_t idesc = instr_desc(npad);
   // conversion mapping: lane = token-in-group (k0) + 8 * (unit & 3); a warp item = (token group, unit >> 2)
   const int k0 = lane & 7, u_lo = lane >> 3;
-  constexpr int kAItems = (kChunk / 8) * 4 / (kWgThreads / 32);   // A items per warp and chunk (4)
-  constexpr int kBItems = 2;                                      // B items per warp and chunk (at most)
-  const int b_per_tg = (npad / 8 + 3) / 4;
-  // The packed bytes, scales and gradient vectors of chunk c+1 are loaded into registers before
-  // chunk c is converted, so their latency hides behind the conversion and the MMAs.
+  constexpr int kAItems = (kChunk / 8) * 4 / (kWgThreads / 32);   // A items per warp and chunk
+  const int b_per_tg = (npad / 8 + 3) / 4;                         // 1 or 2 B items per token group
+  // B tiles per buffer: the scale is folded into the gradient operand, so group scales (one per
+  // 128-channel tile, i.e. per segment) need one scaled copy of the gradient rows per segment
+  const int nb = (BITS < 8 && p.group) ? NSEG : 1;
+  // Per-thread source pointers and shared-memory offsets are set up once and advanced by a
+  // constant per chunk.  Tokens past the end of the slice contribute nothing because their
+  // gradient rows are stored as zeros; the code rows only have to be readable, so their
+  // pointer is clamped to the last row of the tensor instead of being predicated.
+  const unsigned char* a_src[kAItems];
+  const unsigned char* a_last[kAItems];
+  const float* a_sc[kAItems];             // 8-bit path: scale of the A item
+  uint32_t a_dst[kAItems];
+#pragma unroll
+  for (int i = 0; i < kAItems; ++i) {
+    const int item = warp + i * (kWgThreads / 32);
+    const int tg = item >> 2, unit = ((item & 3) << 2) + u_lo;
+    const long long t = t_begin + tg * 8 + k0;
+    const int colb = byte0 + (unit << 3);
+    a_src[i] = p.codes + t * cb + colb;
+    a_last[i] = p.codes + (p.rows - 1) * cb + colb;
+    a_sc[i] = p.scales + t * G + (p.group ? (colb >> 7) : 0);
+    a_dst[i] = tg * kALbo + unit * kASbo + k0 * 16;
+  }
+  // B item of this thread (one per warp and chunk at most)
+  const int b_tg = b_per_tg == 2 ? (warp >> 1) : warp;
+  const int b_n1 = (b_per_tg == 2 ? (warp & 1) : 0) * 4 + u_lo;
+  const bool b_own = warp < (kChunk / 8) * b_per_tg && b_n1 < npad / 8;
+  const bool b_real = b_own && (b_n1 << 3) < a.rank;               // ranks past `rank` stay zero
+  long long b_t = t_begin + b_tg * 8 + k0;
+  const __nv_bfloat16* b_src = a.grad + b_t * a.rank + (b_n1 << 3);
+  const float* b_sc = p.scales + b_t * G + (p.group ? (byte0 >> 7) : 0);
+  const int b_sc_seg = p.group ? (segw >> 7) : 0;                  // scale index step between segments
+  const uint32_t b_dst = b_tg * b_lbo + b_n1 * kBSbo + k0 * 16;
+  const long long a_step = static_cast<long long>(kChunk) * cb;
+  const float* const sc_last = p.scales + (p.rows - 1) * G;       // last row of scales (clamp for reads)
+
   uint2 cb_reg[kAItems];
-  float sc_reg[kAItems];
-  uint4 g_reg[kBItems];
-  auto fetch = [&](int c) {
-    const long long t0 = t_begin + static_cast<long long>(c) * kChunk;
+  float sc_reg[kAItems];          // 8-bit path only
+  uint4 g_reg;
+  float gs_reg[NSEG];
+  auto fetch = [&]() {
 #pragma unroll
     for (int i = 0; i < kAItems; ++i) {
-      const int item = warp + i * (kWgThreads / 32);
-      const int tg = item >> 2, unit = ((item & 3) << 2) + u_lo;
-      const long long t = t0 + tg * 8 + k0;
-      cb_reg[i] = make_uint2(0, 0);
-      sc_reg[i] = 0.f;
-      if (t < t_end) {
-        cb_reg[i] = ld_stream_u2(p.codes + t * cb + byte0 + (unit << 3));
-        if (!p.group) sc_reg[i] = __ldg(p.scales + t);
+      const unsigned char* src = a_src[i] < a_last[i] ? a_src[i] : a_last[i];
+      cb_reg[i] = ld_stream_u2(src);
+      if (BITS == 8) {
+        const float* sp = a_sc[i] < sc_last + G ? a_sc[i] : sc_last;
+        sc_reg[i] = __ldg(sp);
+        a_sc[i] += kChunk * G;
+      }
+      a_src[i] += a_step;
+    }
+    g_reg = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int s = 0; s < NSEG; ++s) gs_reg[s] = 0.f;
+    if (b_real && b_t < t_end) {
+      g_reg = *reinterpret_cast<const uint4*>(b_src);
+      if (BITS < 8) {
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s)
+          if (s < nb) gs_reg[s] = __ldg(b_sc + s * b_sc_seg);
       }
     }
-#pragma unroll
-    for (int i = 0; i < kBItems; ++i) {
-      const int item = warp + i * (kWgThreads / 32);
-      const int tg = item / b_per_tg, n1 = (item % b_per_tg) * 4 + u_lo;
-      const long long t = t0 + tg * 8 + k0;
-      g_reg[i] = make_uint4(0, 0, 0, 0);
-      if (item < (kChunk / 8) * b_per_tg && n1 < npad / 8 && t < t_end && (n1 << 3) < a.rank)
-        g_reg[i] = *reinterpret_cast<const uint4*>(a.grad + t * a.rank + (n1 << 3));
-    }
+    b_t += kChunk;
+    b_src += kChunk * a.rank;
+    b_sc += kChunk * G;
   };
-  if (nchunks > 0) fetch(0);
+  if (nchunks > 0) fetch();
+  const uint32_t a_smem = smem_u32(a_buf), b_smem = smem_u32(b_buf);
+  const uint32_t b_k_step = (2u * b_lbo) >> 4, b_s_step = nb > 1 ? (b_stage >> 4) : 0u;   // descriptor address steps
   for (int c = 0; c < nchunks; ++c) {
     const int buf = c & 1;
     // move this chunk's registers aside and start the next chunk's loads
     uint2 cb_cur[kAItems];
     float sc_cur[kAItems];
-    uint4 g_cur[kBItems];
+    float gs_cur[NSEG];
 #pragma unroll
     for (int i = 0; i < kAItems; ++i) { cb_cur[i] = cb_reg[i]; sc_cur[i] = sc_reg[i]; }
+    const uint4 g_cur = g_reg;
 #pragma unroll
-    for (int i = 0; i < kBItems; ++i) g_cur[i] = g_reg[i];
-    if (c + 1 < nchunks) fetch(c + 1);
+    for (int s = 0; s < NSEG; ++s) gs_cur[s] = gs_reg[s];
+    if (c + 1 < nchunks) fetch();
     if (c >= 2) {
       if (!mbar_wait_bounded(&bar_done[buf], ((c >> 1) - 1) & 1)) *fail = 1;
       tc_fence_after();
     }
-    const long long t0 = t_begin + static_cast<long long>(c) * kChunk;
-    unsigned char* abase = a_buf + static_cast<uint32_t>(buf) * NSEG * kAStage;
-    unsigned char* bbase = b_buf + static_cast<uint32_t>(buf) * b_stage;
-    // ---- A: codes -> bf16 values
+    const uint32_t abase = a_smem + static_cast<uint32_t>(buf) * NSEG * kAStage;
+    const uint32_t bbase = b_smem + static_cast<uint32_t>(buf) * nb * b_stage;
+    // ---- A operand.  Below 8 bits: the integer code minus its offset as an exact bf16 (a field is
+    // dropped into the mantissa of 128.0 with one byte permute per pair, then 128 + offset is
+    // subtracted in packed bf16 arithmetic).  8 bits: dequantised values.
 #pragma unroll
     for (int i = 0; i < kAItems; ++i) {
-      const int item = warp + i * (kWgThreads / 32);
-      const int tg = item >> 2, unit = ((item & 3) << 2) + u_lo;
-      const long long t = t0 + tg * 8 + k0;
-      const bool live = t < t_end;
 #pragma unroll
       for (int s = 0; s < NSEG; ++s) {
-        uint4 packed_vals = make_uint4(0, 0, 0, 0);
-        if (live) {
+        uint4 v;
+        if (BITS == 8) {
           float f[8];
-          const int col = s * segw + byte0 + (unit << 3);
-          const float sc = p.group ? __ldg(p.scales + t * G + (col >> 7)) : sc_cur[i];
-          dequant8<BITS>(cb_cur[i], s, sc, f);
-          packed_vals = pack_bf16x8(f);
+          dequant8<BITS>(cb_cur[i], s, sc_cur[i], f);
+          v = pack_bf16x8(f);
+        } else {
+          constexpr uint32_t m = 0x01010101u * CodeTraits<BITS>::kMask;
+          const uint32_t lo = (cb_cur[i].x >> (s * BITS)) & m, hi = (cb_cur[i].y >> (s * BITS)) & m;
+          const __nv_bfloat162 bias = __float2bfloat162_rn(128.f + static_cast<float>(CodeTraits<BITS>::kOff));
+          auto two = [&](uint32_t w, uint32_t sel) {
+            const uint32_t bits = __byte_perm(w, 0x43004300u, sel);      // (128 + field) as bf16x2
+            __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&bits), bias);
+            return *reinterpret_cast<uint32_t*>(&r);
+          };
+          v = make_uint4(two(lo, 0x7150), two(lo, 0x7352), two(hi, 0x7150), two(hi, 0x7352));
         }
-        *reinterpret_cast<uint4*>(abase + s * kAStage + tg * kALbo + unit * kASbo + k0 * 16) = packed_vals;
+        st_shared_u4(abase + s * kAStage + a_dst[i], v);
       }
     }
-    // ---- B: gradient rows
+    // ---- B operand: gradient rows, times the token (or token-and-tile) scale below 8 bits
+    if (b_own) {
+      if (BITS == 8) {
+        st_shared_u4(bbase + b_dst, g_cur);
+      } else {
+        float gv[8];
+        unpack_bf16x8(g_cur, gv);
 #pragma unroll
-    for (int i = 0; i < kBItems; ++i) {
-      const int item = warp + i * (kWgThreads / 32);
-      const int tg = item / b_per_tg, n1 = (item % b_per_tg) * 4 + u_lo;
-      if (item < (kChunk / 8) * b_per_tg && n1 < npad / 8)
-        *reinterpret_cast<uint4*>(bbase + tg * b_lbo + n1 * kBSbo + k0 * 16) = g_cur[i];
+        for (int s = 0; s < NSEG; ++s) {
+          if (s < nb) {
+            float sv[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sv[e] = gv[e] * gs_cur[s];
+            st_shared_u4(bbase + s * b_stage + b_dst, pack_bf16x8(sv));
+          }
+        }
+      }
     }
     fence_proxy_async();          // generic-proxy stores -> visible to the tensor-core (async) proxy
     tc_fence_before();
@@ -227,13 +292,19 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
     if (*fail) break;
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t a_addr = smem_u32(abase), b_addr = smem_u32(bbase);
+      // Only the address field (low word) of a descriptor changes between instructions: one
+      // add per operand and instruction keeps this single-thread section short -- every other
+      // warp meets it again at the next barrier.
+      const uint32_t a_lo = desc_lo(abase, kALbo), b_lo = desc_lo(bbase, b_lbo);
+      const uint32_t acc0 = c > 0 ? 1u : 0u;
 #pragma unroll
       for (int s = 0; s < NSEG; ++s) {
+#pragma unroll
         for (int ks = 0; ks < kChunk / 16; ++ks) {
-          const uint64_t da = smem_desc(a_addr + s * kAStage + ks * 2 * kALbo, kALbo, kASbo);
-          const uint64_t db = smem_desc(b_addr + ks * 2 * b_lbo, b_lbo, kBSbo);
-          umma_bf16(tmem_base + static_cast<uint32_t>(s * npad), da, db, idesc, (c > 0 || ks > 0) ? 1u : 0u);
+          umma_bf16(tmem_base + static_cast<uint32_t>(s) * static_cast<uint32_t>(npad),
+                    a_lo + ((s * kAStage + ks * 2 * kALbo) >> 4), desc_hi(kASbo),
+                    b_lo + static_cast<uint32_t>(s) * b_s_step + static_cast<uint32_t>(ks) * b_k_step, desc_hi(kBSbo),
+                    idesc, ks > 0 ? 1u : acc0);
         }
       }
       umma_commit(&bar_done[buf]);
@@ -297,34 +368,165 @@ __global__ void wgrad_rotate_rows_kernel(float* out, int D, int n) {
   for (int c = threadIdx.x; c < D; c += blockDim.x) row[c] = rowbuf[c];
 }
 
-static int wgrad_splits(long long rows, int cols, int bits) {
-  const int tiles = cols * bits / 8 / kTileM;
-  if (tiles <= 0) return 1;
+// ---- columns of the outlier channels: out[n, channels[j]] = sum_t grad[t, n] * out_value[t, j].
+// A CTA owns a token slice and walks it in chunks of kSideChunk tokens: the chunk's gradient rows
+// and outlier values (both contiguous in memory) are copied to shared memory with 16-byte loads
+// by all threads, then a thread owning (outlier j, 8 consecutive ranks) accumulates over the
+// chunk.  A warp covers 4 outliers x 8 rank groups at rank 64: the value read is a broadcast, the
+// gradient read one conflict-free 128-byte line.  Slices are summed in a fixed order by
+// wgrad_side_scatter_kernel, which also scatters to the channel columns.
+constexpr int kSideChunk = 64;
+
+__global__ void wgrad_side_kernel(const __nv_bfloat16* __restrict__ out_value, const __nv_bfloat16* __restrict__ grad,
+                                  long long rows, long long rows_per, int k, int rank, float* __restrict__ part) {
+  extern __shared__ __align__(16) unsigned char side_smem[];
+  __nv_bfloat16* sg = reinterpret_cast<__nv_bfloat16*>(side_smem);              // [kSideChunk][rank]
+  __nv_bfloat16* sv = sg + kSideChunk * rank;                                    // [kSideChunk][k] (+ padding)
+  const int r8 = rank >> 3;
+  const int units = k * r8;
+  const long long t0 = blockIdx.x * rows_per;   // rows_per is a multiple of kSideChunk: chunk starts stay 16-byte aligned
+  long long t1 = t0 + rows_per;
+  if (t1 > rows) t1 = rows;
+  constexpr int kMaxOwn = 4;                    // units per thread (host sizes the CTA so that this covers all)
+  float acc[kMaxOwn][8];
+#pragma unroll
+  for (int o = 0; o < kMaxOwn; ++o)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[o][e] = 0.f;
+  for (long long c0 = t0; c0 < t1; c0 += kSideChunk) {
+    const int nt = static_cast<int>(t1 - c0 < kSideChunk ? t1 - c0 : kSideChunk);
+    const int g16 = nt * rank * 2 / 16;                    // rank % 8 == 0: whole 16-byte pieces
+    const uint4* gsrc = reinterpret_cast<const uint4*>(grad + c0 * rank);
+    for (int i = threadIdx.x; i < g16; i += blockDim.x) reinterpret_cast<uint4*>(sg)[i] = __ldg(gsrc + i);
+    const int vbytes = nt * k * 2;
+    const int v16 = vbytes / 16;
+    const uint4* vsrc = reinterpret_cast<const uint4*>(out_value + c0 * k);
+    for (int i = threadIdx.x; i < v16; i += blockDim.x) reinterpret_cast<uint4*>(sv)[i] = __ldg(vsrc + i);
+    for (int i = v16 * 8 + threadIdx.x; i < nt * k; i += blockDim.x) sv[i] = out_value[c0 * k + i];   // ragged tail
+    __syncthreads();
+#pragma unroll
+    for (int o = 0; o < kMaxOwn; ++o) {
+      const int u = threadIdx.x + o * blockDim.x;
+      if (u < units) {
+        const int j = u / r8, n8 = u - j * r8;
+#pragma unroll 4
+        for (int t = 0; t < nt; ++t) {
+          const float v = __bfloat162float(sv[t * k + j]);
+          float g[8];
+          unpack_bf16x8(*reinterpret_cast<const uint4*>(sg + t * rank + (n8 << 3)), g);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[o][e] = fmaf(v, g[e], acc[o][e]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int o = 0; o < kMaxOwn; ++o) {
+    const int u = threadIdx.x + o * blockDim.x;
+    if (u < units) {
+      const int j = u / r8, n8 = u - j * r8;
+      float* dst = part + (static_cast<long long>(blockIdx.x) * k + j) * rank + (n8 << 3);
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[o][0], acc[o][1], acc[o][2], acc[o][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[o][4], acc[o][5], acc[o][6], acc[o][7]);
+    }
+  }
+}
+
+__global__ void wgrad_side_scatter_kernel(const float* __restrict__ part, int slices, const int* __restrict__ channels,
+                                          int k, int rank, int D, float* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;   // (j, n)
+  if (i >= k * rank) return;
+  const int j = i / rank, n = i - j * rank;
+  float s = 0.f;
+  for (int q = 0; q < slices; ++q) s += part[static_cast<long long>(q) * k * rank + i];
+  out[static_cast<long long>(n) * D + channels[j]] = s;
+}
+
+struct WgradPlan {
+  int splits;          // token slices of the tensor-core kernel
+  int side_slices;     // token slices of the outlier-column kernel (0: no outlier channels)
+  long long side_rows_per;
+  uint32_t smem_bytes, tmem_cols;
+  int npad;
+  long long scratch_floats;
+};
+
+// Resident CTAs per SM from the kernel's own resource use (registers, shared memory, threads).
+template <int BITS>
+static int wgrad_ctas_per_sm(uint32_t smem_bytes, int dev) {
+  auto kern = lora_wgrad_kernel<BITS>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) != cudaSuccess) return 0;
+  cudaFuncAttributes fa;
+  if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return 0;
+  int smem_sm = 0, regs_sm = 0, thr_sm = 0, reserved = 0;
+  if (cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&thr_sm, cudaDevAttrMaxThreadsPerMultiProcessor, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess)
+    return 0;
+  const long long per_cta_smem = static_cast<long long>(smem_bytes) + fa.sharedSizeBytes + reserved;
+  const int regs_cta = ((fa.numRegs + 7) / 8 * 8) * kWgThreads;
+  int n = static_cast<int>(smem_sm / per_cta_smem);
+  if (regs_cta > 0 && regs_sm / regs_cta < n) n = regs_sm / regs_cta;
+  if (thr_sm / kWgThreads < n) n = thr_sm / kWgThreads;
+  return n;
+}
+
+// One wave of CTAs: tiles * splits <= SMs * resident CTAs per SM, so that no CTA waits for a slot.
+static int wgrad_plan(const hyc_packed* saved, int rank, WgradPlan* pl) {
+  const int D = saved->cols, bits = saved->bits, nseg = 8 / bits;
+  const int tiles = D * bits / 8 / kTileM;
+  pl->npad = (rank + 15) / 16 * 16;
+  uint32_t cols = 32;
+  while (cols < static_cast<uint32_t>(nseg * pl->npad)) cols *= 2;
+  pl->tmem_cols = cols;
+  const uint32_t b_stage = (kChunk / 8) * (pl->npad / 8) * 128u;
+  const uint32_t nb = (bits < 8 && saved->group) ? nseg : 1u;
+  pl->smem_bytes = 1024 + 2u * nseg * kAStage + 2u * nb * b_stage;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  long long splits = (2 * sms + tiles - 1) / tiles;  // two CTAs per SM
-  const long long max_splits = (rows + kChunk - 1) / kChunk;
+  // the device queries are cached per (device, bits, shared-memory size)
+  struct Known { int dev, bits, per_sm; uint32_t smem; };
+  static Known known[32];
+  static int n_known = 0;
+  static std::mutex mu;
+  int per_sm = -1;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < n_known; ++i)
+      if (known[i].dev == dev && known[i].bits == bits && known[i].smem == pl->smem_bytes) per_sm = known[i].per_sm;
+    if (per_sm < 0) {
+      per_sm = bits == 2 ? wgrad_ctas_per_sm<2>(pl->smem_bytes, dev)
+               : bits == 4 ? wgrad_ctas_per_sm<4>(pl->smem_bytes, dev) : wgrad_ctas_per_sm<8>(pl->smem_bytes, dev);
+      if (per_sm >= 1 && n_known < 32) known[n_known++] = Known{dev, bits, per_sm, pl->smem_bytes};
+    }
+  }
+  if (per_sm < 1) return HYC_ERR_CUDA;
+  // tensor memory: 512 columns per SM shared by the resident CTAs
+  if (per_sm * cols > 512u) per_sm = 512 / cols;
+  long long splits = static_cast<long long>(sms) * per_sm / tiles;
+  const long long max_splits = (saved->rows + kChunk - 1) / kChunk;
   if (splits > max_splits) splits = max_splits;
-  if (splits < 1) splits = 1;
   if (splits > 64) splits = 64;
-  return static_cast<int>(splits);
+  if (splits < 1) splits = 1;
+  pl->splits = static_cast<int>(splits);
+  pl->side_slices = 0;
+  pl->side_rows_per = 0;
+  if (saved->n_channels > 0) {
+    // about two CTAs per SM, slices a multiple of the chunk
+    long long per = (saved->rows + 2 * sms - 1) / (2 * sms);
+    per = (per + kSideChunk - 1) / kSideChunk * kSideChunk;
+    pl->side_rows_per = per;
+    pl->side_slices = static_cast<int>((saved->rows + per - 1) / per);
+  }
+  pl->scratch_floats = static_cast<long long>(pl->splits) * rank * D +
+                       static_cast<long long>(pl->side_slices) * saved->n_channels * rank;
+  return HYC_OK;
 }
 
-}  // namespace hyc
-
-using namespace hyc;
-
-extern "C" {
-
-int hyc_lora_wgrad_splits(int64_t rows, int32_t cols, int32_t bits) {
-  if (rows < 0 || cols <= 0 || (bits != 2 && bits != 4 && bits != 8)) return HYC_ERR_SHAPE;
-  return wgrad_splits(rows, cols, bits);
-}
-
-int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, float* out, float* partials,
-                   void* stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!saved || !saved->codes || !grad || !out || !partials) return HYC_ERR_NULL;
+static int wgrad_check(const hyc_packed* saved, int rank) {
+  if (!saved) return HYC_ERR_NULL;
   if (saved->mode != HYC_MODE_N) return HYC_ERR_MODE;
   if (saved->bits != 2 && saved->bits != 4 && saved->bits != 8) return HYC_ERR_BITS;
   const int D = saved->cols;
@@ -335,15 +537,46 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
       saved->rotate != 1024 && saved->rotate != 4096)
     return HYC_ERR_SHAPE;
   if (saved->rotate && D % saved->rotate != 0) return HYC_ERR_SHAPE;
-  if (!saved->scales) return HYC_ERR_NULL;
-  if ((reinterpret_cast<uintptr_t>(grad) & 15u) || (reinterpret_cast<uintptr_t>(saved->codes) & 15u)) return HYC_ERR_ALIGN;
+  if (saved->n_channels < 0 || saved->n_channels > D) return HYC_ERR_SHAPE;
+  if (static_cast<long long>(saved->n_channels) * (rank >> 3) > 2048) return HYC_ERR_SHAPE;   // outlier-column kernel: 4 units x 512 threads
+  return HYC_OK;
+}
+
+}  // namespace hyc
+
+using namespace hyc;
+
+extern "C" {
+
+int64_t hyc_lora_wgrad_scratch_floats(const hyc_packed* saved, int32_t rank) {
+  const int rc = wgrad_check(saved, rank);
+  if (rc != HYC_OK) return rc;
+  WgradPlan pl;
+  const int rp = wgrad_plan(saved, rank, &pl);
+  if (rp != HYC_OK) return rp;
+  return pl.scratch_floats > 0 ? pl.scratch_floats : 1;
+}
+
+int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, float* out, float* partials,
+                   void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int rc = wgrad_check(saved, rank);
+  if (rc != HYC_OK) return rc;
+  if (!saved->codes || !grad || !out || !partials || !saved->scales) return HYC_ERR_NULL;
+  if (saved->n_channels > 0 && (!saved->channels || !saved->out_value)) return HYC_ERR_NULL;
+  const int D = saved->cols;
+  if ((reinterpret_cast<uintptr_t>(grad) & 15u) || (reinterpret_cast<uintptr_t>(saved->codes) & 15u) ||
+      (reinterpret_cast<uintptr_t>(partials) & 15u))
+    return HYC_ERR_ALIGN;
   const long long slab = static_cast<long long>(rank) * D;
   if (saved->rows == 0) {
     if (cudaMemsetAsync(out, 0, slab * sizeof(float), stream) != cudaSuccess) return HYC_ERR_CUDA;
     return HYC_OK;
   }
-  const int nseg = 8 / saved->bits;
-  const int splits = wgrad_splits(saved->rows, D, saved->bits);
+  WgradPlan pl;
+  const int rp = wgrad_plan(saved, rank, &pl);
+  if (rp != HYC_OK) return rp;
+  const int splits = pl.splits;
   WgradArgs a;
   memset(&a, 0, sizeof(a));
   a.p.mode = saved->mode; a.p.bits = saved->bits; a.p.rows = saved->rows; a.p.cols = D; a.p.seq = saved->seq;
@@ -353,15 +586,12 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
   a.p.scales = saved->scales;
   a.grad = static_cast<const __nv_bfloat16*>(grad);
   a.rank = rank;
-  a.npad = (rank + 15) / 16 * 16;
+  a.npad = pl.npad;
   const long long per = (saved->rows + splits - 1) / splits;
   a.tokens_per_split = (per + kChunk - 1) / kChunk * kChunk;
   a.partials = partials;
-  uint32_t cols = 32;
-  while (cols < static_cast<uint32_t>(nseg * a.npad)) cols *= 2;
-  a.tmem_cols = cols;
-  const uint32_t b_stage = (kChunk / 8) * (a.npad / 8) * 128u;
-  const uint32_t smem_bytes = 1024 + 2u * nseg * kAStage + 2u * b_stage;
+  a.tmem_cols = pl.tmem_cols;
+  const uint32_t smem_bytes = pl.smem_bytes;
   const dim3 grid(D * saved->bits / 8 / kTileM, splits);
 #define HYC_WG(B)                                                                                         \
   {                                                                                                       \
@@ -380,6 +610,21 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
     if (sm > 48 * 1024)
       cudaFuncSetAttribute(wgrad_rotate_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     wgrad_rotate_rows_kernel<<<rank, 256, sm, stream>>>(out, D, saved->rotate);
+  }
+  if (pl.side_slices > 0) {
+    const int k = saved->n_channels;
+    float* side = partials + static_cast<long long>(splits) * slab;
+    const int units = k * (rank >> 3);
+    const int own = (units + 511) / 512;                 // units per thread, at most 4 (wgrad_check)
+    const int threads = ((units + own - 1) / own + 31) / 32 * 32;
+    const size_t sm = static_cast<size_t>(kSideChunk) * (rank + k) * 2 + 16;
+    if (sm > 48 * 1024)
+      if (cudaFuncSetAttribute(wgrad_side_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
+        return HYC_ERR_CUDA;
+    wgrad_side_kernel<<<pl.side_slices, threads, sm, stream>>>(static_cast<const __nv_bfloat16*>(saved->out_value), a.grad,
+                                                               saved->rows, pl.side_rows_per, k, rank, side);
+    wgrad_side_scatter_kernel<<<(k * rank + 255) / 256, 256, 0, stream>>>(side, pl.side_slices, saved->channels, k, rank,
+                                                                          D, out);
   }
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }

@@ -341,16 +341,17 @@ def select_channels(score: torch.Tensor, k: int) -> torch.Tensor:
 
 def lora_wgrad_supported(p: Packed, rank: int) -> bool:
     """Formats the tensor-core weight-gradient kernel takes."""
+    k = 0 if p.channels is None else p.channels.numel()
     return (p.mode == "N" and rank % 8 == 0 and 8 <= rank <= 64 and (p.cols * p.bits // 8) % 128 == 0
-            and p.rows > 0)
+            and p.rows > 0 and k * (rank // 8) <= 2048)
 
 
 def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False) -> torch.Tensor:
     """``dW[r, D] = sum_t G[t, r] * X_hat[t, d]`` in fp32 from the packed input.
 
     Channel-mode activations go to the dequant-fused tcgen05 kernel (the
-    reconstruction never touches HBM); the outlier channels' columns are the
-    skinny product ``G^T @ out_value``.  Other formats are rebuilt by the
+    reconstruction never touches HBM); the outlier channels' columns, the
+    skinny product ``G^T @ out_value``, come from a second kernel of the same call.  Other formats are rebuilt by the
     decompress kernel and contracted by a library GEMM in bf16 with fp32
     accumulation -- the arithmetic of the reference (efficient_linear.py:61-67)
     followed by the autograd engine's sum over the batch."""
@@ -360,14 +361,13 @@ def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False
     if force_library or not lora_wgrad_supported(p, rank):
         xh = decompress(p).reshape(p.rows, p.cols)
         return (g.t() @ xh).float()
-    splits = lib.hyc_lora_wgrad_splits(p.rows, p.cols, p.bits)
-    out = torch.empty((rank, p.cols), dtype=torch.float32, device=g.device)
-    partials = torch.empty(splits * rank * p.cols, dtype=torch.float32, device=g.device)
     rec = p.record()
+    need = lib.hyc_lora_wgrad_scratch_floats(C.byref(rec), rank)
+    if need < 0:
+        check(int(need), "hyc_lora_wgrad_scratch_floats")
+    out = torch.empty((rank, p.cols), dtype=torch.float32, device=g.device)
+    partials = torch.empty(need, dtype=torch.float32, device=g.device)
     check(lib.hyc_lora_wgrad(C.byref(rec), _ptr(g), rank, _ptr(out), _ptr(partials), _stream()), "hyc_lora_wgrad")
-    if p.channels is not None and p.channels.numel():
-        side = (g.t() @ p.out_value).float()
-        out.index_copy_(1, p.channels.long(), side)
     return out
 
 

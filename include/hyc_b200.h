@@ -193,12 +193,12 @@ int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* ch
  *     out[n, d] = sum_t grad[t, n] * X_hat[t, d],   fp32 [rank, cols].
  * Replaces the decompress + batched GEMM + batch sum of efficient_linear.py:61,66-67 without
  * writing X_hat to memory.  grad is bf16 [rows, rank] (contiguous, 16-byte aligned), rank a
- * multiple of 8 in [8, 64]; cols*bits/8 must be a multiple of 128.  `partials` is scratch of
- * hyc_lora_wgrad_splits(rows, cols, bits) * rank * cols floats.  The columns of the outlier
- * channels are NOT filled in by this call (their codes are the zero code): the caller sets
- * out[:, channels] = grad^T * out_value (a [rank, k] product).  With rotation the result
- * already includes the inverse rotation. */
-int hyc_lora_wgrad_splits(int64_t rows, int32_t cols, int32_t bits);
+ * multiple of 8 in [8, 64]; cols*bits/8 must be a multiple of 128.  `partials` is 16-byte aligned
+ * scratch of hyc_lora_wgrad_scratch_floats(saved, rank) floats (a negative return is a hyc_status).
+ * The columns of the outlier channels are out[:, channels] = grad^T * out_value, computed by a
+ * second pair of kernels in the same call; with rotation the result already includes the inverse
+ * rotation.  The sums are taken in a fixed order (no atomics): the result is reproducible. */
+int64_t hyc_lora_wgrad_scratch_floats(const hyc_packed* saved, int32_t rank);
 int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, float* out, float* partials, void* stream);
 
 /* Thresholded ("sparse") copy of attention probabilities, rows x cols with cols <= 65535.
