@@ -26,7 +26,7 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
   fill_req_packed(&req, out, true);
   req.slot_bytes = static_cast<uint32_t>(out->cols) * es;
   if (fast.ok) {
-    req.rot = fast.rot;
+    req.rot = fast.rot == 1;
     req.osm = true;
     req.wsm = norm != nullptr;
     req.bsm = norm != nullptr && norm->kind == HYC_NORM_LAYER;
@@ -34,7 +34,8 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
   LaunchPlan plan;
   // the register-resident kernel frees a slot right after pass 1: two stages suffice and
   // leave room for more resident CTAs
-  rc = plan_launch(req, out->rows, &plan, 0, fast.ok ? fast.threads : 0, fast.ok ? 2 : 3);
+  // (three when the norm output re-reads the staged row after the in-register rotation)
+  rc = plan_launch(req, out->rows, &plan, 0, fast.ok ? fast.threads : 0, fast.ok ? ((fast.rot == 2 && norm) ? 3 : 2) : 3);
   if (rc) return rc;
   FwdArgs a;
   memset(&a, 0, sizeof(a));

@@ -11,8 +11,11 @@
 // channels: the streaming pass treats those channels as the zeros their codes
 // encode, and after the barrier the threads that own the outlier list fix the
 // outputs there from the stored bf16 originals (prefetched at the top of the
-// iteration).  The rotation adds a shared-memory hand-over from the unit
-// mapping to the 256-channel chunk mapping, because its butterflies cross lanes.
+// iteration).  Rotation: in the unit mapping a warp holds 256 consecutive
+// channels of every segment, so when the segment width is a multiple of the
+// rotation block the butterflies run in registers on the freshly dequantised
+// values (ROT == 2); otherwise (ROT == 1) the row is handed over through shared
+// memory to a mapping of aligned 256-channel chunks.
 #pragma once
 #include "hyc_fwd_fast.cuh"
 
@@ -72,10 +75,11 @@ struct BwdSmem {
 };
 
 // Per-thread register groups: NR groups of 8 channels; col[r] < 0 marks an idle group.
-template <int BITS, int UPT, bool ROT>
+// ROT: 0 no rotation, 1 rotation through shared memory (chunk mapping), 2 rotation in registers (unit mapping)
+template <int BITS, int UPT, int ROT>
 struct Groups {
   static constexpr int NSEG = 8 / BITS;
-  static constexpr int NR = ROT ? UPT : UPT * NSEG;
+  static constexpr int NR = ROT == 1 ? UPT : UPT * NSEG;
   int col[NR];
   uint32_t mask[2];  // 8 bits per register group: outlier channels inside the group
   // chan: this CTA's shared copy of the ascending outlier channel list
@@ -94,9 +98,9 @@ struct Groups {
     const int segw = D / NSEG, U = segw >> 3;
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
-      const int c = ROT ? (((warp + r * nwarps) << 8) + (lane << 3))
-                        : ((r % NSEG) * segw + ((threadIdx.x + (r / NSEG) * blockDim.x) << 3));
-      const bool ok = ROT ? (c < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
+      const int c = ROT == 1 ? (((warp + r * nwarps) << 8) + (lane << 3))
+                             : ((r % NSEG) * segw + ((threadIdx.x + (r / NSEG) * blockDim.x) << 3));
+      const bool ok = ROT == 1 ? (c < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
       col[r] = ok ? c : -1;
     }
   }
@@ -105,9 +109,9 @@ struct Groups {
 // Rebuild this thread's slice of a row from its packed bytes `codes_row` (staged in shared
 // memory).  Outlier channels come out as the zero their code encodes (ROT: see ZERO).
 // ROUND: values are rounded to bf16 (what a reconstruction holds); without it the caller
-// rounds when it packs its output.  ROT: goes through w_rot (shared, fp32 [D]) and contains
-// two CTA barriers.
-template <int BITS, int UPT, bool ROT, bool ROUND, bool ZERO = false>
+// rounds when it packs its output.  ROT == 1: goes through w_rot (shared, fp32 [D]) and contains
+// two CTA barriers.  ROT == 2: every warp executes the shuffles, idle groups carry zeros.
+template <int BITS, int UPT, int ROT, bool ROUND, bool ZERO = false>
 __device__ __forceinline__ void rebuild_row(const PackedDev& p, const Groups<BITS, UPT, ROT>& g, float* w_rot,
                                             const unsigned char* codes_row, long long row,
                                             float (&f)[Groups<BITS, UPT, ROT>::NR][8]) {
@@ -117,7 +121,8 @@ __device__ __forceinline__ void rebuild_row(const PackedDev& p, const Groups<BIT
   const int G = p.group ? (D >> 7) : 1;
   const float* sc_row = p.scales + row * G;
   const float sc_tok = p.group ? 0.f : __ldg(sc_row);
-  if (!ROT) {
+  if (ROT != 1) {
+    const int lane = threadIdx.x & 31;
 #pragma unroll
     for (int iu = 0; iu < UPT; ++iu) {
       if (g.col[iu * NSEG] >= 0) {
@@ -127,7 +132,24 @@ __device__ __forceinline__ void rebuild_row(const PackedDev& p, const Groups<BIT
         for (int s = 0; s < NSEG; ++s) {
           const float sc = p.group ? __ldg(sc_row + (g.col[iu * NSEG + s] >> 7)) : sc_tok;
           dequant8<BITS>(cb, s, sc, f[iu * NSEG + s]);
-          if (ROUND) round_bf16x8(f[iu * NSEG + s]);
+          if (ROUND && ROT == 0) round_bf16x8(f[iu * NSEG + s]);
+        }
+      } else if (ROT == 2) {
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[iu * NSEG + s][e] = 0.f;
+      }
+      if (ROT == 2) {
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+          const int r = iu * NSEG + s;
+          rotate_group(f[r], p.rotate, lane);
+          if (ROUND) round_bf16x8(f[r]);
+          if (ZERO) {
+            const uint32_t m = g.group_mask(r);
+            if (m) zero_masked(f[r], m);
+          }
         }
       }
     }
@@ -253,7 +275,7 @@ struct DecFastArgs {
   BwdSmem L;
 };
 
-template <int BITS, int UPT, bool ROT>
+template <int BITS, int UPT, int ROT>
 __global__ void __launch_bounds__(512, 2) decompress_n_fast_kernel(const __grid_constant__ DecFastArgs a) {
   constexpr int NR = Groups<BITS, UPT, ROT>::NR;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -325,7 +347,7 @@ __device__ __forceinline__ float gelu_tanh_grad_f(float x) {
   return 0.5f * ((1.f + t) + x * ((1.f - t * t) * gamma * (1.f + 3.f * kappa * x * x)));
 }
 
-template <int BITS, int UPT, bool ROT, typename GT, int OP>
+template <int BITS, int UPT, int ROT, typename GT, int OP>
 __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_constant__ ActFastArgs a) {
   constexpr int NR = Groups<BITS, UPT, ROT>::NR;
   constexpr bool PROD = OP == HYC_ACT_PRODUCT;
@@ -429,7 +451,7 @@ struct NormBwdFastArgs {
   BwdSmem L;
 };
 
-template <int BITS, int UPT, bool ROT, typename GT>
+template <int BITS, int UPT, int ROT, typename GT>
 __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_constant__ NormBwdFastArgs a) {
   constexpr int NR = Groups<BITS, UPT, ROT>::NR;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -456,7 +478,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
   Groups<BITS, UPT, ROT> g;
   g.init(D);
   __syncthreads();
-  if (ROT) g.init_masks(fs.chan, k);
+  if (ROT != 0) g.init_masks(fs.chan, k);
   const float inv_d = 1.0f / static_cast<float>(D);
   const long long rows = p.rows, stride = gridDim.x;
   long long row = blockIdx.x;
@@ -575,7 +597,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
 struct BwdPlan {
   bool ok;
   int threads, upt, grid;
-  bool rot;
+  int rot;   // 0 none, 1 through shared memory, 2 in registers
   BwdSmem L;
 };
 
@@ -588,11 +610,12 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
   memset(&b, 0, sizeof(b));
   if (q->mode != HYC_MODE_N || q->rotate > 256) return b;
   const int D = q->cols, nseg = 8 / q->bits;
-  b.rot = q->rotate != 0;
+  // rotation in registers needs every segment to start on a rotation-block boundary
+  b.rot = q->rotate == 0 ? 0 : ((D / nseg) % q->rotate == 0 ? 2 : 1);
   int threads = g_tune_threads ? g_tune_threads : (D <= 1024 ? 64 : D <= 4096 ? 128 : 256);
   // kernels that hold two operands per element in registers run better with fewer elements per thread
   if (!g_tune_threads && min_threads && threads < min_threads && D >= 8 * min_threads) threads = min_threads;
-  if (b.rot) {
+  if (b.rot == 1) {
     const int chunks = (D + 255) / 256;
     for (; threads <= max_threads; threads *= 2) {
       const int cpt = (chunks + threads / 32 - 1) / (threads / 32);
@@ -600,6 +623,8 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
     }
   } else {
     const int U = D / nseg / 8;
+    // a thread owns whole units: more threads than units would idle
+    while (threads > 32 && threads / 2 >= U) threads /= 2;
     for (; threads <= max_threads; threads *= 2) {
       const int upt = (U + threads - 1) / threads;
       if (upt * nseg <= reg_groups) { b.ok = true; b.threads = threads; b.upt = upt; break; }
@@ -615,7 +640,7 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
   b.L.off_misc = take(16);
   b.L.off_chan = take((q->n_channels > 0 ? q->n_channels : 1) * 4);
   b.L.off_chan2 = take(((q2 && q2->n_channels > 0) ? q2->n_channels : 1) * 4);
-  if (b.rot) b.L.off_rot = take(D * 4);
+  if (b.rot == 1) b.L.off_rot = take(D * 4);
   if (want_w) b.L.off_wsm = take(D * 4);
   if (acc_rows) b.L.off_acc = take(static_cast<uint32_t>(acc_rows) * D * 4);
   off = align_up(off, 128);
@@ -651,10 +676,12 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
   }
 #define HYC_BWD_UPT(PLAN, B, UP, CAP, LAUNCH)                                                  \
   if ((PLAN).upt == UP) {                                                                      \
-    if ((PLAN).rot) {                                                                          \
-      if constexpr (UP <= CAP) { LAUNCH(B, UP, true) done__ = true; }                          \
+    if ((PLAN).rot == 1) {                                                                     \
+      if constexpr (UP <= CAP) { LAUNCH(B, UP, 1) done__ = true; }                             \
+    } else if ((PLAN).rot == 2) {                                                              \
+      if constexpr (UP * (8 / B) <= CAP) { LAUNCH(B, UP, 2) done__ = true; }                   \
     } else {                                                                                   \
-      if constexpr (UP * (8 / B) <= CAP) { LAUNCH(B, UP, false) done__ = true; }               \
+      if constexpr (UP * (8 / B) <= CAP) { LAUNCH(B, UP, 0) done__ = true; }                   \
     }                                                                                          \
   }
 

@@ -15,9 +15,14 @@
 // mantissa bits and is merged into the packed word with one shift-add, the
 // constant's exponent bits being cancelled once per word.
 //
-// With rotation (block size <= 256) pass 1 runs in the chunk mapping of
-// fwht_row (lane l holds channels 8l..8l+7 of a 256-channel chunk), writes the
-// rotated fp32 row to shared memory and pass 2 packs from there.
+// Rotation (block size <= 256).  In the unit mapping a warp already holds 256
+// consecutive channels of every segment, so when the segment width is a multiple of
+// the rotation block (ROT == 2) the butterflies run in place on the registers of
+// pass 1 and pass 2 packs from them; the norm output then re-reads the staged row,
+// which therefore stays one row longer in its slot.  Otherwise (ROT == 1) pass 1 runs
+// in the chunk mapping of fwht_row (lane l holds channels 8l..8l+7 of an aligned
+// 256-channel chunk), writes the rotated fp32 row to shared memory and pass 2 packs
+// from there.
 #pragma once
 #include "hyc_fwd.cuh"
 
@@ -127,7 +132,7 @@ __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-// UPT: units per thread (ROT: 256-channel chunks per warp)
+// UPT: units per thread (ROT == 1: 256-channel chunks per warp)
 //
 // Per row i:   pass 1 (registers <- staged row i, statistics)
 //              wait for row i+1, save + zero its outlier channels
@@ -137,11 +142,12 @@ __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { re
 // The norm output of an outlier channel is computed from the saved original by the thread
 // that saved it and stored one barrier after the vector stores of the row, which orders the
 // two stores to the same address.
-template <typename XT, int BITS, bool NORM, int UPT, bool ROT>
+template <typename XT, int BITS, bool NORM, int UPT, int ROT>
 __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constant__ FwdArgs a) {
   using C = CodeTraits<BITS>;
   constexpr int NSEG = C::kSeg;
-  constexpr int NR = ROT ? UPT : UPT * NSEG;
+  constexpr int NR = ROT == 1 ? UPT : UPT * NSEG;
+  constexpr bool kLateRefill = ROT == 2 && NORM;   // pass 2 re-reads the staged row
   extern __shared__ __align__(128) unsigned char smem[];
   const PackedDev& p = a.p;
   const int D = p.cols;
@@ -200,9 +206,9 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
       float s1 = 0.f, dummy = 0.f;
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
-        const int col = ROT ? (((warp + r * nwarps) << 8) + (lane << 3))
+        const int col = ROT == 1 ? (((warp + r * nwarps) << 8) + (lane << 3))
                             : ((r % NSEG) * segw + ((threadIdx.x + (r / NSEG) * blockDim.x) << 3));
-        const bool ok = ROT ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
+        const bool ok = ROT == 1 ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
         if (ok) {
           load8<XT>(xs, col, f[r]);
 #pragma unroll
@@ -216,9 +222,9 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     float ss = 0.f, amax = 0.f;
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
-      const int col = ROT ? (((warp + r * nwarps) << 8) + (lane << 3))
+      const int col = ROT == 1 ? (((warp + r * nwarps) << 8) + (lane << 3))
                           : ((r % NSEG) * segw + ((threadIdx.x + (r / NSEG) * blockDim.x) << 3));
-      const bool ok = ROT ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
+      const bool ok = ROT == 1 ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
       float a8 = 0.f;
       if (ok) {
         if (!ln) load8<XT>(xs, col, f[r]);
@@ -231,12 +237,17 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
             for (int e = 0; e < 8; ++e) ss = fmaf(f[r][e], f[r][e], ss);
           }
         }
-        if (!ROT) a8 = absmax8(f[r]);
+        if (ROT == 0) a8 = absmax8(f[r]);
       } else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[r][e] = 0.f;
       }
-      if (ROT) {
+      if (ROT == 2) {
+        // in place: the norm output re-reads the staged row
+        rotate_group(f[r], p.rotate, lane);
+        a8 = absmax8(f[r]);
+      }
+      if (ROT == 1) {
         // rotate a copy; the original stays in f[r] for the norm output
         float t[8];
 #pragma unroll
@@ -282,14 +293,17 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     reduce_sum_max(ss, amax, w.red + par * 64);
     if (w.misc[2]) {
       if (threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
-      drain_ring(ring, i + 1, row_next + stride, rows, stride);
+      drain_ring(ring, i + 1, row_next + stride, rows, stride, kLateRefill ? ring.stages - 2 : ring.stages - 1);
       return;
     }
     if (threadIdx.x == 0) {
-      const long long next = row + ring.stages * stride;
-      if (next < rows) {
+      // the slot every thread has finished with: this row's, or the previous row's when pass 2 reads it again
+      const long long freed = kLateRefill ? row_prev : row;
+      const int slot_free = kLateRefill ? (i + ring.stages - 1) % ring.stages : st;
+      const long long next = freed + ring.stages * stride;
+      if (freed >= 0 && next < rows) {
         fence_proxy_async();
-        issue_x_row<XT>(a, ring, st, next);
+        issue_x_row<XT>(a, ring, slot_free, next);
       }
     }
     // ---- norm output of the previous row at its outlier channels
@@ -322,26 +336,33 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     if (NORM) {
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
-        const int col = ROT ? (((warp + r * nwarps) << 8) + (lane << 3))
+        const int col = ROT == 1 ? (((warp + r * nwarps) << 8) + (lane << 3))
                             : ((r % NSEG) * segw + ((threadIdx.x + (r / NSEG) * blockDim.x) << 3));
-        const bool ok = ROT ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
+        const bool ok = ROT == 1 ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
         if (ok) {
           float y[8], wv[8];
           load8<float>(wsm, col, wv);
+          float xv[8];
+          if (ROT == 2) {
+            load8<XT>(xs, col, xv);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) xv[e] = f[r][e];
+          }
           if (ln) {
             float bv[8];
             load8<float>(bsm, col, bv);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) y[e] = (f[r][e] - mean) * rstd * wv[e] + bv[e];
+            for (int e = 0; e < 8; ++e) y[e] = (xv[e] - mean) * rstd * wv[e] + bv[e];
           } else {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) y[e] = f[r][e] * rstd * wv[e];
+            for (int e = 0; e < 8; ++e) y[e] = xv[e] * rstd * wv[e];
           }
           store8<XT>(yrow, col, y);
         }
       }
     }
-    if (!ROT) {
+    if (ROT != 1) {
 #pragma unroll
       for (int iu = 0; iu < UPT; ++iu) {
         const int u = threadIdx.x + iu * blockDim.x;
@@ -404,20 +425,22 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
 struct FastPlan {
   bool ok;
   int threads, upt;
-  bool rot;
+  int rot;   // 0 none, 1 through shared memory (chunk mapping), 2 in registers (unit mapping)
 };
 
 // The fast kernel takes the channel-outlier mode with no rotation or a rotation block <= 256;
 // group scales need 128-channel groups that do not straddle segments.
 inline FastPlan plan_fast(const hyc_packed* q, int elem_size) {
-  FastPlan f{false, 0, 0, false};
+  FastPlan f{false, 0, 0, 0};
   if (q->mode != HYC_MODE_N) return f;
   const int D = q->cols, nseg = 8 / q->bits;
   if (q->rotate > 256) return f;
-  f.rot = q->rotate != 0;
+  // rotation in registers needs every segment to start on a rotation-block boundary
+  f.rot = q->rotate == 0 ? 0 : 1;
+  if (q->rotate && (D / nseg) % q->rotate == 0 && !(q->group && (D / nseg) % 128 != 0)) f.rot = 2;
   const int reg_cap = elem_size == 2 ? 8 : 4;  // 8-element register groups per thread
   int threads = g_tune_threads ? g_tune_threads : (D <= 1024 ? 64 : D <= 4096 ? 128 : 256);
-  if (f.rot) {
+  if (f.rot == 1) {
     const int chunks = (D + 255) / 256;
     for (; threads <= 256; threads *= 2) {
       const int cpt = (chunks + threads / 32 - 1) / (threads / 32);
@@ -426,6 +449,7 @@ inline FastPlan plan_fast(const hyc_packed* q, int elem_size) {
   } else {
     if (q->group && (D / nseg) % 128 != 0) return f;
     const int U = D / nseg / 8;
+    while (threads > 32 && threads / 2 >= U) threads /= 2;   // a thread owns whole units
     for (; threads <= 256; threads *= 2) {
       const int upt = (U + threads - 1) / threads;
       if (upt * nseg <= reg_cap) { f.ok = true; f.threads = threads; f.upt = upt; break; }
@@ -445,7 +469,7 @@ static int launch_fwd_fast(const FwdArgs& a, const LaunchPlan& plan, const FastP
   // register groups per thread are capped by plan_fast; larger combinations are never instantiated
 #define HYC_FAST_LAUNCH(BITS, UPT, ROT)                                     \
   {                                                                         \
-    if constexpr ((ROT ? UPT : UPT * (8 / BITS)) <= (sizeof(XT) == 2 ? 8 : 4)) { \
+    if constexpr ((ROT == 1 ? UPT : UPT * (8 / BITS)) <= (sizeof(XT) == 2 ? 8 : 4)) { \
       auto kern = fwd_n_fast_kernel<XT, BITS, NORM, UPT, ROT>;              \
       int rc = set_smem(kern, plan.L.total);                                \
       if (rc) return rc;                                                    \
@@ -467,7 +491,7 @@ static int launch_fwd_fast(const FwdArgs& a, const LaunchPlan& plan, const FastP
     case 4: HYC_FAST_UPT(4, ROT) break;                                     \
     default: HYC_FAST_UPT(8, ROT) break;                                    \
   }
-  if (f.rot) { HYC_FAST_BITS(true) } else { HYC_FAST_BITS(false) }
+  if (f.rot == 1) { HYC_FAST_BITS(1) } else if (f.rot == 2) { HYC_FAST_BITS(2) } else { HYC_FAST_BITS(0) }
 #undef HYC_FAST_BITS
 #undef HYC_FAST_UPT
 #undef HYC_FAST_LAUNCH

@@ -168,9 +168,11 @@ __device__ inline void setup_packed(const PackedDev& p, const Work& w) {
 }
 
 // after an expired wait: give this CTA's other copies a bounded chance to land
-__device__ inline void drain_ring(RowRing& ring, int i_done, long long next_row, long long rows, long long stride) {
+__device__ inline void drain_ring(RowRing& ring, int i_done, long long next_row, long long rows, long long stride,
+                                  int in_flight = -1) {
   if (threadIdx.x != 0) return;
-  for (int s = 1; s < ring.stages; ++s) {
+  const int last = in_flight < 0 ? ring.stages - 1 : in_flight;
+  for (int s = 1; s <= last; ++s) {
     const int i = i_done + s;
     if (next_row + static_cast<long long>(s - 1) * stride >= rows) break;
     (void)mbar_wait_bounded(&ring.bars[i % ring.stages], (i / ring.stages) & 1);

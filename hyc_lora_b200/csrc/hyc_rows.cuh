@@ -96,6 +96,24 @@ __device__ __forceinline__ void butterfly8(float (&f)[8]) {
   for (int i = 0; i < 4; ++i) { t = f[i]; f[i] = t + f[i + 4]; f[i + 4] = t - f[i + 4]; }
 }
 
+// Rotation of the 8 values a lane holds of a 256-channel window (lane l: channels 8l..8l+7),
+// block size n <= 256: three butterfly stages inside the thread, then one shuffle stage per
+// doubling, then the normalisation.  Every lane of the warp must call it.
+__device__ __forceinline__ void rotate_group(float (&f)[8], int n, int lane) {
+  butterfly8(f);
+#pragma unroll
+  for (int m2 = 1; m2 <= 16; m2 <<= 1) {
+    if ((m2 << 3) < n) {
+      const float sgn = (lane & m2) ? -1.f : 1.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = __fmaf_rn(sgn, f[e], __shfl_xor_sync(0xffffffffu, f[e], m2));
+    }
+  }
+  const float rs = rotate_norm(n);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) f[e] *= rs;
+}
+
 // Normalised Walsh-Hadamard transform of every aligned block of n channels of
 // the row `src` (masked outlier channels read as 0), result in `rot` (fp32).
 // src may alias rot.  Lane l of a warp holds channels 8l..8l+7 of a 256-channel

@@ -152,6 +152,9 @@ N_CASES = [
     (20, 14336, torch.bfloat16, 2, 128, 0, 0.02),
     (1, 4096, torch.bfloat16, 4, 0, 0, 0.01),
     (2000, 4096, torch.bfloat16, 4, 0, 256, 0.01),
+    # rotation in registers with a half-filled last warp (segments of 384 channels, blocks of 64)
+    (37, 768, torch.bfloat16, 4, 0, 64, 0.01),
+    (50, 4096, torch.bfloat16, 4, 128, 256, 0.01),
 ]
 
 
@@ -206,17 +209,21 @@ def test_n_mode_ties_zero_rows_and_nonfinite_values(pk):
 
 # ------------------------------------------------------------------ fused norm forward
 
-@pytest.mark.parametrize("kind,dtype,d", [("rms", torch.bfloat16, 4096), ("rms_gemma", torch.bfloat16, 1024),
-                                          ("ln", torch.float32, 768), ("ln", torch.bfloat16, 3072),
-                                          ("rms", torch.float32, 768), ("rms", torch.bfloat16, 11008)])
-def test_norm_forward_matches_oracle(pk, kind, dtype, d):
-    rows = 45
+@pytest.mark.parametrize("kind,dtype,d,rotate,rows", [
+    ("rms", torch.bfloat16, 4096, 0, 45), ("rms_gemma", torch.bfloat16, 1024, 0, 45),
+    ("ln", torch.float32, 768, 0, 45), ("ln", torch.bfloat16, 3072, 0, 45),
+    ("rms", torch.float32, 768, 0, 45), ("rms", torch.bfloat16, 11008, 0, 45),
+    # rotation in registers (the norm output re-reads the staged row), several rows per CTA
+    ("rms", torch.bfloat16, 4096, 256, 3001), ("ln", torch.bfloat16, 768, 64, 5003),
+    # rotation through shared memory (segments not aligned to the block)
+    ("rms", torch.bfloat16, 11008, 256, 45)])
+def test_norm_forward_matches_oracle(pk, kind, dtype, d, rotate, rows):
     x, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=dtype, salt=d)
     w = synthetic.norm_weight(d, 0.1, dtype=dtype)
     b = (0.05 * torch.randn(d, generator=torch.Generator().manual_seed(d))).to(dtype)
     k = oc.n_outlier_count(d, 0.01)
     ch = oc.n_select_channels(oc.n_channel_scores(x), k)
-    p, y, rstd, mean = pk.compress_n(x.to(DEV), ch.to(DEV), 4, 0, 0,
+    p, y, rstd, mean = pk.compress_n(x.to(DEV), ch.to(DEV), 4, 0, rotate,
                                      norm=dict(kind=kind, weight=w.to(DEV), bias=b.to(DEV), eps=1e-5))
     y_o, mean_o, rstd_o = oc.norm_forward(x, w, b, 1e-5, kind)
     assert y.dtype == x.dtype and y.shape == x.shape
@@ -227,8 +234,9 @@ def test_norm_forward_matches_oracle(pk, kind, dtype, d):
     if kind == "ln":
         assert (mean.cpu() - mean_o).abs().max() < 1e-4 * x.float().abs().max()
     # the compressed copy is of the norm INPUT and is bit-exact
-    c = oc.n_compress(x, ch, 4, 0, 0)
+    c = oc.n_compress(x, ch, 4, 0, rotate)
     assert torch.equal(p.codes.cpu(), c.codes) and torch.equal(p.scales.cpu(), c.scales)
+    assert not p.wait_expired()
 
 
 # ------------------------------------------------------------------ backward kernels
