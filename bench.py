@@ -323,18 +323,20 @@ def run_ours(args):
                        "algorithmic_bytes_per_row": bytes_per_step // ROWS},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": committed_traffic(), "peak_source": f"of {which}",
-                         "kernel": "hyc::fwd_kernel<bf16, N, 4, norm>"},
+                         "kernel": "hyc::fwd_n_fast_kernel<bf16, 4, norm, 2, 0>"},
             "e2e": {"value": (bytes_per_step * e2e_steps * world) / (e2e_ms / 1e3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "pipeline": "8 pieces of 8192 rows; H2D, kernel and D2H on three streams"},
             "gpu_launches": args.steps,
             "clocks": clocks,
         }
-        # bounded CPU sample of the same workload (about 10-20 s)
-        nbytes, times, cores = cpu_arm(2048, 5)
-        line["cpu_baseline"] = {"value": nbytes / statistics.median(times) / 1e9, "unit": "GB/s", "cores": cores,
-                                "kind": "port", "sample": "2048 of 65536 rows, median of 5 runs, PyTorch CPU port of the "
-                                                          "reference's eager norm + compress chain"}
+        # bounded CPU sample of the same workload (about 10-20 s); single-GPU runs only, so that the
+        # host cores are not shared with other ranks
+        if world == 1:
+            nbytes, times, cores = cpu_arm(2048, 5)
+            line["cpu_baseline"] = {"value": nbytes / statistics.median(times) / 1e9, "unit": "GB/s", "cores": cores,
+                                    "kind": "port", "sample": "2048 of 65536 rows, median of 5 runs, PyTorch CPU port of "
+                                                              "the reference's eager norm + compress chain"}
         if args.sweep:
             line["sweep"] = sweep(packed, synthetic, oc, x, w, peak)
     # free the operator benchmark's buffers before the model is built
@@ -491,8 +493,28 @@ def run_case(args):
     norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
     dy = torch.randn(rows, COLS, device="cuda", dtype=torch.bfloat16)
     rstd = torch.ones(rows, device="cuda")
-    p = packed.compress_n(x, ch, BITS, args.group, args.rotate)
     g64 = torch.randn(rows, 64, device="cuda", dtype=torch.bfloat16)
+    if args.mode == "R":
+        # reference mode: statistics as the reference calibrates them (batch element 0 of a [T/512, 512, D] view)
+        x3 = x.reshape(rows // 512, 512, COLS)
+        thr, _, _, scale = oc.r_calibrate(x3[:1].cpu(), 0.01, 1.0, BITS, "per-channel", 0, 0)
+        thr, scale = thr.cuda(), scale.cuda()
+        p = packed.compress_r(x3, thr, scale, BITS, outlier_ratio=0.01)
+        dy3 = dy.reshape(x3.shape)
+        fns = {
+            "norm_compress": lambda: packed.compress_r(x3, thr, scale, BITS, outlier_ratio=0.01, norm=norm),
+            "compress": lambda: packed.compress_r(x3, thr, scale, BITS, outlier_ratio=0.01),
+            "decompress": lambda: packed.decompress(p),
+            "norm_bwd": lambda: packed.norm_bwd(p, dy3, w, rstd, None, "rms"),
+            "silu_bwd": lambda: packed.act_bwd("silu", p, dy3),
+        }
+        for _ in range(args.launches):
+            fns[args.case]()
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "mode": "R", "rows": rows, "launches": args.launches,
+                          "status": int(p.status.item()), "pool_used": int(p.pool_used.item())}))
+        return
+    p = packed.compress_n(x, ch, BITS, args.group, args.rotate)
     fns = {
         "lora_wgrad": lambda: packed.lora_wgrad(p, g64),
         "norm_compress": lambda: packed.compress_n(x, ch, BITS, args.group, args.rotate, norm=norm),
@@ -523,6 +545,7 @@ def main():
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--group", type=int, default=GROUP)
     ap.add_argument("--rotate", type=int, default=ROTATE)
+    ap.add_argument("--mode", default="N", choices=["N", "R"], help="--case: channel mode (N) or reference mode (R)")
     args = ap.parse_args()
     if args.case:
         run_case(args)

@@ -1,6 +1,6 @@
 // Library-wide state, error strings, tuning knobs and the forward entry points
 // (argument checks + launch planning; the kernels are instantiated elsewhere).
-#include "hyc_fwd_fast.cuh"
+#include "hyc_fwd_r_fast.cuh"
 
 namespace hyc {
 
@@ -21,6 +21,28 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
   }
   if (out->rows == 0) return HYC_OK;
   const int es = x->dtype == HYC_BF16 ? 2 : 4;
+  if (out->mode == HYC_MODE_R) {
+    // register-resident kernel for 2/4/8-bit codes; 1-bit codes and rows too wide for it take the generic kernel
+    const RFastPlan rf = plan_r_fast(out, es, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER);
+    if (rf.ok) {
+      RFastArgs ra;
+      memset(&ra, 0, sizeof(ra));
+      ra.p = to_dev(out);
+      ra.x = static_cast<const unsigned char*>(x->base);
+      ra.row_stride = x->row_stride; ra.batch_stride = x->batch_stride; ra.chunk_stride = x->chunk_stride;
+      ra.chunks = x->chunks;
+      if (norm) {
+        ra.kind = norm->kind; ra.eps = norm->eps; ra.weight = norm->weight; ra.bias = norm->bias;
+        ra.param_bf16 = norm->param_dtype == HYC_BF16;
+        ra.y = norm->y; ra.rstd = norm->rstd; ra.mean = norm->mean;
+      }
+      ra.L = rf.L;
+      cudaError_t e = cudaMemsetAsync(out->pool_used, 0, sizeof(uint32_t), stream);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(pool_used)");
+      return x->dtype == HYC_BF16 ? launch_fwd_r_fast_bf16(ra, rf, norm != nullptr, stream)
+                                  : launch_fwd_r_fast_f32(ra, rf, norm != nullptr, stream);
+    }
+  }
   const FastPlan fast = plan_fast(out, es);
   LayoutReq req;
   fill_req_packed(&req, out, true);
