@@ -16,6 +16,11 @@
 // rotation block the butterflies run in registers on the freshly dequantised
 // values (ROT == 2); otherwise (ROT == 1) the row is handed over through shared
 // memory to a mapping of aligned 256-channel chunks.
+//
+// Reference mode (ROT == 3) uses the same kernels: the row is rebuilt with the reference's bf16
+// rounding points, bf16(bf16(lowrank) + bf16((code - offset) * scale)), element outliers are
+// streamed as the zero their code encodes and fixed after the row's barrier from the row's
+// pool entries (column, bf16 value); the low-rank row travels in the staging slot.
 #pragma once
 #include "hyc_fwd_fast.cuh"
 
@@ -71,11 +76,14 @@ __device__ __forceinline__ void ld_stream8<float>(const float* p, float (&f)[8])
 
 struct BwdSmem {
   uint32_t off_red, off_misc, off_chan, off_chan2, off_rot, off_wsm, off_acc, off_slots, slot_bytes, total;
+  uint32_t off_csc, off_csc2;   // reference mode: per-channel scales (bf16 [D]) of the operands
+  uint32_t off_lr, off_lr2;     // reference mode: low-rank rows inside a staging slot
   int stages;
 };
 
 // Per-thread register groups: NR groups of 8 channels; col[r] < 0 marks an idle group.
-// ROT: 0 no rotation, 1 rotation through shared memory (chunk mapping), 2 rotation in registers (unit mapping)
+// ROT: 0 no rotation, 1 rotation through shared memory (chunk mapping), 2 rotation in registers (unit mapping),
+// 3 reference mode (unit mapping, no rotation)
 template <int BITS, int UPT, int ROT>
 struct Groups {
   static constexpr int NSEG = 8 / BITS;
@@ -111,13 +119,69 @@ struct Groups {
 // ROUND: values are rounded to bf16 (what a reconstruction holds); without it the caller
 // rounds when it packs its output.  ROT == 1: goes through w_rot (shared, fp32 [D]) and contains
 // two CTA barriers.  ROT == 2: every warp executes the shuffles, idle groups carry zeros.
+// what the reference-mode rebuild needs besides the packed bytes
+struct RefCtx {
+  const __nv_bfloat16* csc;   // per-channel scales in shared memory, or nullptr
+  const __nv_bfloat16* lrs;   // low-rank row in the staging slot, or nullptr
+  float sc_row;               // per-tensor / per-token scale
+};
+
+__device__ __forceinline__ RefCtx ref_ctx(const PackedDev& p, const __nv_bfloat16* csc, const unsigned char* slot,
+                                          uint32_t off_lr, long long row) {
+  RefCtx c;
+  c.csc = p.scale_kind == kScaleChannel ? csc : nullptr;
+  c.lrs = p.lowrank ? reinterpret_cast<const __nv_bfloat16*>(slot + off_lr) : nullptr;
+  c.sc_row = p.scale_kind == kScaleTensor ? __bfloat162float(p.scale[0])
+             : p.scale_kind == kScaleToken ? __bfloat162float(p.scale[row % p.seq]) : 1.f;
+  return c;
+}
+
+// reconstruction of one element outlier (pool entry e) the way the reference adds it:
+// bf16(lowrank + value); `lr_row` is the low-rank row in global memory or nullptr
+__device__ __forceinline__ float ref_outlier_value(uint32_t e, const __nv_bfloat16* lr_row) {
+  float val = bf16_bits_to_float(e >> 16);
+  if (lr_row) val = bf16_round(__bfloat162float(lr_row[e & 0xffffu]) + val);
+  return val;
+}
+
 template <int BITS, int UPT, int ROT, bool ROUND, bool ZERO = false>
 __device__ __forceinline__ void rebuild_row(const PackedDev& p, const Groups<BITS, UPT, ROT>& g, float* w_rot,
                                             const unsigned char* codes_row, long long row,
-                                            float (&f)[Groups<BITS, UPT, ROT>::NR][8]) {
+                                            float (&f)[Groups<BITS, UPT, ROT>::NR][8], const RefCtx* rc = nullptr) {
   constexpr int NSEG = 8 / BITS;
   constexpr int NR = Groups<BITS, UPT, ROT>::NR;
   const int D = p.cols;
+  if (ROT == 3) {
+#pragma unroll
+    for (int iu = 0; iu < UPT; ++iu) {
+      if (g.col[iu * NSEG] >= 0) {
+        const uint2 cb = *reinterpret_cast<const uint2*>(codes_row + g.col[iu * NSEG]);
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+          const int r = iu * NSEG + s, col = g.col[r];
+          dequant8<BITS>(cb, s, 1.f, f[r]);          // code - offset
+          float sc[8];
+          if (rc->csc) {
+            load8<__nv_bfloat16>(rc->csc, col, sc);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sc[e] = rc->sc_row;
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[r][e] *= sc[e];
+          round_bf16x8(f[r]);
+          if (rc->lrs) {
+            float l[8];
+            load8<__nv_bfloat16>(rc->lrs, col, l);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[r][e] += l[e];
+            round_bf16x8(f[r]);
+          }
+        }
+      }
+    }
+    return;
+  }
   const int G = p.group ? (D >> 7) : 1;
   const float* sc_row = p.scales + row * G;
   const float sc_tok = p.group ? 0.f : __ldg(sc_row);
@@ -203,16 +267,24 @@ __device__ __forceinline__ void rebuild_row(const PackedDev& p, const Groups<BIT
 // The staging ring of the consumers: `streams` byte ranges per row land in one slot.
 struct RowFeed {
   RowRing ring;
-  uint32_t bytes[3];
-  uint32_t offset[3];
-  const unsigned char* base[3];
+  uint32_t bytes[5];
+  uint32_t offset[5];
+  const unsigned char* base[5];
+  int period[5];   // 0: one source row per row; n: source row = row % n (low-rank rows repeat every sequence)
   int streams;
+  __device__ __forceinline__ void add(const void* src, uint32_t nbytes, uint32_t off, int per = 0) {
+    base[streams] = static_cast<const unsigned char*>(src);
+    bytes[streams] = nbytes; offset[streams] = off; period[streams] = per;
+    ++streams;
+  }
   __device__ __forceinline__ void issue(int stage, long long row) {
     uint32_t total = 0;
     for (int q = 0; q < streams; ++q) total += bytes[q];
     mbar_expect_tx(&ring.bars[stage], total);
-    for (int q = 0; q < streams; ++q)
-      bulk_g2s(ring.slot(stage) + offset[q], base[q] + row * bytes[q], bytes[q], &ring.bars[stage]);
+    for (int q = 0; q < streams; ++q) {
+      const long long src_row = period[q] ? row % period[q] : row;
+      bulk_g2s(ring.slot(stage) + offset[q], base[q] + src_row * bytes[q], bytes[q], &ring.bars[stage]);
+    }
   }
   __device__ __forceinline__ void prologue(long long first, long long rows, long long stride) {
     if (threadIdx.x == 0)
@@ -242,6 +314,7 @@ __device__ __forceinline__ FeedSetup feed_setup(unsigned char* smem, const BwdSm
   FeedSetup s;
   s.feed.ring = RowRing{reinterpret_cast<uint64_t*>(smem), smem + L.off_slots, L.slot_bytes, L.stages};
   s.feed.ring.init();
+  s.feed.streams = 0;
   s.chan = reinterpret_cast<int*>(smem + L.off_chan);
   s.chan2 = reinterpret_cast<int*>(smem + L.off_chan2);
   s.w_rot = reinterpret_cast<float*>(smem + L.off_rot);
@@ -282,11 +355,15 @@ __global__ void __launch_bounds__(512, 2) decompress_n_fast_kernel(const __grid_
   const PackedDev& p = a.p;
   const int D = p.cols, k = p.n_channels;
   FeedSetup fs = feed_setup(smem, a.L);
-  fs.feed.streams = 1;
-  fs.feed.bytes[0] = static_cast<uint32_t>(D) * BITS / 8;
-  fs.feed.offset[0] = 0;
-  fs.feed.base[0] = p.codes;
-  for (int j = threadIdx.x; j < k; j += blockDim.x) fs.chan[j] = max(0, min(D - 1, p.channels[j]));
+  fs.feed.add(p.codes, static_cast<uint32_t>(D) * BITS / 8, 0);
+  if (ROT == 3 && p.lowrank) fs.feed.add(p.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr, p.seq);
+  __nv_bfloat16* csc = reinterpret_cast<__nv_bfloat16*>(smem + a.L.off_csc);
+  if (ROT == 3) {
+    if (p.scale_kind == kScaleChannel)
+      for (int c = threadIdx.x; c < D; c += blockDim.x) csc[c] = p.scale[c];
+  } else {
+    for (int j = threadIdx.x; j < k; j += blockDim.x) fs.chan[j] = max(0, min(D - 1, p.channels[j]));
+  }
   Groups<BITS, UPT, ROT> g;
   g.init(D);
   // output offset of every register group (head layouts cut the row into chunks)
@@ -305,10 +382,19 @@ __global__ void __launch_bounds__(512, 2) decompress_n_fast_kernel(const __grid_
     const int st = i % fs.feed.ring.stages;
     // the outlier values of this row, fetched early by the threads that will store them
     __nv_bfloat16 ov = __float2bfloat16_rn(0.f);
-    if (threadIdx.x < k) ov = p.out_value[row * k + threadIdx.x];
+    uint2 meta = make_uint2(0u, 0u);
+    uint32_t ent = 0;
+    if (ROT == 3) {
+      meta = p.row_meta[row];
+      if (threadIdx.x < meta.y) ent = p.pool[meta.x + threadIdx.x];
+    } else if (threadIdx.x < k) {
+      ov = p.out_value[row * k + threadIdx.x];
+    }
     feed_wait(fs, i);
     float f[NR][8];
-    rebuild_row<BITS, UPT, ROT, false>(p, g, fs.w_rot, fs.feed.ring.slot(st), row, f);
+    RefCtx rc;
+    if (ROT == 3) rc = ref_ctx(p, csc, fs.feed.ring.slot(st), a.L.off_lr, row);
+    rebuild_row<BITS, UPT, ROT, false>(p, g, fs.w_rot, fs.feed.ring.slot(st), row, f, &rc);
     __nv_bfloat16* orow = a.chunks == 1 ? a.out + row * a.row_stride
                                         : a.out + (row / p.seq) * a.batch_stride + (row % p.seq) * a.row_stride;
 #pragma unroll
@@ -317,10 +403,20 @@ __global__ void __launch_bounds__(512, 2) decompress_n_fast_kernel(const __grid_
     __syncthreads();
     if (feed_failed(fs, p.status, i, row, rows, stride)) return;
     fs.feed.refill(st, row, rows, stride);
-    for (int j = threadIdx.x; j < k; j += blockDim.x) {
-      const int cc = fs.chan[j];
-      const int c = cc / clen;
-      orow[c * a.chunk_stride + (cc - c * clen)] = j == threadIdx.x ? ov : p.out_value[row * k + j];
+    if (ROT == 3) {
+      const __nv_bfloat16* lr_row = p.lowrank ? p.lowrank + (row % p.seq) * static_cast<long long>(D) : nullptr;
+      for (uint32_t j = threadIdx.x; j < meta.y; j += blockDim.x) {
+        const uint32_t e = j == threadIdx.x ? ent : p.pool[meta.x + j];
+        const int cc = static_cast<int>(e & 0xffffu);
+        const int c = cc / clen;
+        orow[c * a.chunk_stride + (cc - c * clen)] = __float2bfloat16_rn(ref_outlier_value(e, lr_row));
+      }
+    } else {
+      for (int j = threadIdx.x; j < k; j += blockDim.x) {
+        const int cc = fs.chan[j];
+        const int c = cc / clen;
+        orow[c * a.chunk_stride + (cc - c * clen)] = j == threadIdx.x ? ov : p.out_value[row * k + j];
+      }
     }
   }
 }
@@ -359,12 +455,22 @@ __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_con
   const uint32_t off_c2 = (cb + 127u) & ~127u;
   const uint32_t off_g = PROD ? 2 * off_c2 : off_c2;
   FeedSetup fs = feed_setup(smem, a.L);
-  fs.feed.streams = PROD ? 3 : 2;
-  fs.feed.bytes[0] = cb; fs.feed.offset[0] = 0; fs.feed.base[0] = p.codes;
-  fs.feed.bytes[1] = static_cast<uint32_t>(D) * sizeof(GT); fs.feed.offset[1] = off_g; fs.feed.base[1] = a.g;
-  if (PROD) { fs.feed.bytes[2] = cb; fs.feed.offset[2] = off_c2; fs.feed.base[2] = a.p2.codes; }
-  for (int j = threadIdx.x; j < k; j += blockDim.x) fs.chan[j] = max(0, min(D - 1, p.channels[j]));
-  for (int j = threadIdx.x; j < k2; j += blockDim.x) fs.chan2[j] = max(0, min(D - 1, a.p2.channels[j]));
+  fs.feed.add(p.codes, cb, 0);
+  fs.feed.add(a.g, static_cast<uint32_t>(D) * sizeof(GT), off_g);
+  if (PROD) fs.feed.add(a.p2.codes, cb, off_c2);
+  __nv_bfloat16* csc = reinterpret_cast<__nv_bfloat16*>(smem + a.L.off_csc);
+  __nv_bfloat16* csc2 = reinterpret_cast<__nv_bfloat16*>(smem + a.L.off_csc2);
+  if (ROT == 3) {
+    if (p.lowrank) fs.feed.add(p.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr, p.seq);
+    if (PROD && a.p2.lowrank) fs.feed.add(a.p2.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr2, a.p2.seq);
+    if (p.scale_kind == kScaleChannel)
+      for (int c = threadIdx.x; c < D; c += blockDim.x) csc[c] = p.scale[c];
+    if (PROD && a.p2.scale_kind == kScaleChannel)
+      for (int c = threadIdx.x; c < D; c += blockDim.x) csc2[c] = a.p2.scale[c];
+  } else {
+    for (int j = threadIdx.x; j < k; j += blockDim.x) fs.chan[j] = max(0, min(D - 1, p.channels[j]));
+    for (int j = threadIdx.x; j < k2; j += blockDim.x) fs.chan2[j] = max(0, min(D - 1, a.p2.channels[j]));
+  }
   Groups<BITS, UPT, ROT> g;
   g.init(D);
   __syncthreads();
@@ -374,15 +480,23 @@ __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_con
   for (int i = 0; row < rows; ++i, row += stride) {
     const int st = i % fs.feed.ring.stages;
     float ov = 0.f, ov2 = 0.f;
-    if (threadIdx.x < k) ov = __bfloat162float(p.out_value[row * k + threadIdx.x]);
-    if (PROD && threadIdx.x < k2) ov2 = __bfloat162float(a.p2.out_value[row * k2 + threadIdx.x]);
+    uint2 meta = make_uint2(0u, 0u), meta2 = make_uint2(0u, 0u);
+    if (ROT == 3) {
+      meta = p.row_meta[row];
+      if (PROD) meta2 = a.p2.row_meta[row];
+    } else {
+      if (threadIdx.x < k) ov = __bfloat162float(p.out_value[row * k + threadIdx.x]);
+      if (PROD && threadIdx.x < k2) ov2 = __bfloat162float(a.p2.out_value[row * k2 + threadIdx.x]);
+    }
     feed_wait(fs, i);
     const unsigned char* slot = fs.feed.ring.slot(st);
     const GT* gs = reinterpret_cast<const GT*>(slot + off_g);
     GT* d1 = reinterpret_cast<GT*>(a.dx1) + row * D;
     GT* d2 = reinterpret_cast<GT*>(a.dx2) + row * D;
     float f[NR][8];
-    rebuild_row<BITS, UPT, ROT, true>(p, g, fs.w_rot, slot, row, f);
+    RefCtx rc;
+    if (ROT == 3) rc = ref_ctx(p, csc, slot, a.L.off_lr, row);
+    rebuild_row<BITS, UPT, ROT, true>(p, g, fs.w_rot, slot, row, f, &rc);
     if (PROD) {
       // dx2 = x1 * g is finished before the second operand is rebuilt
 #pragma unroll
@@ -395,7 +509,8 @@ __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_con
           store8<GT>(d2, g.col[r], o);
         }
       }
-      rebuild_row<BITS, UPT, ROT, true>(a.p2, g, fs.w_rot, slot + off_c2, row, f);
+      if (ROT == 3) rc = ref_ctx(a.p2, csc2, slot, a.L.off_lr2, row);
+      rebuild_row<BITS, UPT, ROT, true>(a.p2, g, fs.w_rot, slot + off_c2, row, f, &rc);
     }
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
@@ -412,12 +527,35 @@ __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_con
     }
     // upstream gradient at the outlier channels, read before the slot is handed back
     float gq = 0.f, gq2 = 0.f;
-    if (threadIdx.x < k) gq = static_cast<float>(gs[fs.chan[threadIdx.x]]);
-    if (PROD && threadIdx.x < k2) gq2 = static_cast<float>(gs[fs.chan2[threadIdx.x]]);
+    if (ROT != 3) {
+      if (threadIdx.x < k) gq = static_cast<float>(gs[fs.chan[threadIdx.x]]);
+      if (PROD && threadIdx.x < k2) gq2 = static_cast<float>(gs[fs.chan2[threadIdx.x]]);
+    }
     __syncthreads();
     if (feed_failed(fs, p.status, i, row, rows, stride)) return;
     fs.feed.refill(st, row, rows, stride);
     const GT* grow = reinterpret_cast<const GT*>(a.g) + row * D;
+    if (ROT == 3) {
+      // element outliers of the row: the outputs that depend on the reconstruction are redone there
+      const __nv_bfloat16* lr_row = p.lowrank ? p.lowrank + (row % p.seq) * static_cast<long long>(D) : nullptr;
+      for (uint32_t j = threadIdx.x; j < meta.y; j += blockDim.x) {
+        const uint32_t e = p.pool[meta.x + j];
+        const int c = static_cast<int>(e & 0xffffu);
+        const float o = ref_outlier_value(e, lr_row);
+        const float gv = static_cast<float>(grow[c]);
+        if (PROD) d2[c] = from_float<GT>(o * gv);
+        else d1[c] = from_float<GT>((OP == HYC_ACT_SILU ? silu_grad_f(o) : gelu_tanh_grad_f(o)) * gv);
+      }
+      if (PROD) {
+        const __nv_bfloat16* lr_row2 = a.p2.lowrank ? a.p2.lowrank + (row % a.p2.seq) * static_cast<long long>(D) : nullptr;
+        for (uint32_t j = threadIdx.x; j < meta2.y; j += blockDim.x) {
+          const uint32_t e = a.p2.pool[meta2.x + j];
+          const int c = static_cast<int>(e & 0xffffu);
+          d1[c] = from_float<GT>(static_cast<float>(grow[c]) * ref_outlier_value(e, lr_row2));
+        }
+      }
+      continue;
+    }
     for (int j = threadIdx.x; j < k; j += blockDim.x) {
       const int c = fs.chan[j];
       const float o = j == threadIdx.x ? ov : __bfloat162float(p.out_value[row * k + j]);
@@ -460,16 +598,20 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
   const uint32_t cb = static_cast<uint32_t>(D) * BITS / 8;
   const uint32_t off_g = (cb + 127u) & ~127u;
   FeedSetup fs = feed_setup(smem, a.L);
-  fs.feed.streams = 2;
-  fs.feed.bytes[0] = cb; fs.feed.offset[0] = 0; fs.feed.base[0] = p.codes;
-  fs.feed.bytes[1] = static_cast<uint32_t>(D) * sizeof(GT); fs.feed.offset[1] = off_g; fs.feed.base[1] = a.dy;
+  fs.feed.add(p.codes, cb, 0);
+  fs.feed.add(a.dy, static_cast<uint32_t>(D) * sizeof(GT), off_g);
+  if (ROT == 3 && p.lowrank) fs.feed.add(p.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr, p.seq);
+  __nv_bfloat16* csc = reinterpret_cast<__nv_bfloat16*>(smem + a.L.off_csc);
+  if (ROT == 3 && p.scale_kind == kScaleChannel)
+    for (int c = threadIdx.x; c < D; c += blockDim.x) csc[c] = p.scale[c];
   float* wsm = reinterpret_cast<float*>(smem + a.L.off_wsm);
   float* red = reinterpret_cast<float*>(smem + a.L.off_red);
   float* acc_w = reinterpret_cast<float*>(smem + a.L.off_acc);
   float* acc_b = acc_w + D;
   const bool ln = a.kind == HYC_NORM_LAYER;
   const float plus = a.kind == HYC_NORM_RMS_GEMMA ? 1.f : 0.f;
-  for (int j = threadIdx.x; j < k; j += blockDim.x) fs.chan[j] = max(0, min(D - 1, p.channels[j]));
+  if (ROT != 3)
+    for (int j = threadIdx.x; j < k; j += blockDim.x) fs.chan[j] = max(0, min(D - 1, p.channels[j]));
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     wsm[c] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[c])
                            : static_cast<const float*>(a.weight)[c]) + plus;
@@ -478,7 +620,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
   Groups<BITS, UPT, ROT> g;
   g.init(D);
   __syncthreads();
-  if (ROT != 0) g.init_masks(fs.chan, k);
+  if (ROT == 1 || ROT == 2) g.init_masks(fs.chan, k);
   const float inv_d = 1.0f / static_cast<float>(D);
   const long long rows = p.rows, stride = gridDim.x;
   long long row = blockIdx.x;
@@ -489,12 +631,21 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
     const float rstd = __ldg(a.rstd + row);
     const float mean = ln ? __ldg(a.mean + row) : 0.f;
     float ov = 0.f;
-    if (threadIdx.x < k) ov = __bfloat162float(p.out_value[row * k + threadIdx.x]);
+    uint2 meta = make_uint2(0u, 0u);
+    uint32_t ent = 0;
+    if (ROT == 3) {
+      meta = p.row_meta[row];
+      if (threadIdx.x < meta.y) ent = p.pool[meta.x + threadIdx.x];
+    } else if (threadIdx.x < k) {
+      ov = __bfloat162float(p.out_value[row * k + threadIdx.x]);
+    }
     feed_wait(fs, i);
     const unsigned char* slot = fs.feed.ring.slot(st);
     const GT* gs = reinterpret_cast<const GT*>(slot + off_g);
     float f[NR][8];
-    rebuild_row<BITS, UPT, ROT, true, true>(p, g, fs.w_rot, slot, row, f);
+    RefCtx rc;
+    if (ROT == 3) rc = ref_ctx(p, csc, slot, a.L.off_lr, row);
+    rebuild_row<BITS, UPT, ROT, true, true>(p, g, fs.w_rot, slot, row, f, &rc);
     // f becomes x-hat, wd = w * dy
     float c1 = 0.f, c2 = 0.f;
     float wd[NR][8];
@@ -516,13 +667,26 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
     }
     // outlier channels: the true x-hat differs from the streamed one by o * rstd
     float gq = 0.f;
-    for (int j = threadIdx.x; j < k; j += blockDim.x) {
-      const int c = fs.chan[j];
-      const float o = j == threadIdx.x ? ov : __bfloat162float(p.out_value[row * k + j]);
-      float gy = static_cast<float>(gs[c]);
-      if (sizeof(GT) == 4) gy = bf16_round(gy);
-      if (j == threadIdx.x) gq = gy;
-      c1 = fmaf(o * rstd, wsm[c] * gy, c1);
+    if (ROT == 3) {
+      // element outliers: the streamed x-hat used the low-rank value alone (their code is the zero code)
+      for (uint32_t j = threadIdx.x; j < meta.y; j += blockDim.x) {
+        const uint32_t e = j == threadIdx.x ? ent : p.pool[meta.x + j];
+        const int c = static_cast<int>(e & 0xffffu);
+        const float was = rc.lrs ? __bfloat162float(rc.lrs[c]) : 0.f;
+        const float o = ref_outlier_value(e, rc.lrs) - was;
+        float gy = static_cast<float>(gs[c]);
+        if (sizeof(GT) == 4) gy = bf16_round(gy);
+        c1 = fmaf(o * rstd, wsm[c] * gy, c1);
+      }
+    } else {
+      for (int j = threadIdx.x; j < k; j += blockDim.x) {
+        const int c = fs.chan[j];
+        const float o = j == threadIdx.x ? ov : __bfloat162float(p.out_value[row * k + j]);
+        float gy = static_cast<float>(gs[c]);
+        if (sizeof(GT) == 4) gy = bf16_round(gy);
+        if (j == threadIdx.x) gq = gy;
+        c1 = fmaf(o * rstd, wsm[c] * gy, c1);
+      }
     }
     {
 #pragma unroll
@@ -571,6 +735,21 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
     __syncthreads();
     fs.feed.refill(st, row, rows, stride);
     const GT* grow = reinterpret_cast<const GT*>(a.dy) + row * D;
+    if (ROT == 3) {
+      const __nv_bfloat16* lr_row = p.lowrank ? p.lowrank + (row % p.seq) * static_cast<long long>(D) : nullptr;
+      for (uint32_t j = threadIdx.x; j < meta.y; j += blockDim.x) {
+        const uint32_t e = j == threadIdx.x ? ent : p.pool[meta.x + j];
+        const int c = static_cast<int>(e & 0xffffu);
+        const float o = ref_outlier_value(e, lr_row);
+        const float was = lr_row ? __bfloat162float(lr_row[c]) : 0.f;
+        float gy = static_cast<float>(grow[c]);
+        if (sizeof(GT) == 4) gy = bf16_round(gy);
+        const float xh = (o - mean) * rstd;
+        dxrow[c] = __float2bfloat16_rn((wsm[c] * gy - (xh * c1 + c2)) * rstd);
+        if (a.need_dw) acc_w[c] += gy * ((o - was) * rstd);
+      }
+      continue;
+    }
     for (int j = threadIdx.x; j < k; j += blockDim.x) {
       const int c = fs.chan[j];
       const float o = j == threadIdx.x ? ov : __bfloat162float(p.out_value[row * k + j]);
@@ -608,10 +787,12 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
                              int default_stages = 3) {
   BwdPlan b;
   memset(&b, 0, sizeof(b));
-  if (q->mode != HYC_MODE_N || q->rotate > 256) return b;
+  const bool ref = q->mode == HYC_MODE_R;
+  if (ref ? (q->bits != 2 && q->bits != 4 && q->bits != 8) : q->rotate > 256) return b;
+  if (q2 && q2->mode != q->mode) return b;
   const int D = q->cols, nseg = 8 / q->bits;
   // rotation in registers needs every segment to start on a rotation-block boundary
-  b.rot = q->rotate == 0 ? 0 : ((D / nseg) % q->rotate == 0 ? 2 : 1);
+  b.rot = ref ? 3 : q->rotate == 0 ? 0 : ((D / nseg) % q->rotate == 0 ? 2 : 1);
   int threads = g_tune_threads ? g_tune_threads : (D <= 1024 ? 64 : D <= 4096 ? 128 : 256);
   // kernels that hold two operands per element in registers run better with fewer elements per thread
   if (!g_tune_threads && min_threads && threads < min_threads && D >= 8 * min_threads) threads = min_threads;
@@ -638,8 +819,16 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
   auto take = [&](uint32_t bytes) { uint32_t o = off; off = align_up(off + bytes, 16); return o; };
   b.L.off_red = take(2 * 64 * 4);
   b.L.off_misc = take(16);
-  b.L.off_chan = take((q->n_channels > 0 ? q->n_channels : 1) * 4);
-  b.L.off_chan2 = take(((q2 && q2->n_channels > 0) ? q2->n_channels : 1) * 4);
+  b.L.off_chan = take((!ref && q->n_channels > 0 ? q->n_channels : 1) * 4);
+  b.L.off_chan2 = take(((!ref && q2 && q2->n_channels > 0) ? q2->n_channels : 1) * 4);
+  if (ref && q->scale_kind == HYC_SCALE_CHANNEL) b.L.off_csc = take(D * 2);
+  if (ref && q2 && q2->scale_kind == HYC_SCALE_CHANNEL) b.L.off_csc2 = take(D * 2);
+  if (ref) {
+    // low-rank rows ride at the end of a staging slot
+    slot_bytes = align_up(slot_bytes, 128);
+    if (q->lowrank) { b.L.off_lr = slot_bytes; slot_bytes += align_up(static_cast<uint32_t>(D) * 2, 128); }
+    if (q2 && q2->lowrank) { b.L.off_lr2 = slot_bytes; slot_bytes += align_up(static_cast<uint32_t>(D) * 2, 128); }
+  }
   if (b.rot == 1) b.L.off_rot = take(D * 4);
   if (want_w) b.L.off_wsm = take(D * 4);
   if (acc_rows) b.L.off_acc = take(static_cast<uint32_t>(acc_rows) * D * 4);
@@ -680,6 +869,8 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
       if constexpr (UP <= CAP) { LAUNCH(B, UP, 1) done__ = true; }                             \
     } else if ((PLAN).rot == 2) {                                                              \
       if constexpr (UP * (8 / B) <= CAP) { LAUNCH(B, UP, 2) done__ = true; }                   \
+    } else if ((PLAN).rot == 3) {                                                              \
+      if constexpr (UP * (8 / B) <= CAP) { LAUNCH(B, UP, 3) done__ = true; }                   \
     } else {                                                                                   \
       if constexpr (UP * (8 / B) <= CAP) { LAUNCH(B, UP, 0) done__ = true; }                   \
     }                                                                                          \
