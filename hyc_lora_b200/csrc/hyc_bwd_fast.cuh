@@ -378,14 +378,18 @@ __global__ void __launch_bounds__(512, 2) decompress_n_fast_kernel(const __grid_
   const long long rows = p.rows, stride = gridDim.x;
   long long row = blockIdx.x;
   fs.feed.prologue(row, rows, stride);
+  uint2 meta_pref = (ROT == 3 && row < rows) ? p.row_meta[row] : make_uint2(0u, 0u);
   for (int i = 0; row < rows; ++i, row += stride) {
     const int st = i % fs.feed.ring.stages;
     // the outlier values of this row, fetched early by the threads that will store them
     __nv_bfloat16 ov = __float2bfloat16_rn(0.f);
-    uint2 meta = make_uint2(0u, 0u);
+    // reference mode: this row's pool range was fetched one row ahead, so that the entry load
+    // below does not wait for it
+    const uint2 meta = meta_pref;
     uint32_t ent = 0;
     if (ROT == 3) {
-      meta = p.row_meta[row];
+      const long long nr = row + stride;
+      meta_pref = nr < rows ? p.row_meta[nr] : make_uint2(0u, 0u);
       if (threadIdx.x < meta.y) ent = p.pool[meta.x + threadIdx.x];
     } else if (threadIdx.x < k) {
       ov = p.out_value[row * k + threadIdx.x];
@@ -477,13 +481,16 @@ __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_con
   const long long rows = p.rows, stride = gridDim.x;
   long long row = blockIdx.x;
   fs.feed.prologue(row, rows, stride);
+  uint2 meta_pref = (ROT == 3 && row < rows) ? p.row_meta[row] : make_uint2(0u, 0u);
+  uint2 meta_pref2 = (ROT == 3 && PROD && row < rows) ? a.p2.row_meta[row] : make_uint2(0u, 0u);
   for (int i = 0; row < rows; ++i, row += stride) {
     const int st = i % fs.feed.ring.stages;
     float ov = 0.f, ov2 = 0.f;
-    uint2 meta = make_uint2(0u, 0u), meta2 = make_uint2(0u, 0u);
+    const uint2 meta = meta_pref, meta2 = meta_pref2;
     if (ROT == 3) {
-      meta = p.row_meta[row];
-      if (PROD) meta2 = a.p2.row_meta[row];
+      const long long nr = row + stride;
+      meta_pref = nr < rows ? p.row_meta[nr] : make_uint2(0u, 0u);
+      if (PROD) meta_pref2 = nr < rows ? a.p2.row_meta[nr] : make_uint2(0u, 0u);
     } else {
       if (threadIdx.x < k) ov = __bfloat162float(p.out_value[row * k + threadIdx.x]);
       if (PROD && threadIdx.x < k2) ov2 = __bfloat162float(a.p2.out_value[row * k2 + threadIdx.x]);
@@ -613,7 +620,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
   if (ROT != 3)
     for (int j = threadIdx.x; j < k; j += blockDim.x) fs.chan[j] = max(0, min(D - 1, p.channels[j]));
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
-    wsm[c] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[c])
+    wsm[split_index(c, D)] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[c])
                            : static_cast<const float*>(a.weight)[c]) + plus;
     if (a.need_dw) { acc_w[c] = 0.f; if (a.need_db) acc_b[c] = 0.f; }
   }
@@ -625,16 +632,20 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
   const long long rows = p.rows, stride = gridDim.x;
   long long row = blockIdx.x;
   fs.feed.prologue(row, rows, stride);
+  uint2 meta_pref = (ROT == 3 && row < rows) ? p.row_meta[row] : make_uint2(0u, 0u);
   for (int i = 0; row < rows; ++i, row += stride) {
     const int st = i % fs.feed.ring.stages;
     __nv_bfloat16* dxrow = a.dx + row * D;
     const float rstd = __ldg(a.rstd + row);
     const float mean = ln ? __ldg(a.mean + row) : 0.f;
     float ov = 0.f;
-    uint2 meta = make_uint2(0u, 0u);
+    // reference mode: this row's pool range was fetched one row ahead, so that the entry load
+    // below does not wait for it
+    const uint2 meta = meta_pref;
     uint32_t ent = 0;
     if (ROT == 3) {
-      meta = p.row_meta[row];
+      const long long nr = row + stride;
+      meta_pref = nr < rows ? p.row_meta[nr] : make_uint2(0u, 0u);
       if (threadIdx.x < meta.y) ent = p.pool[meta.x + threadIdx.x];
     } else if (threadIdx.x < k) {
       ov = __bfloat162float(p.out_value[row * k + threadIdx.x]);
@@ -654,7 +665,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
       if (g.col[r] >= 0) {
         float gv[8], wv[8];
         load8<GT>(gs, g.col[r], gv);
-        load8<float>(wsm, g.col[r], wv);
+        load8_split(wsm, D, g.col[r], wv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const float gy = sizeof(GT) == 4 ? bf16_round(gv[e]) : gv[e];
@@ -676,7 +687,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
         const float o = ref_outlier_value(e, rc.lrs) - was;
         float gy = static_cast<float>(gs[c]);
         if (sizeof(GT) == 4) gy = bf16_round(gy);
-        c1 = fmaf(o * rstd, wsm[c] * gy, c1);
+        c1 = fmaf(o * rstd, wsm[split_index(c, D)] * gy, c1);
       }
     } else {
       for (int j = threadIdx.x; j < k; j += blockDim.x) {
@@ -685,7 +696,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
         float gy = static_cast<float>(gs[c]);
         if (sizeof(GT) == 4) gy = bf16_round(gy);
         if (j == threadIdx.x) gq = gy;
-        c1 = fmaf(o * rstd, wsm[c] * gy, c1);
+        c1 = fmaf(o * rstd, wsm[split_index(c, D)] * gy, c1);
       }
     }
     {
@@ -745,7 +756,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
         float gy = static_cast<float>(grow[c]);
         if (sizeof(GT) == 4) gy = bf16_round(gy);
         const float xh = (o - mean) * rstd;
-        dxrow[c] = __float2bfloat16_rn((wsm[c] * gy - (xh * c1 + c2)) * rstd);
+        dxrow[c] = __float2bfloat16_rn((wsm[split_index(c, D)] * gy - (xh * c1 + c2)) * rstd);
         if (a.need_dw) acc_w[c] += gy * ((o - was) * rstd);
       }
       continue;
@@ -756,7 +767,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
       float gy = j == threadIdx.x ? gq : static_cast<float>(grow[c]);
       if (sizeof(GT) == 4 && j != threadIdx.x) gy = bf16_round(gy);
       const float xh = (o - mean) * rstd;
-      dxrow[c] = __float2bfloat16_rn((wsm[c] * gy - (xh * c1 + c2)) * rstd);
+      dxrow[c] = __float2bfloat16_rn((wsm[split_index(c, D)] * gy - (xh * c1 + c2)) * rstd);
       if (a.need_dw) acc_w[c] += gy * (o * rstd);  // the streamed pass added gy * (0 - mean) * rstd
     }
   }

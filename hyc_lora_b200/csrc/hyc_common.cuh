@@ -132,6 +132,18 @@ __device__ __forceinline__ void load8<float>(const float* row, int col, float (&
   f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 
+// fp32 tables of D entries that every thread reads 8 consecutive channels at a time (norm weights,
+// reciprocal scales) are kept in shared memory with the two halves of each group of 8 apart:
+// channel c sits at ((c >> 2) & 1) * D/2 + (c >> 3) * 4 + (c & 3).  A warp's two 16-byte reads
+// then touch consecutive 16-byte pieces instead of every other one: no bank conflicts.
+__device__ __forceinline__ int split_index(int c, int D) { return ((c >> 2) & 1) * (D >> 1) + ((c >> 3) << 2) + (c & 3); }
+__device__ __forceinline__ void load8_split(const float* table, int D, int col, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(table + ((col >> 3) << 2));
+  const float4 b = *reinterpret_cast<const float4*>(table + (D >> 1) + ((col >> 3) << 2));
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
 template <typename T>
 __device__ __forceinline__ void store8(T* row, int col, const float (&f)[8]);
 

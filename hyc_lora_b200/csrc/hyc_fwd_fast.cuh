@@ -171,10 +171,10 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
   if (NORM) {
     const float plus = a.kind == HYC_NORM_RMS_GEMMA ? 1.f : 0.f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
-      wsm[c] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[c])
+      wsm[split_index(c, D)] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[c])
                              : static_cast<const float*>(a.weight)[c]) + plus;
       if (ln)
-        bsm[c] = a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[c])
+        bsm[split_index(c, D)] = a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[c])
                               : static_cast<const float*>(a.bias)[c];
     }
   }
@@ -312,7 +312,8 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
       XT* yprev = reinterpret_cast<XT*>(a.y) + row_prev * a.row_stride;
       for (int j = threadIdx.x; j < k; j += blockDim.x) {
         const int c = w.chan[j];
-        const float y = ln ? ((o_prv[j] - mean_prev) * rstd_prev * wsm[c] + bsm[c]) : (o_prv[j] * rstd_prev * wsm[c]);
+        const int cs = split_index(c, D);
+        const float y = ln ? ((o_prv[j] - mean_prev) * rstd_prev * wsm[cs] + bsm[cs]) : (o_prv[j] * rstd_prev * wsm[cs]);
         yprev[c] = from_float<XT>(y);
       }
     }
@@ -341,7 +342,7 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
         const bool ok = ROT == 1 ? (col < D) : ((threadIdx.x + (r / NSEG) * blockDim.x) < U);
         if (ok) {
           float y[8], wv[8];
-          load8<float>(wsm, col, wv);
+          load8_split(wsm, D, col, wv);
           float xv[8];
           if (ROT == 2) {
             load8<XT>(xs, col, xv);
@@ -351,7 +352,7 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
           }
           if (ln) {
             float bv[8];
-            load8<float>(bsm, col, bv);
+            load8_split(bsm, D, col, bv);
 #pragma unroll
             for (int e = 0; e < 8; ++e) y[e] = (xv[e] - mean) * rstd * wv[e] + bv[e];
           } else {
@@ -414,7 +415,8 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     XT* yprev = reinterpret_cast<XT*>(a.y) + row_prev * a.row_stride;
     for (int j = threadIdx.x; j < k; j += blockDim.x) {
       const int c = w.chan[j];
-      const float y = ln ? ((o_prv[j] - mean_prev) * rstd_prev * wsm[c] + bsm[c]) : (o_prv[j] * rstd_prev * wsm[c]);
+      const int cs = split_index(c, D);
+        const float y = ln ? ((o_prv[j] - mean_prev) * rstd_prev * wsm[cs] + bsm[cs]) : (o_prv[j] * rstd_prev * wsm[cs]);
       yprev[c] = from_float<XT>(y);
     }
   }
