@@ -323,10 +323,14 @@ __device__ __forceinline__ FeedSetup feed_setup(unsigned char* smem, const BwdSm
   return s;
 }
 
-// bounded wait on the slot of iteration i; an expired wait raises the CTA's sticky flag
-__device__ __forceinline__ void feed_wait(FeedSetup& s, int i) {
-  const int st = i % s.feed.ring.stages;
-  if (!mbar_wait_bounded(&s.feed.ring.bars[st], (i / s.feed.ring.stages) & 1)) s.misc[0] = 1;
+// bounded wait on slot `st` in barrier phase `ph`; an expired wait raises the CTA's sticky flag
+__device__ __forceinline__ void feed_wait(FeedSetup& s, int st, uint32_t ph) {
+  if (!mbar_wait_bounded(&s.feed.ring.bars[st], ph)) s.misc[0] = 1;
+}
+
+// next ring position / barrier phase (counters instead of divisions by the run-time stage count)
+__device__ __forceinline__ void feed_advance(const FeedSetup& s, int& st, uint32_t& ph) {
+  if (++st == s.feed.ring.stages) { st = 0; ph ^= 1u; }
 }
 
 // after the row's barrier: true if the CTA must stop (some wait expired)
@@ -379,8 +383,9 @@ __global__ void __launch_bounds__(512, 2) decompress_n_fast_kernel(const __grid_
   long long row = blockIdx.x;
   fs.feed.prologue(row, rows, stride);
   uint2 meta_pref = (ROT == 3 && row < rows) ? p.row_meta[row] : make_uint2(0u, 0u);
-  for (int i = 0; row < rows; ++i, row += stride) {
-    const int st = i % fs.feed.ring.stages;
+  int st = 0;
+  uint32_t ph = 0;
+  for (int i = 0; row < rows; ++i, row += stride, feed_advance(fs, st, ph)) {
     // the outlier values of this row, fetched early by the threads that will store them
     __nv_bfloat16 ov = __float2bfloat16_rn(0.f);
     // reference mode: this row's pool range was fetched one row ahead, so that the entry load
@@ -394,7 +399,7 @@ __global__ void __launch_bounds__(512, 2) decompress_n_fast_kernel(const __grid_
     } else if (threadIdx.x < k) {
       ov = p.out_value[row * k + threadIdx.x];
     }
-    feed_wait(fs, i);
+    feed_wait(fs, st, ph);
     float f[NR][8];
     RefCtx rc;
     if (ROT == 3) rc = ref_ctx(p, csc, fs.feed.ring.slot(st), a.L.off_lr, row);
@@ -483,8 +488,9 @@ __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_con
   fs.feed.prologue(row, rows, stride);
   uint2 meta_pref = (ROT == 3 && row < rows) ? p.row_meta[row] : make_uint2(0u, 0u);
   uint2 meta_pref2 = (ROT == 3 && PROD && row < rows) ? a.p2.row_meta[row] : make_uint2(0u, 0u);
-  for (int i = 0; row < rows; ++i, row += stride) {
-    const int st = i % fs.feed.ring.stages;
+  int st = 0;
+  uint32_t ph = 0;
+  for (int i = 0; row < rows; ++i, row += stride, feed_advance(fs, st, ph)) {
     float ov = 0.f, ov2 = 0.f;
     const uint2 meta = meta_pref, meta2 = meta_pref2;
     if (ROT == 3) {
@@ -495,7 +501,7 @@ __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_con
       if (threadIdx.x < k) ov = __bfloat162float(p.out_value[row * k + threadIdx.x]);
       if (PROD && threadIdx.x < k2) ov2 = __bfloat162float(a.p2.out_value[row * k2 + threadIdx.x]);
     }
-    feed_wait(fs, i);
+    feed_wait(fs, st, ph);
     const unsigned char* slot = fs.feed.ring.slot(st);
     const GT* gs = reinterpret_cast<const GT*>(slot + off_g);
     GT* d1 = reinterpret_cast<GT*>(a.dx1) + row * D;
@@ -633,8 +639,9 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
   long long row = blockIdx.x;
   fs.feed.prologue(row, rows, stride);
   uint2 meta_pref = (ROT == 3 && row < rows) ? p.row_meta[row] : make_uint2(0u, 0u);
-  for (int i = 0; row < rows; ++i, row += stride) {
-    const int st = i % fs.feed.ring.stages;
+  int st = 0;
+  uint32_t ph = 0;
+  for (int i = 0; row < rows; ++i, row += stride, feed_advance(fs, st, ph)) {
     __nv_bfloat16* dxrow = a.dx + row * D;
     const float rstd = __ldg(a.rstd + row);
     const float mean = ln ? __ldg(a.mean + row) : 0.f;
@@ -650,7 +657,7 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
     } else if (threadIdx.x < k) {
       ov = __bfloat162float(p.out_value[row * k + threadIdx.x]);
     }
-    feed_wait(fs, i);
+    feed_wait(fs, st, ph);
     const unsigned char* slot = fs.feed.ring.slot(st);
     const GT* gs = reinterpret_cast<const GT*>(slot + off_g);
     float f[NR][8];

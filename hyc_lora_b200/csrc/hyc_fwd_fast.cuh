@@ -193,12 +193,18 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
   float rstd_prev = 0.f, mean_prev = 0.f;
   long long row_prev = -1;
   int i = 0;
+  // ring position and barrier phase of the current row, and the position in the ring of three saved-outlier
+  // rows: counters instead of divisions by the (run-time) stage count
+  int st = 0, st_prev = 0, o3 = 0;
+  uint32_t ph = 0;
   for (; row < rows; ++i, row += stride) {
-    const int st = i % ring.stages;
     const int par = i & 1;
     const XT* xs = reinterpret_cast<const XT*>(ring.slot(st));
     float* gamax = w.gamax + par * G;
-    const float* o_cur = osm + (i % 3) * k;
+    const float* o_cur = osm + o3 * k;
+    const int o3_next = o3 == 2 ? 0 : o3 + 1, o3_prev = o3 == 0 ? 2 : o3 - 1;
+    const int sn = st + 1 == ring.stages ? 0 : st + 1;
+    const uint32_t phn = sn == 0 ? ph ^ 1u : ph;
     float f[NR][8];
     float mean = 0.f;
     // ---- pass 1
@@ -286,9 +292,8 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     // ---- next row: save and zero its outlier channels before the barrier
     const long long row_next = row + stride;
     if (row_next < rows) {
-      const int sn = (i + 1) % ring.stages;
-      if (!mbar_wait_bounded(&ring.bars[sn], ((i + 1) / ring.stages) & 1)) w.misc[2] = 1;
-      gather_and_zero<XT>(p, w, reinterpret_cast<XT*>(ring.slot(sn)), osm + ((i + 1) % 3) * k, row_next);
+      if (!mbar_wait_bounded(&ring.bars[sn], phn)) w.misc[2] = 1;
+      gather_and_zero<XT>(p, w, reinterpret_cast<XT*>(ring.slot(sn)), osm + o3_next * k, row_next);
     }
     reduce_sum_max(ss, amax, w.red + par * 64);
     if (w.misc[2]) {
@@ -299,7 +304,7 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     if (threadIdx.x == 0) {
       // the slot every thread has finished with: this row's, or the previous row's when pass 2 reads it again
       const long long freed = kLateRefill ? row_prev : row;
-      const int slot_free = kLateRefill ? (i + ring.stages - 1) % ring.stages : st;
+      const int slot_free = kLateRefill ? st_prev : st;
       const long long next = freed + ring.stages * stride;
       if (freed >= 0 && next < rows) {
         fence_proxy_async();
@@ -308,7 +313,7 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     }
     // ---- norm output of the previous row at its outlier channels
     if (NORM && row_prev >= 0) {
-      const float* o_prv = osm + ((i + 2) % 3) * k;
+      const float* o_prv = osm + o3_prev * k;
       XT* yprev = reinterpret_cast<XT*>(a.y) + row_prev * a.row_stride;
       for (int j = threadIdx.x; j < k; j += blockDim.x) {
         const int c = w.chan[j];
@@ -408,10 +413,14 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
     row_prev = row;
     rstd_prev = rstd;
     mean_prev = mean;
+    st_prev = st;
+    st = sn;
+    ph = phn;
+    o3 = o3_next;
   }
   if (NORM && row_prev >= 0) {
     __syncthreads();
-    const float* o_prv = osm + ((i + 2) % 3) * k;
+    const float* o_prv = osm + (o3 == 0 ? 2 : o3 - 1) * k;
     XT* yprev = reinterpret_cast<XT*>(a.y) + row_prev * a.row_stride;
     for (int j = threadIdx.x; j < k; j += blockDim.x) {
       const int c = w.chan[j];
