@@ -100,6 +100,8 @@ SYMBOLS = {
     "hyc_softmax_expand": (C.c_int, [C.POINTER(HycSparseRows), C.c_void_p, C.c_void_p]),
     "hyc_softmax_bwd": (C.c_int, [C.POINTER(HycSparseRows), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "hyc_nf4_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "hyc_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                           C.c_int32, C.c_void_p]),
     "hyc_select_channels_static_max_cols": (C.c_int, []),
     "hyc_select_channels_noalloc": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
 }

@@ -15,8 +15,8 @@
 // accumulators in tensor memory, and commits to an mbarrier that tells everybody when the
 // staging buffer may be overwritten (two buffers; the packed bytes of chunk c+1 are already in
 // registers while chunk c is converted).  At the end four warps read the accumulators back
-// with tcgen05.ld and store one partial [rank, D] slab per token slice; a second kernel adds
-// the slabs.
+// with tcgen05.ld and store one partial [rank, D] slab per token slice; wgrad_finish_kernel adds
+// the slabs, rotates the rows back and drops in the outlier channels' columns.
 //
 // Channel-outlier mode only.  Outlier channels carry the zero code, so their columns come out
 // as zero here; the caller adds G^T * out_value there.  With rotation the kernel contracts the
@@ -348,24 +348,41 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
   if (warp == 0) tmem_dealloc(tmem_base, a.tmem_cols);
 }
 
-// out[n, d] = sum over slabs
-__global__ void wgrad_reduce_kernel(const float* partials, int splits, long long slab, float* out) {
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= slab) return;
-  float s = 0.f;
-  for (int q = 0; q < splits; ++q) s += partials[q * slab + i];
-  out[i] = s;
-}
-
-// block rotation of every output row (rows are short: one CTA per row, row staged in shared memory)
-__global__ void wgrad_rotate_rows_kernel(float* out, int D, int n) {
+// Last kernel of the call, one CTA per (output row n, part of the row): adds the partial slabs in a
+// fixed order, applies the inverse block rotation to the summed row in shared memory (the rotation
+// commutes with the contraction over tokens), overwrites the outlier channels' entries with the sums
+// of the side partials, and writes the row.
+__global__ void wgrad_finish_kernel(const float* __restrict__ partials, int splits, const float* __restrict__ side,
+                                    int slices, const int* __restrict__ channels, int k, int rank, int D, int rotate,
+                                    float* __restrict__ out) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* rowbuf = reinterpret_cast<float*>(smem_raw);
-  float* row = out + static_cast<long long>(blockIdx.x) * D;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) rowbuf[c] = row[c];
+  const int n = blockIdx.x;
+  const int len = D / gridDim.y, d0 = blockIdx.y * len;
+  const long long slab = static_cast<long long>(rank) * D;
+  const float* src = partials + static_cast<long long>(n) * D + d0;
+  for (int c = threadIdx.x << 2; c < len; c += blockDim.x << 2) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < splits; ++q) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src + q * slab + c));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(rowbuf + c) = acc;
+  }
   __syncthreads();
-  fwht_row<float, false>(rowbuf, nullptr, rowbuf, D, n);
-  for (int c = threadIdx.x; c < D; c += blockDim.x) row[c] = rowbuf[c];
+  if (rotate) fwht_row<float, false>(rowbuf, nullptr, rowbuf, len, rotate);
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    const int ch = channels[j] - d0;
+    if (ch >= 0 && ch < len) {
+      float sum = 0.f;
+      for (int q = 0; q < slices; ++q) sum += side[(static_cast<long long>(q) * k + j) * rank + n];
+      rowbuf[ch] = sum;
+    }
+  }
+  __syncthreads();
+  float* dst = out + static_cast<long long>(n) * D + d0;
+  for (int c = threadIdx.x << 2; c < len; c += blockDim.x << 2)
+    *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(rowbuf + c);
 }
 
 // ---- columns of the outlier channels: out[n, channels[j]] = sum_t grad[t, n] * out_value[t, j].
@@ -374,7 +391,7 @@ __global__ void wgrad_rotate_rows_kernel(float* out, int D, int n) {
 // by all threads, then a thread owning (outlier j, 8 consecutive ranks) accumulates over the
 // chunk.  A warp covers 4 outliers x 8 rank groups at rank 64: the value read is a broadcast, the
 // gradient read one conflict-free 128-byte line.  Slices are summed in a fixed order by
-// wgrad_side_scatter_kernel, which also scatters to the channel columns.
+// wgrad_finish_kernel, which also writes them to the channel columns.
 constexpr int kSideChunk = 64;
 
 __global__ void wgrad_side_kernel(const __nv_bfloat16* __restrict__ out_value, const __nv_bfloat16* __restrict__ grad,
@@ -431,16 +448,6 @@ __global__ void wgrad_side_kernel(const __nv_bfloat16* __restrict__ out_value, c
       *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[o][4], acc[o][5], acc[o][6], acc[o][7]);
     }
   }
-}
-
-__global__ void wgrad_side_scatter_kernel(const float* __restrict__ part, int slices, const int* __restrict__ channels,
-                                          int k, int rank, int D, float* __restrict__ out) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;   // (j, n)
-  if (i >= k * rank) return;
-  const int j = i / rank, n = i - j * rank;
-  float s = 0.f;
-  for (int q = 0; q < slices; ++q) s += part[static_cast<long long>(q) * k * rank + i];
-  out[static_cast<long long>(n) * D + channels[j]] = s;
 }
 
 struct WgradPlan {
@@ -604,16 +611,9 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
   if (saved->bits == 2) HYC_WG(2) else if (saved->bits == 4) HYC_WG(4) else HYC_WG(8)
 #undef HYC_WG
   if (cudaGetLastError() != cudaSuccess) return HYC_ERR_CUDA;
-  wgrad_reduce_kernel<<<static_cast<int>((slab + 255) / 256), 256, 0, stream>>>(partials, splits, slab, out);
-  if (saved->rotate) {
-    const size_t sm = static_cast<size_t>(D) * 4;
-    if (sm > 48 * 1024)
-      cudaFuncSetAttribute(wgrad_rotate_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    wgrad_rotate_rows_kernel<<<rank, 256, sm, stream>>>(out, D, saved->rotate);
-  }
+  const int k = saved->n_channels;
+  const float* side = partials + static_cast<long long>(splits) * slab;
   if (pl.side_slices > 0) {
-    const int k = saved->n_channels;
-    float* side = partials + static_cast<long long>(splits) * slab;
     const int units = k * (rank >> 3);
     const int own = (units + 511) / 512;                 // units per thread, at most 4 (wgrad_check)
     const int threads = ((units + own - 1) / own + 31) / 32 * 32;
@@ -622,9 +622,20 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
       if (cudaFuncSetAttribute(wgrad_side_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
         return HYC_ERR_CUDA;
     wgrad_side_kernel<<<pl.side_slices, threads, sm, stream>>>(static_cast<const __nv_bfloat16*>(saved->out_value), a.grad,
-                                                               saved->rows, pl.side_rows_per, k, rank, side);
-    wgrad_side_scatter_kernel<<<(k * rank + 255) / 256, 256, 0, stream>>>(side, pl.side_slices, saved->channels, k, rank,
-                                                                          D, out);
+                                                               saved->rows, pl.side_rows_per, k, rank,
+                                                               const_cast<float*>(side));
+  }
+  {
+    // parts of a row are independent when they hold whole rotation blocks
+    const int unit = saved->rotate ? saved->rotate : 128;
+    int parts = 8;
+    while (parts > 1 && (D % parts != 0 || (D / parts) % unit != 0 || (D / parts) % 128 != 0)) parts >>= 1;
+    const size_t sm = static_cast<size_t>(D / parts) * 4;
+    if (sm > 48 * 1024)
+      if (cudaFuncSetAttribute(wgrad_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
+        return HYC_ERR_CUDA;
+    wgrad_finish_kernel<<<dim3(rank, parts), 256, sm, stream>>>(partials, splits, side, pl.side_slices, saved->channels,
+                                                               pl.side_slices > 0 ? k : 0, rank, D, saved->rotate, out);
   }
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }

@@ -62,12 +62,63 @@ class LlamaHadamard(nn.Module):
         return x1 * x2
 
 
-def _rope(q, k, theta):
-    b, h, s, d = q.shape
-    pos = torch.arange(s, device=q.device, dtype=torch.float32)
-    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=q.device, dtype=torch.float32) / d))
-    ang = torch.outer(pos, inv)
-    cos, sin = torch.cat((ang.cos(), ang.cos()), -1).to(q.dtype), torch.cat((ang.sin(), ang.sin()), -1).to(q.dtype)
+_ROPE_TABLES = {}
+
+
+def _rope_table(seq: int, head_dim: int, theta: float, device) -> torch.Tensor:
+    """fp32 [seq, head_dim/2, 2] = (cos, sin) of (position, pair index), cached per device."""
+    key = (seq, head_dim, float(theta), str(device))
+    tab = _ROPE_TABLES.get(key)
+    if tab is None:
+        pos = torch.arange(seq, device=device, dtype=torch.float32)
+        inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+        ang = torch.outer(pos, inv)
+        tab = torch.stack((ang.cos(), ang.sin()), dim=-1).contiguous()
+        _ROPE_TABLES[key] = tab
+    return tab
+
+
+class _RopeFunc(torch.autograd.Function):
+    """Rotary embedding of the query and key projections ([b, s, heads * hd] bf16, contiguous, not views) by one
+    in-place kernel launch; the backward is the rotation by the negative angle, applied in place to the
+    incoming gradients."""
+
+    @staticmethod
+    def forward(ctx, q, k, table, hq, hk, hd):
+        from .. import _lib
+        from ..packed import _stream
+        b, s, _ = q.shape
+        ctx.table, ctx.dims = table, (b * s, s, hq, hk, hd)
+        _lib.check(_lib.lib.hyc_rope(q.data_ptr(), k.data_ptr(), table.data_ptr(), b * s, s, hq, hk, hd, 0, _stream()),
+                   "hyc_rope")
+        ctx.mark_dirty(q, k)
+        return q, k
+
+    @staticmethod
+    def backward(ctx, gq, gk):
+        from .. import _lib
+        from ..packed import _stream
+        tokens, s, hq, hk, hd = ctx.dims
+        gq, gk = gq.contiguous().clone(), gk.contiguous().clone()
+        _lib.check(_lib.lib.hyc_rope(gq.data_ptr(), gk.data_ptr(), ctx.table.data_ptr(), tokens, s, hq, hk, hd, 1,
+                                     _stream()), "hyc_rope")
+        return gq, gk, None, None, None, None
+
+
+def _rope(q, k, theta, hq, hk):
+    """q [b, s, hq * hd], k [b, s, hk * hd] -> rotated [b, s, heads, hd].  CUDA bf16 projections go through the
+    fused kernel (in place: they are fresh tensors); anything else (the CPU hosts the fixtures are made from)
+    through tensor ops."""
+    b, s, _ = q.shape
+    d = q.shape[-1] // hq
+    tab = _rope_table(s, d, theta, q.device)
+    if q.is_cuda and q.dtype == torch.bfloat16 and d % 16 == 0 and q.is_contiguous() and k.is_contiguous() \
+            and q._base is None and k._base is None:
+        q, k = _RopeFunc.apply(q, k, tab, hq, hk, d)
+        return q.view(b, s, hq, d), k.view(b, s, hk, d)
+    q, k = q.reshape(b, s, hq, d), k.reshape(b, s, hk, d)
+    cos = torch.cat((tab[..., 0], tab[..., 0]), -1).to(q.dtype)[None, :, None, :]
+    sin = torch.cat((tab[..., 1], tab[..., 1]), -1).to(q.dtype)[None, :, None, :]
 
     def rot(x):
         x1, x2 = x[..., : d // 2], x[..., d // 2:]
@@ -90,10 +141,9 @@ class Attention(nn.Module):
         b, s, _ = x.shape
         c = self.c
         hd = c.hidden // c.heads
-        q = self.q_proj(x).view(b, s, c.heads, hd).transpose(1, 2)
-        k = self.k_proj(x).view(b, s, c.kv_heads, hd).transpose(1, 2)
         v = self.v_proj(x).view(b, s, c.kv_heads, hd).transpose(1, 2)
-        q, k = _rope(q, k, c.rope_theta)
+        q, k = _rope(self.q_proj(x), self.k_proj(x), c.rope_theta, c.heads, c.kv_heads)
+        q, k = q.transpose(1, 2), k.transpose(1, 2)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=c.kv_heads != c.heads)
         return self.o_proj(o.transpose(1, 2).reshape(b, s, c.heads * hd))
 

@@ -134,7 +134,12 @@ class LoRALinear(nn.Module):
         self.scaling = alpha / r
 
     def forward(self, x):
-        return self.base_layer(x) + self.lora_B(self.lora_A(x)) * self.scaling
+        # base + scaling * (A x) B^T with the scale and the add in the GEMM's epilogue (no separate
+        # elementwise kernels); lora_A stays a module so that it can be swapped for the compressing linear
+        base = self.base_layer(x)
+        h = self.lora_A(x)
+        base.view(-1, base.shape[-1]).addmm_(h.reshape(-1, h.shape[-1]), self.lora_B.weight.t(), alpha=self.scaling)
+        return base
 
 
 def lora_parameters(model: nn.Module):

@@ -16,9 +16,19 @@ class SiteOptions:
     is the reference's arithmetic; ``"channel"`` keeps the top ``outlier_ratio``
     absmax channels in bf16, quantises the rest with a dynamic absmax scale per
     token (``group_size=0``) or per 128 channels, optionally after a block
-    Walsh-Hadamard rotation (``rotate`` = block size)."""
+    Walsh-Hadamard rotation (``rotate`` = block size).
 
-    def __init__(self, outlier_ratio: float, outlier_mode: str = "element", group_size: int = 0, rotate: int = 0):
+    The rotation kernels keep the butterflies in registers when every packed
+    segment (``cols / (8 / bits)`` channels) starts on a block boundary.  With
+    ``fit_rotate`` (default) a site whose segments do not, e.g. 11 008 channels at
+    4 bits with blocks of 256, uses the largest supported block that does (64
+    there); ``fit_rotate=False`` keeps the requested block and the slower
+    shared-memory hand-over."""
+
+    BLOCKS = (4096, 1024, 256, 64, 16)
+
+    def __init__(self, outlier_ratio: float, outlier_mode: str = "element", group_size: int = 0, rotate: int = 0,
+                 fit_rotate: bool = True):
         if outlier_mode not in ("element", "channel"):
             raise ValueError("outlier_mode must be 'element' or 'channel'")
         if group_size not in (0, 128):
@@ -26,12 +36,23 @@ class SiteOptions:
         if rotate not in (0, 16, 64, 256, 1024, 4096):
             raise ValueError("rotate must be 0 or a block size in {16, 64, 256, 1024, 4096}")
         self.outlier_mode, self.group_size, self.rotate = outlier_mode, group_size, rotate
+        self.fit_rotate = fit_rotate
         self.calib = cf.ChannelCalibration(outlier_ratio)
         self._dummy = None
 
     @property
     def channel(self) -> bool:
         return self.outlier_mode == "channel"
+
+    def rotate_for(self, cols: int, bits: int) -> int:
+        """Rotation block used for an activation of ``cols`` channels at ``bits`` bits."""
+        if not self.rotate or not self.fit_rotate:
+            return self.rotate
+        segment = cols // (8 // bits)
+        for block in self.BLOCKS:
+            if block <= self.rotate and segment % block == 0:
+                return block
+        return self.rotate
 
     def dummy_stats(self, device):
         """Placeholders for the four statistic outputs of a Function in channel mode."""
@@ -56,7 +77,9 @@ def compress_site(x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, method, 
         raise RuntimeError("hyc_lora_b200 operators run on CUDA tensors only (there is no CPU path)")
     if opts is not None and opts.channel:
         channels = opts.calib.channels_for(x, iteration)
-        res = cf.channel_compress(x, channels, sub_outlier_bit, opts.group_size, opts.rotate, norm=norm)
+        cols = x.shape[-1] if x.dim() != 4 else x.shape[1] * x.shape[3]
+        res = cf.channel_compress(x, channels, sub_outlier_bit, opts.group_size, opts.rotate_for(cols, sub_outlier_bit),
+                                  norm=norm)
         stats = opts.dummy_stats(x.device)
         if norm is None:
             return res, stats, None

@@ -233,6 +233,15 @@ int hyc_softmax_bwd(const hyc_sparse_rows* in, const void* g, int g_dtype, void*
 int hyc_nf4_dequant(const void* codes, const float* absmax, const float* codebook, int64_t n, void* out_bf16,
                     void* stream);
 
+/* Rotary position embedding of the host models, in place on the query and key projections
+ * (bf16 [tokens, heads, head_dim], contiguous, head_dim a multiple of 16), half-split pairing as in
+ * rotate_half / apply_rotary_pos_emb (models/modeling_llama.py:228-260).  `cos_sin` is fp32
+ * [seq, head_dim/2, 2] = (cos, sin) of (position, pair index); the position of a token is
+ * token % seq.  `inverse` != 0 rotates by the negative angle (the backward of the forward).
+ * Host-model plumbing, not part of the compression path. */
+int hyc_rope(void* q, void* k, const float* cos_sin, int64_t tokens, int32_t seq, int32_t heads_q, int32_t heads_k,
+             int32_t head_dim, int32_t inverse, void* stream);
+
 /* Channel selection for callers that cannot allocate device memory.  (No counterpart in the
  * reference; added for hosts that own no device allocator -- a foreign-language binding that
  * only sees raw pointers handed to it, or a runtime whose memory plan is frozen once its

@@ -154,3 +154,25 @@ def test_decoder_lora_gradients_match_the_reference_operators():
             want = torch.from_numpy(fix["grad/" + name])
             worst = min(worst, _cos(p.grad.cpu(), want))
     assert worst >= 0.999, worst
+
+
+@pytest.mark.parametrize("hq,hk,hd,s", [(4, 4, 128, 37), (8, 2, 64, 16)])
+def test_rotary_kernel_matches_tensor_ops(hq, hk, hd, s):
+    """The fused in-place rotary kernel against the tensor-op formulation (fp32), forward and backward."""
+    from hyc_lora_b200.hosts.llama import _rope
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(2, s, hq, hd, generator=g).to(torch.bfloat16)
+    k = torch.randn(2, s, hk, hd, generator=g).to(torch.bfloat16)
+    gq, gk = torch.randn(2, s, hq, hd, generator=g), torch.randn(2, s, hk, hd, generator=g)
+    # reference: the same function on CPU fp32 tensors takes the tensor-op path
+    qr, kr = q.float().requires_grad_(True), k.float().requires_grad_(True)
+    yq, yk = _rope(qr.reshape(2, s, hq * hd), kr.reshape(2, s, hk * hd), 10000.0, hq, hk)
+    ((yq * gq).sum() + (yk * gk).sum()).backward()
+    qd, kd = q.cuda().requires_grad_(True), k.cuda().requires_grad_(True)
+    # fresh non-view tensors: the kernel rotates them in place
+    zq, zk = _rope((qd * 1).reshape(2, s, hq * hd) + 0, (kd * 1).reshape(2, s, hk * hd) + 0, 10000.0, hq, hk)
+    ((zq.float() * gq.cuda()).sum() + (zk.float() * gk.cuda()).sum()).backward()
+    for got, want in ((zq, yq), (zk, yk), (qd.grad, qr.grad), (kd.grad, kr.grad)):
+        got, want = got.detach().float().cpu(), want.detach().float()
+        assert (got - want).abs().max() <= 1e-2 * want.abs().max() + 1e-3
+        assert _cos(got, want) > 0.9999

@@ -101,6 +101,60 @@ def test_r_mode_against_oracle_ragged_rows(pk, dtype, bits, method):
     assert torch.equal(pk.decompress(p).cpu(), oc.r_decompress(c))
 
 
+def test_r_mode_rows_with_more_outliers_than_the_shared_list(pk):
+    """A threshold far inside the distribution gives rows with thousands of element outliers: more than the
+    kernel's per-row shared list holds, so warp 0 regenerates the row's entries straight into the pool."""
+    x, _ = synthetic.sweep_activation(40, 4096, 0.01, dtype=torch.bfloat16, salt=77)
+    x = x.reshape(2, 20, 4096)
+    _, _, _, scale = oc.r_calibrate(x, 0.01, 1.0, 4, "per-channel", 0)
+    thr = torch.tensor(0.5)
+    c = oc.r_compress(x, thr, scale, 4, 1.0)
+    assert c.out_index.shape[1] > 40 * 600
+    p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), 4, pool_entries=40 * 4096)
+    assert torch.equal(p.codes.cpu().reshape(c.codes.shape).view(torch.uint8), c.codes.view(torch.uint8))
+    flat, val = p.outlier_coo()
+    o_flat, o_val = _oracle_coo_flat(c)
+    assert torch.equal(flat, o_flat) and torch.equal(val, o_val)
+    assert torch.equal(pk.decompress(p).cpu(), oc.r_decompress(c))
+    assert not p.overflowed() and not p.wait_expired()
+
+
+@pytest.mark.parametrize("kind,bits,method,rank", [("rms", 4, "per-channel", 4), ("ln", 8, "per-token", 0),
+                                                   ("rms", 2, "per-tensor", 0)])
+def test_r_mode_fused_norm_many_rows_per_cta(pk, kind, bits, method, rank):
+    """Reference mode with the norm fused, low-rank part staged with the row, several rows per CTA."""
+    b, seq, d = 24, 128, 1024
+    x, _ = synthetic.sweep_activation(b * seq, d, 0.01, dtype=torch.bfloat16, salt=bits + rank)
+    x = x.reshape(b, seq, d)
+    thr, L, R, scale = oc.r_calibrate(x, 0.01, 1.0, bits, method, rank, 0)
+    lr = (oc.fit_rows(L, seq) @ R).to(torch.bfloat16) if rank else None
+    w = synthetic.norm_weight(d, 0.1, dtype=torch.bfloat16)
+    bias = (0.05 * torch.randn(d, generator=torch.Generator().manual_seed(1))).to(torch.bfloat16)
+    c = oc.r_compress(x, thr, scale, bits, 1.0, L if rank else None, R if rank else None)
+    p, y, rstd, mean = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), bits,
+                                     lowrank=None if lr is None else lr.to(DEV), outlier_ratio=0.02,
+                                     norm=dict(kind=kind, weight=w.to(DEV), bias=bias.to(DEV), eps=1e-5))
+    assert torch.equal(p.codes.cpu().reshape(c.codes.shape).view(torch.uint8), c.codes.view(torch.uint8))
+    flat, val = p.outlier_coo()
+    o_flat, o_val = _oracle_coo_flat(c)
+    assert torch.equal(flat, o_flat) and torch.equal(val, o_val)
+    y_o, mean_o, rstd_o = oc.norm_forward(x, w, bias, 1e-5, kind)
+    assert ((y.float().cpu() - y_o.float()).abs() <= 1e-2 * y_o.float().abs() + 1e-3).all()
+    assert _rel_err(rstd, rstd_o) < 1e-5
+    xh = oc.r_decompress(c)
+    assert torch.equal(pk.decompress(p).cpu(), xh)
+    # consumers on the same packed record
+    dy = torch.randn(b, seq, d, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    dx_o, _, _ = oc.norm_backward(xh, dy, w.float(), mean_o, rstd_o, kind)
+    dx, _, _ = pk.norm_bwd(p, dy.to(DEV), w.float().to(DEV), rstd_o.to(DEV),
+                           None if mean_o is None else mean_o.to(DEV), kind)
+    assert _rel_err(dx, dx_o) < 1e-2
+    o = oc.silu_backward(xh, dy)
+    got = pk.act_bwd("silu", p, dy.to(DEV))
+    assert ((got.float().cpu() - o.float()).abs() <= 1e-2 * o.float().abs() + 1e-4).all()
+    assert not p.overflowed() and not p.wait_expired()
+
+
 def test_r_mode_head_layout(pk):
     x, _ = synthetic.roundtrip_activation(2, 24, 768, planted=4, dtype=torch.bfloat16, salt=3)
     heads = x.reshape(2, 24, 12, 64).permute(0, 2, 1, 3)        # [B,H,S,hd] view, as the attention code makes it

@@ -81,3 +81,15 @@ def test_norm_signatures_match_reference_text():
     fwd = [n for n in inspect.signature(EfficientMemoryRMSNormFunc.forward).parameters if n != "extra"]
     assert fwd == ["ctx", "x", "normalized_shape", "outlier_ratio", "sub_outlier_ratio", "sub_outlier_bit",
                    "sub_outlier_quantize_method", "rank", "weight", "bias", "eps", "iteration", "static_value"]
+
+
+def test_rotation_block_fits_packed_segments():
+    """Sites whose packed segments do not start on a rotation-block boundary use the largest block that fits."""
+    from hyc_lora_b200.operators._common import SiteOptions
+    s = SiteOptions(0.01, "channel", 0, 256)
+    assert s.rotate_for(4096, 4) == 256 and s.rotate_for(4096, 2) == 256
+    assert s.rotate_for(11008, 4) == 64 and s.rotate_for(11008, 8) == 256
+    assert s.rotate_for(14336, 2) == 256 and s.rotate_for(768, 4) == 64
+    s.fit_rotate = False
+    assert s.rotate_for(11008, 4) == 256
+    assert SiteOptions(0.01, "channel", 0, 0).rotate_for(11008, 4) == 0

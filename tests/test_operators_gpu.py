@@ -273,6 +273,23 @@ def test_channel_mode_modules_match_oracle():
     assert ((xd.grad.float().cpu() - o.float()).abs() <= 1e-2 * o.float().abs() + 1e-4).all()
 
 
+def test_channel_mode_wide_site_uses_fitting_rotation_block():
+    """11 008 channels at 4 bits: segments of 5 504 channels do not start on 256-block boundaries, so the
+    site rotates in blocks of 64; the result is the oracle's for that block size."""
+    from hyc_lora_b200.operators.efficient_silu import EfficientMemorySiLU
+    d = 11008
+    x = _act(2, 19, d, salt=60, gain=30.0)
+    dy = _rand(x.shape, 61)
+    ch = oc.n_select_channels(oc.n_channel_scores(x), oc.n_outlier_count(d, 0.01))
+    act = EfficientMemorySiLU(outlier_ratio=0.01, sub_outlier_bit=4, rank=0, outlier_mode="channel", rotate=256)
+    assert act.site.rotate_for(d, 4) == 64
+    xd = x.to(DEV).requires_grad_(True)
+    act(xd).backward(dy.to(DEV))
+    xh = oc.n_decompress(oc.n_compress(x.reshape(-1, d), ch, 4, 0, 64)).reshape(x.shape)
+    o = oc.silu_backward(xh, dy)
+    assert ((xd.grad.float().cpu() - o.float()).abs() <= 1e-2 * o.float().abs() + 1e-4).all()
+
+
 def test_low_rank_site_and_calibration_state_roundtrip():
     """rank > 0: the randomized SVD differs between devices, so the check is against the exact
     derivative; then a second module restored from the first one's calibration state reproduces
