@@ -43,7 +43,7 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
                                   : launch_fwd_r_fast_f32(ra, rf, norm != nullptr, stream);
     }
   }
-  const FastPlan fast = plan_fast(out, es);
+  FastPlan fast = plan_fast(out, es);
   LayoutReq req;
   fill_req_packed(&req, out, true);
   req.slot_bytes = static_cast<uint32_t>(out->cols) * es;
@@ -57,7 +57,18 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
   // the register-resident kernel frees a slot right after pass 1: two stages suffice and
   // leave room for more resident CTAs
   // (three when the norm output re-reads the staged row after the in-register rotation)
-  rc = plan_launch(req, out->rows, &plan, 0, fast.ok ? fast.threads : 0, fast.ok ? ((fast.rot == 2 && norm) ? 3 : 2) : 3);
+  const bool late_refill = fast.ok && fast.rot == 2 && norm;
+  rc = plan_launch(req, out->rows, &plan, 0, fast.ok ? fast.threads : 0, fast.ok ? (late_refill ? 3 : 2) : 3,
+                   late_refill ? 3 : 1);
+  if (rc == HYC_ERR_SMEM && fast.ok) {
+    // the row is too wide for the register-resident kernel's staging: take the generic kernel
+    fast.ok = false;
+    LayoutReq g;
+    fill_req_packed(&g, out, true);
+    g.slot_bytes = req.slot_bytes;
+    req = g;
+    rc = plan_launch(req, out->rows, &plan, 0, 0, 3);
+  }
   if (rc) return rc;
   FwdArgs a;
   memset(&a, 0, sizeof(a));

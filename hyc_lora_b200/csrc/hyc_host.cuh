@@ -97,18 +97,21 @@ struct LaunchPlan {
 // Pick threads, staging depth and CTAs per SM so that the staging rings of the
 // resident CTAs fill most of an SM's shared memory; the grid is that many CTAs
 // on every SM (or one CTA per row when there are fewer rows).
+// `min_stages`: the fewest staging slots the kernel works with (a kernel that hands a slot back one row late
+// waits forever with fewer than three).
 inline int plan_launch(const LayoutReq& r, long long rows, LaunchPlan* out, int grid_cap = 0, int force_threads = 0,
-                       int default_stages = 3) {
+                       int default_stages = 3, int min_stages = 1) {
   int threads = force_threads ? force_threads : g_tune_threads ? g_tune_threads : (r.D <= 1024 ? 64 : r.D <= 4096 ? 128 : 256);
   int stages = g_tune_stages ? g_tune_stages : default_stages;
+  if (stages < min_stages) stages = min_stages;
   if (stages > kMaxStages) stages = kMaxStages;
   SmemLayout L = make_layout(r, stages);
-  while (L.total > kSmemPerCtaMax && stages > 1) L = make_layout(r, --stages);
+  while (L.total > kSmemPerCtaMax && stages > min_stages) L = make_layout(r, --stages);
   if (L.total > kSmemPerCtaMax) return HYC_ERR_SMEM;
   int ctas = g_tune_ctas ? g_tune_ctas : 8;
   while (ctas > 1 && (static_cast<uint32_t>(ctas) * (L.total + 1024) > kSmemBudget || ctas * threads > 2048)) --ctas;
   // with few resident CTAs prefer more threads and fewer stages of a fat row
-  if (!g_tune_stages && ctas < 4 && stages > 2) {
+  if (!g_tune_stages && ctas < 4 && stages > 2 && min_stages <= 2) {
     SmemLayout L2 = make_layout(r, 2);
     int c2 = 8;
     while (c2 > 1 && (static_cast<uint32_t>(c2) * (L2.total + 1024) > kSmemBudget || c2 * threads > 2048)) --c2;

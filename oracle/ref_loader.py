@@ -16,7 +16,9 @@ import os
 import sys
 import types
 
-REFERENCE_ROOT = os.environ.get("HYC_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: HYC_REFERENCE_ROOT, else a directory named "reference" next to this repository
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REFERENCE_ROOT = os.environ.get("HYC_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference"))
 
 _cached = None
 

@@ -141,7 +141,7 @@ def test_r_mode_fused_norm_many_rows_per_cta(pk, kind, bits, method, rank):
     y_o, mean_o, rstd_o = oc.norm_forward(x, w, bias, 1e-5, kind)
     assert ((y.float().cpu() - y_o.float()).abs() <= 1e-2 * y_o.float().abs() + 1e-3).all()
     assert _rel_err(rstd, rstd_o) < 1e-5
-    xh = oc.r_decompress(c)
+    xh = oc.r_decompress(c, L if rank else None, R if rank else None)
     assert torch.equal(pk.decompress(p).cpu(), xh)
     # consumers on the same packed record
     dy = torch.randn(b, seq, d, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
