@@ -270,7 +270,9 @@ def test_n_mode_ties_zero_rows_and_nonfinite_values(pk):
     # rotation in registers (the norm output re-reads the staged row), several rows per CTA
     ("rms", torch.bfloat16, 4096, 256, 3001), ("ln", torch.bfloat16, 768, 64, 5003),
     # rotation through shared memory (segments not aligned to the block)
-    ("rms", torch.bfloat16, 11008, 256, 45)])
+    ("rms", torch.bfloat16, 11008, 256, 45),
+    # wide row, rotation in registers: needs three staging slots although shared memory is tight
+    ("rms", torch.bfloat16, 11008, 64, 1500)])
 def test_norm_forward_matches_oracle(pk, kind, dtype, d, rotate, rows):
     x, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=dtype, salt=d)
     w = synthetic.norm_weight(d, 0.1, dtype=dtype)
