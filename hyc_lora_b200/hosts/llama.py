@@ -79,15 +79,14 @@ def _rope_table(seq: int, head_dim: int, theta: float, device) -> torch.Tensor:
 
 
 class _RopeFunc(torch.autograd.Function):
-    """Rotary embedding of the query and key projections ([b, s, heads * hd] bf16, contiguous, not views) by one
+    """Rotary embedding of the query and key projections ([b * s, heads * hd] bf16 in memory, contiguous, not views) by one
     in-place kernel launch; the backward is the rotation by the negative angle, applied in place to the
     incoming gradients."""
 
     @staticmethod
-    def forward(ctx, q, k, table, hq, hk, hd):
+    def forward(ctx, q, k, table, hq, hk, hd, b, s):
         from .. import _lib
         from ..packed import _stream
-        b, s, _ = q.shape
         ctx.table, ctx.dims = table, (b * s, s, hq, hk, hd)
         _lib.check(_lib.lib.hyc_rope(q.data_ptr(), k.data_ptr(), table.data_ptr(), b * s, s, hq, hk, hd, 0, _stream()),
                    "hyc_rope")
@@ -102,7 +101,7 @@ class _RopeFunc(torch.autograd.Function):
         gq, gk = gq.contiguous().clone(), gk.contiguous().clone()
         _lib.check(_lib.lib.hyc_rope(gq.data_ptr(), gk.data_ptr(), ctx.table.data_ptr(), tokens, s, hq, hk, hd, 1,
                                      _stream()), "hyc_rope")
-        return gq, gk, None, None, None, None
+        return gq, gk, None, None, None, None, None, None
 
 
 def _rope(q, k, theta, hq, hk):
@@ -112,10 +111,17 @@ def _rope(q, k, theta, hq, hk):
     b, s, _ = q.shape
     d = q.shape[-1] // hq
     tab = _rope_table(s, d, theta, q.device)
-    if q.is_cuda and q.dtype == torch.bfloat16 and d % 16 == 0 and q.is_contiguous() and k.is_contiguous() \
-            and q._base is None and k._base is None:
-        q, k = _RopeFunc.apply(q, k, tab, hq, hk, d)
-        return q.view(b, s, hq, d), k.view(b, s, hk, d)
+    if q.is_cuda and q.dtype == torch.bfloat16 and d % 16 == 0:
+        # the kernel rotates whole tensors in place; a projection that hands out a reshaped view of its
+        # (contiguous) output is rotated through that output, since an in-place Function with two results
+        # may not be given views
+        qb = q._base if q._base is not None else q
+        kb = k._base if k._base is not None else k
+        if (q.is_contiguous() and k.is_contiguous() and qb.is_contiguous() and kb.is_contiguous()
+                and qb.numel() == q.numel() and kb.numel() == k.numel() and qb._base is None and kb._base is None
+                and qb.data_ptr() == q.data_ptr() and kb.data_ptr() == k.data_ptr()):
+            qb, kb = _RopeFunc.apply(qb, kb, tab, hq, hk, d, b, s)
+            return qb.view(b, s, hq, d), kb.view(b, s, hk, d)
     q, k = q.reshape(b, s, hq, d), k.reshape(b, s, hk, d)
     cos = torch.cat((tab[..., 0], tab[..., 0]), -1).to(q.dtype)[None, :, None, :]
     sin = torch.cat((tab[..., 1], tab[..., 1]), -1).to(q.dtype)[None, :, None, :]

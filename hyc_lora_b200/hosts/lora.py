@@ -136,10 +136,12 @@ class LoRALinear(nn.Module):
     def forward(self, x):
         # base + scaling * (A x) B^T with the scale and the add in the GEMM's epilogue (no separate
         # elementwise kernels); lora_A stays a module so that it can be swapped for the compressing linear
-        base = self.base_layer(x)
+        # (the base output is produced 2-D so that the in-place update is not an update through a view,
+        # which autograd would undo with full-size copies in backward)
+        base = self.base_layer(x.reshape(-1, x.shape[-1]))
         h = self.lora_A(x)
-        base.view(-1, base.shape[-1]).addmm_(h.reshape(-1, h.shape[-1]), self.lora_B.weight.t(), alpha=self.scaling)
-        return base
+        base.addmm_(h.reshape(-1, h.shape[-1]), self.lora_B.weight.t(), alpha=self.scaling)
+        return base.view(*x.shape[:-1], base.shape[-1])
 
 
 def lora_parameters(model: nn.Module):
