@@ -513,7 +513,9 @@ static int wgrad_plan(const hyc_packed* saved, int rank, WgradPlan* pl) {
   // tensor memory: 512 columns per SM shared by the resident CTAs
   if (per_sm * cols > 512u) per_sm = 512 / cols;
   long long splits = static_cast<long long>(sms) * per_sm / tiles;
-  const long long max_splits = (saved->rows + kChunk - 1) / kChunk;
+  // every slice costs a partial slab (written, then read by the finish kernel) and a prologue/epilogue:
+  // keep at least four chunks per slice
+  const long long max_splits = ((saved->rows + kChunk - 1) / kChunk + 3) / 4;
   if (splits > max_splits) splits = max_splits;
   if (splits > 64) splits = 64;
   if (splits < 1) splits = 1;
