@@ -37,6 +37,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 ROWS, COLS, BITS, FRACTION, GROUP, ROTATE = 65536, 4096, 4, 0.01, 0, 0
+# rows per piece of the end-to-end pipeline (measured: 8192 -> 81 GB/s, 4096 -> 81, 2048 -> 77, 1024 -> 70: the copies back to the host bound it)
+E2E_PIECE_ROWS = int(os.environ.get("HYC_E2E_PIECE_ROWS", "8192"))
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -264,7 +266,7 @@ def run_ours(args):
     xin = torch.empty_like(x)
     # The rows go through in pieces so that the copy of piece i+1 to the device, the kernel on piece i
     # and the copy of piece i-1 back to the host overlap (PCIe is full duplex): three streams, events.
-    piece = 8192
+    piece = E2E_PIECE_ROWS
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     pieces = [(r0, min(ROWS, r0 + piece)) for r0 in range(0, ROWS, piece)]
 
@@ -326,7 +328,7 @@ def run_ours(args):
                          "kernel": "hyc::fwd_n_fast_kernel<bf16, 4, norm, 2, 0>"},
             "e2e": {"value": (bytes_per_step * e2e_steps * world) / (e2e_ms / 1e3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "pipeline": "8 pieces of 8192 rows; H2D, kernel and D2H on three streams"},
+                    "pipeline": f"{len(pieces)} pieces of {piece} rows; H2D, kernel and D2H on three streams"},
             "gpu_launches": args.steps,
             "clocks": clocks,
         }
