@@ -16,7 +16,9 @@
 // staging buffer may be overwritten (two buffers; the packed bytes of chunk c+1 are already in
 // registers while chunk c is converted).  At the end four warps read the accumulators back
 // with tcgen05.ld and store one partial [rank, D] slab per token slice; wgrad_finish_kernel adds
-// the slabs, rotates the rows back and drops in the outlier channels' columns.
+// the slabs, rotates the rows back and drops in the outlier channels' columns.  Those columns,
+// grad^T * out_value, come from extra CTAs of the same launch whose A operand is the stored
+// bf16 outlier values (128 outlier channels per CTA) instead of converted codes.
 //
 // Channel-outlier mode only.  Outlier channels carry the zero code, so their columns come out
 // as zero here; the caller adds G^T * out_value there.  With rotation the kernel contracts the
@@ -106,6 +108,13 @@ struct WgradArgs {
   long long tokens_per_split;
   float* partials;            // [splits][rank][D]
   uint32_t tmem_cols;
+  // outlier channels: CTAs with blockIdx.x >= tiles contract the stored bf16 values of 128 outlier
+  // channels each instead of dequantised codes
+  int tiles;                  // code tiles (blockIdx.x < tiles)
+  int side_split;             // side CTAs per outlier tile and token slice (each takes a part of the slice)
+  int k;                      // outlier channels
+  const __nv_bfloat16* out_value;   // [T, k]
+  float* side;                // [splits][k][rank]
 };
 
 // A staging: [token group of 8][unit of 8 channels (16)][8 tokens][8 channels] bf16
@@ -146,9 +155,18 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int byte0 = blockIdx.x * kTileM;                 // first packed byte column of this CTA
-  const long long t_begin = static_cast<long long>(blockIdx.y) * a.tokens_per_split;
-  const long long t_end = min(p.rows, t_begin + a.tokens_per_split);
+  const bool is_side = static_cast<int>(blockIdx.x) >= a.tiles;
+  const int side_x = is_side ? static_cast<int>(blockIdx.x) - a.tiles : 0;
+  const int side_sub = side_x % a.side_split;            // which part of the token slice a side CTA takes
+  const int side_j0 = (side_x / a.side_split) * kTileM;  // first outlier of a side CTA
+  const int byte0 = is_side ? 0 : blockIdx.x * kTileM;   // first packed byte column of this CTA
+  long long t_begin = static_cast<long long>(blockIdx.y) * a.tokens_per_split;
+  long long t_end = min(p.rows, t_begin + a.tokens_per_split);
+  if (is_side && a.side_split > 1) {
+    const long long sub_len = ((a.tokens_per_split + a.side_split - 1) / a.side_split + kChunk - 1) / kChunk * kChunk;
+    t_begin += side_sub * sub_len;
+    t_end = min(t_end, t_begin + sub_len);
+  }
   const int nchunks = t_end > t_begin ? static_cast<int>((t_end - t_begin + kChunk - 1) / kChunk) : 0;
   const uint32_t idesc = instr_desc(npad);
   // conversion mapping: lane = token-in-group (k0) + 8 * (unit & 3); a warp item = (token group, unit >> 2)
@@ -157,7 +175,8 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
   const int b_per_tg = (npad / 8 + 3) / 4;                         // 1 or 2 B items per token group
   // B tiles per buffer: the scale is folded into the gradient operand, so group scales (one per
   // 128-channel tile, i.e. per segment) need one scaled copy of the gradient rows per segment
-  const int nb = (BITS < 8 && p.group) ? NSEG : 1;
+  const int nb = (BITS < 8 && p.group && !is_side) ? NSEG : 1;
+  const int nseg_eff = is_side ? 1 : NSEG;               // a side CTA holds one tile of outlier channels
   // Per-thread source pointers and shared-memory offsets are set up once and advanced by a
   // constant per chunk.  Tokens past the end of the slice contribute nothing because their
   // gradient rows are stored as zeros; the code rows only have to be readable, so their
@@ -198,8 +217,8 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
 #pragma unroll
     for (int i = 0; i < kAItems; ++i) {
       const unsigned char* src = a_src[i] < a_last[i] ? a_src[i] : a_last[i];
-      cb_reg[i] = ld_stream_u2(src);
-      if (BITS == 8) {
+      cb_reg[i] = is_side ? make_uint2(0u, 0u) : ld_stream_u2(src);
+      if (BITS == 8 && !is_side) {
         const float* sp = a_sc[i] < sc_last + G ? a_sc[i] : sc_last;
         sc_reg[i] = __ldg(sp);
         a_sc[i] += kChunk * G;
@@ -214,7 +233,7 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
       if (BITS < 8) {
 #pragma unroll
         for (int s = 0; s < NSEG; ++s)
-          if (s < nb) gs_reg[s] = __ldg(b_sc + s * b_sc_seg);
+          if (s < nb) gs_reg[s] = is_side ? 1.f : __ldg(b_sc + s * b_sc_seg);
       }
     }
     b_t += kChunk;
@@ -245,6 +264,24 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
     // ---- A operand.  Below 8 bits: the integer code minus its offset as an exact bf16 (a field is
     // dropped into the mantissa of 128.0 with one byte permute per pair, then 128 + offset is
     // subtracted in packed bf16 arithmetic).  8 bits: dequantised values.
+    if (is_side) {
+      // outlier values are bf16 already: eight scalar loads per (token, unit) -- the rows of
+      // out_value are k elements long, not 16-byte aligned -- packed into one 16-byte store
+#pragma unroll
+      for (int i = 0; i < kAItems; ++i) {
+        const int item = warp + i * (kWgThreads / 32);
+        const int tg = item >> 2, unit = ((item & 3) << 2) + u_lo;
+        const int j0 = side_j0 + (unit << 3);
+        long long t = t_begin + static_cast<long long>(c) * kChunk + tg * 8 + k0;
+        if (t > p.rows - 1) t = p.rows - 1;           // readable; such tokens meet zero gradient rows
+        const unsigned short* src = reinterpret_cast<const unsigned short*>(a.out_value) + t * a.k + j0;
+        uint32_t h[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) h[e] = (j0 + e < a.k) ? static_cast<uint32_t>(__ldg(src + e)) : 0u;
+        st_shared_u4(abase + a_dst[i], make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16),
+                                                  h[6] | (h[7] << 16)));
+      }
+    } else {
 #pragma unroll
     for (int i = 0; i < kAItems; ++i) {
 #pragma unroll
@@ -267,6 +304,7 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
         }
         st_shared_u4(abase + s * kAStage + a_dst[i], v);
       }
+    }
     }
     // ---- B operand: gradient rows, times the token (or token-and-tile) scale below 8 bits
     if (b_own) {
@@ -299,6 +337,7 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
       const uint32_t acc0 = c > 0 ? 1u : 0u;
 #pragma unroll
       for (int s = 0; s < NSEG; ++s) {
+        if (s >= nseg_eff) break;
 #pragma unroll
         for (int ks = 0; ks < kChunk / 16; ++ks) {
           umma_bf16(tmem_base + static_cast<uint32_t>(s) * static_cast<uint32_t>(npad),
@@ -323,7 +362,26 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
   __syncthreads();
   const bool failed = *fail != 0;
   if (failed && tid == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
-  if (warp < 4) {
+  if (warp < 4 && is_side) {
+    // accumulator row = outlier channel; partial [slice][outlier][rank]
+    const int j = side_j0 + warp * 32 + lane;
+    float* dst = a.side + ((static_cast<long long>(blockIdx.y) * a.side_split + side_sub) * a.k + j) * a.rank;
+    for (int n0 = 0; n0 < npad; n0 += 16) {
+      uint32_t v[16];
+      if (nchunks > 0 && !failed) {
+        tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(n0), v);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) v[q] = 0u;
+      }
+      if (j < a.k) {
+#pragma unroll
+        for (int q = 0; q < 16; ++q)
+          if (n0 + q < a.rank) dst[n0 + q] = __uint_as_float(v[q]);
+      }
+    }
+  } else if (warp < 4) {
     float* slab = a.partials + static_cast<long long>(blockIdx.y) * a.rank * D;
 #pragma unroll
     for (int s = 0; s < NSEG; ++s) {
@@ -385,75 +443,11 @@ __global__ void wgrad_finish_kernel(const float* __restrict__ partials, int spli
     *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(rowbuf + c);
 }
 
-// ---- columns of the outlier channels: out[n, channels[j]] = sum_t grad[t, n] * out_value[t, j].
-// A CTA owns a token slice and walks it in chunks of kSideChunk tokens: the chunk's gradient rows
-// and outlier values (both contiguous in memory) are copied to shared memory with 16-byte loads
-// by all threads, then a thread owning (outlier j, 8 consecutive ranks) accumulates over the
-// chunk.  A warp covers 4 outliers x 8 rank groups at rank 64: the value read is a broadcast, the
-// gradient read one conflict-free 128-byte line.  Slices are summed in a fixed order by
-// wgrad_finish_kernel, which also writes them to the channel columns.
-constexpr int kSideChunk = 64;
-
-__global__ void wgrad_side_kernel(const __nv_bfloat16* __restrict__ out_value, const __nv_bfloat16* __restrict__ grad,
-                                  long long rows, long long rows_per, int k, int rank, float* __restrict__ part) {
-  extern __shared__ __align__(16) unsigned char side_smem[];
-  __nv_bfloat16* sg = reinterpret_cast<__nv_bfloat16*>(side_smem);              // [kSideChunk][rank]
-  __nv_bfloat16* sv = sg + kSideChunk * rank;                                    // [kSideChunk][k] (+ padding)
-  const int r8 = rank >> 3;
-  const int units = k * r8;
-  const long long t0 = blockIdx.x * rows_per;   // rows_per is a multiple of kSideChunk: chunk starts stay 16-byte aligned
-  long long t1 = t0 + rows_per;
-  if (t1 > rows) t1 = rows;
-  constexpr int kMaxOwn = 4;                    // units per thread (host sizes the CTA so that this covers all)
-  float acc[kMaxOwn][8];
-#pragma unroll
-  for (int o = 0; o < kMaxOwn; ++o)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[o][e] = 0.f;
-  for (long long c0 = t0; c0 < t1; c0 += kSideChunk) {
-    const int nt = static_cast<int>(t1 - c0 < kSideChunk ? t1 - c0 : kSideChunk);
-    const int g16 = nt * rank * 2 / 16;                    // rank % 8 == 0: whole 16-byte pieces
-    const uint4* gsrc = reinterpret_cast<const uint4*>(grad + c0 * rank);
-    for (int i = threadIdx.x; i < g16; i += blockDim.x) reinterpret_cast<uint4*>(sg)[i] = __ldg(gsrc + i);
-    const int vbytes = nt * k * 2;
-    const int v16 = vbytes / 16;
-    const uint4* vsrc = reinterpret_cast<const uint4*>(out_value + c0 * k);
-    for (int i = threadIdx.x; i < v16; i += blockDim.x) reinterpret_cast<uint4*>(sv)[i] = __ldg(vsrc + i);
-    for (int i = v16 * 8 + threadIdx.x; i < nt * k; i += blockDim.x) sv[i] = out_value[c0 * k + i];   // ragged tail
-    __syncthreads();
-#pragma unroll
-    for (int o = 0; o < kMaxOwn; ++o) {
-      const int u = threadIdx.x + o * blockDim.x;
-      if (u < units) {
-        const int j = u / r8, n8 = u - j * r8;
-#pragma unroll 4
-        for (int t = 0; t < nt; ++t) {
-          const float v = __bfloat162float(sv[t * k + j]);
-          float g[8];
-          unpack_bf16x8(*reinterpret_cast<const uint4*>(sg + t * rank + (n8 << 3)), g);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[o][e] = fmaf(v, g[e], acc[o][e]);
-        }
-      }
-    }
-    __syncthreads();
-  }
-#pragma unroll
-  for (int o = 0; o < kMaxOwn; ++o) {
-    const int u = threadIdx.x + o * blockDim.x;
-    if (u < units) {
-      const int j = u / r8, n8 = u - j * r8;
-      float* dst = part + (static_cast<long long>(blockIdx.x) * k + j) * rank + (n8 << 3);
-      *reinterpret_cast<float4*>(dst) = make_float4(acc[o][0], acc[o][1], acc[o][2], acc[o][3]);
-      *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[o][4], acc[o][5], acc[o][6], acc[o][7]);
-    }
-  }
-}
-
 struct WgradPlan {
   int splits;          // token slices of the tensor-core kernel
-  int side_slices;     // token slices of the outlier-column kernel (0: no outlier channels)
-  long long side_rows_per;
+  int side_slices;     // token slices holding outlier-channel partials (0: no outlier channels)
+  int side_tiles;      // extra CTAs per token slice: tiles of 128 outlier channels x side_split
+  int side_split;
   uint32_t smem_bytes, tmem_cols;
   int npad;
   long long scratch_floats;
@@ -512,7 +506,12 @@ static int wgrad_plan(const hyc_packed* saved, int rank, WgradPlan* pl) {
   if (per_sm < 1) return HYC_ERR_CUDA;
   // tensor memory: 512 columns per SM shared by the resident CTAs
   if (per_sm * cols > 512u) per_sm = 512 / cols;
-  long long splits = static_cast<long long>(sms) * per_sm / tiles;
+  // A side CTA has no register prefetch and takes about as long per chunk as a 4-bit code CTA; with 8-bit codes
+  // (one segment per chunk) the code CTAs are faster, so two side CTAs share a token slice.
+  pl->side_split = bits == 8 ? 2 : 1;
+  const int side_tiles = saved->n_channels > 0 ? (saved->n_channels + kTileM - 1) / kTileM * pl->side_split : 0;
+  pl->side_tiles = side_tiles;
+  long long splits = static_cast<long long>(sms) * per_sm / (tiles + side_tiles);
   // every slice costs a partial slab (written, then read by the finish kernel) and a prologue/epilogue:
   // keep at least four chunks per slice
   const long long max_splits = ((saved->rows + kChunk - 1) / kChunk + 3) / 4;
@@ -520,15 +519,8 @@ static int wgrad_plan(const hyc_packed* saved, int rank, WgradPlan* pl) {
   if (splits > 64) splits = 64;
   if (splits < 1) splits = 1;
   pl->splits = static_cast<int>(splits);
-  pl->side_slices = 0;
-  pl->side_rows_per = 0;
-  if (saved->n_channels > 0) {
-    // about two CTAs per SM, slices a multiple of the chunk
-    long long per = (saved->rows + 2 * sms - 1) / (2 * sms);
-    per = (per + kSideChunk - 1) / kSideChunk * kSideChunk;
-    pl->side_rows_per = per;
-    pl->side_slices = static_cast<int>((saved->rows + per - 1) / per);
-  }
+  // outlier-channel partials: one [k, rank] block per token slice
+  pl->side_slices = side_tiles ? pl->splits * pl->side_split : 0;
   pl->scratch_floats = static_cast<long long>(pl->splits) * rank * D +
                        static_cast<long long>(pl->side_slices) * saved->n_channels * rank;
   return HYC_OK;
@@ -547,7 +539,6 @@ static int wgrad_check(const hyc_packed* saved, int rank) {
     return HYC_ERR_SHAPE;
   if (saved->rotate && D % saved->rotate != 0) return HYC_ERR_SHAPE;
   if (saved->n_channels < 0 || saved->n_channels > D) return HYC_ERR_SHAPE;
-  if (static_cast<long long>(saved->n_channels) * (rank >> 3) > 2048) return HYC_ERR_SHAPE;   // outlier-column kernel: 4 units x 512 threads
   return HYC_OK;
 }
 
@@ -600,8 +591,13 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
   a.tokens_per_split = (per + kChunk - 1) / kChunk * kChunk;
   a.partials = partials;
   a.tmem_cols = pl.tmem_cols;
+  a.tiles = D * saved->bits / 8 / kTileM;
+  a.side_split = pl.side_split;
+  a.k = saved->n_channels;
+  a.out_value = static_cast<const __nv_bfloat16*>(saved->out_value);
+  a.side = partials + static_cast<long long>(splits) * slab;
   const uint32_t smem_bytes = pl.smem_bytes;
-  const dim3 grid(D * saved->bits / 8 / kTileM, splits);
+  const dim3 grid(a.tiles + pl.side_tiles, splits);
 #define HYC_WG(B)                                                                                         \
   {                                                                                                       \
     auto kern = lora_wgrad_kernel<B>;                                                                     \
@@ -615,18 +611,6 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
   if (cudaGetLastError() != cudaSuccess) return HYC_ERR_CUDA;
   const int k = saved->n_channels;
   const float* side = partials + static_cast<long long>(splits) * slab;
-  if (pl.side_slices > 0) {
-    const int units = k * (rank >> 3);
-    const int own = (units + 511) / 512;                 // units per thread, at most 4 (wgrad_check)
-    const int threads = ((units + own - 1) / own + 31) / 32 * 32;
-    const size_t sm = static_cast<size_t>(kSideChunk) * (rank + k) * 2 + 16;
-    if (sm > 48 * 1024)
-      if (cudaFuncSetAttribute(wgrad_side_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
-        return HYC_ERR_CUDA;
-    wgrad_side_kernel<<<pl.side_slices, threads, sm, stream>>>(static_cast<const __nv_bfloat16*>(saved->out_value), a.grad,
-                                                               saved->rows, pl.side_rows_per, k, rank,
-                                                               const_cast<float*>(side));
-  }
   {
     // parts of a row are independent when they hold whole rotation blocks
     const int unit = saved->rotate ? saved->rotate : 128;

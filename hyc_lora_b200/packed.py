@@ -341,9 +341,8 @@ def select_channels(score: torch.Tensor, k: int) -> torch.Tensor:
 
 def lora_wgrad_supported(p: Packed, rank: int) -> bool:
     """Formats the tensor-core weight-gradient kernel takes."""
-    k = 0 if p.channels is None else p.channels.numel()
     return (p.mode == "N" and rank % 8 == 0 and 8 <= rank <= 64 and (p.cols * p.bits // 8) % 128 == 0
-            and p.rows > 0 and k * (rank // 8) <= 2048)
+            and p.rows > 0)
 
 
 def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False) -> torch.Tensor:

@@ -195,8 +195,8 @@ int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* ch
  * writing X_hat to memory.  grad is bf16 [rows, rank] (contiguous, 16-byte aligned), rank a
  * multiple of 8 in [8, 64]; cols*bits/8 must be a multiple of 128.  `partials` is 16-byte aligned
  * scratch of hyc_lora_wgrad_scratch_floats(saved, rank) floats (a negative return is a hyc_status).
- * The columns of the outlier channels are out[:, channels] = grad^T * out_value, computed by a
- * second pair of kernels in the same call; with rotation the result already includes the inverse
+ * The columns of the outlier channels are out[:, channels] = grad^T * out_value, computed by extra
+ * thread blocks of the same tensor-core kernel; with rotation the result already includes the inverse
  * rotation.  The sums are taken in a fixed order (no atomics): the result is reproducible. */
 int64_t hyc_lora_wgrad_scratch_floats(const hyc_packed* saved, int32_t rank);
 int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, float* out, float* partials, void* stream);
