@@ -362,14 +362,18 @@ def test_activation_backward_matches_oracle(pk, op, mode, bits, gdtype, d, rotat
 
 # ------------------------------------------------------------------ tensor-core weight gradient
 
-@pytest.mark.parametrize("rows,d,bits,group,rotate,rank", [
-    (512, 4096, 4, 0, 0, 64), (2048, 4096, 4, 0, 256, 64), (300, 768, 4, 0, 0, 16), (1000, 4096, 2, 128, 0, 64),
-    (777, 4096, 8, 0, 256, 16), (64, 11008, 4, 0, 0, 64), (4096, 1024, 4, 128, 64, 32), (70, 4096, 4, 0, 0, 8)])
-def test_lora_weight_gradient_from_codes(pk, rows, d, bits, group, rotate, rank):
-    x, _ = synthetic.sweep_activation(rows, d, 0.01, salt=rank + bits)
+@pytest.mark.parametrize("rows,d,bits,group,rotate,rank,frac", [
+    (512, 4096, 4, 0, 0, 64, 0.01), (2048, 4096, 4, 0, 256, 64, 0.01), (300, 768, 4, 0, 0, 16, 0.01),
+    (1000, 4096, 2, 128, 0, 64, 0.01), (777, 4096, 8, 0, 256, 16, 0.01), (64, 11008, 4, 0, 0, 64, 0.01),
+    (4096, 1024, 4, 128, 64, 32, 0.01), (70, 4096, 4, 0, 0, 8, 0.01),
+    # more than 128 outlier channels (two outlier tiles), 8-bit codes (two outlier CTAs per token slice), no outliers
+    (3000, 4096, 4, 0, 256, 64, 0.05), (5000, 4096, 8, 0, 0, 64, 0.04), (900, 2048, 2, 0, 0, 32, 0.0)])
+def test_lora_weight_gradient_from_codes(pk, rows, d, bits, group, rotate, rank, frac):
+    x, _ = synthetic.sweep_activation(rows, d, max(frac, 0.005), salt=rank + bits)
     g = torch.randn(rows, rank, generator=torch.Generator().manual_seed(rank)).to(torch.bfloat16)
-    ch = oc.n_select_channels(oc.n_channel_scores(x), oc.n_outlier_count(d, 0.01))
-    p = pk.compress_n(x.to(DEV), ch.to(DEV), bits, group, rotate)
+    k = oc.n_outlier_count(d, frac)
+    ch = oc.n_select_channels(oc.n_channel_scores(x), k)
+    p = pk.compress_n(x.to(DEV), ch.to(DEV) if k else None, bits, group, rotate)
     assert pk.lora_wgrad_supported(p, rank)
     dw = pk.lora_wgrad(p, g.to(DEV))
     xh = oc.n_decompress(oc.n_compress(x, ch, bits, group, rotate))
