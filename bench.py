@@ -368,8 +368,13 @@ def train_step_bench(args, world, rank, dev, barrier):
     from hyc_lora_b200 import synthetic
     from hyc_lora_b200.hosts.step import build_trainer
 
-    batch, seq, vocab = 4, 512, 32000
-    trainer = build_trainer("llama2_7b", layers=args.step_layers, bits=4, outlier_ratio=0.01, rotate=256, device=dev)
+    # --step-config mistral_7b: configuration 4 (Mistral-7B shape, GQA 32/8 heads, FFN 14336, batch 2 x 2048 tokens per
+    # GPU, INT2 activations with 2 % outlier channels, no rotation)
+    mistral = args.step_config == "mistral_7b"
+    batch, seq, vocab = (2, 2048, 32000) if mistral else (4, 512, 32000)
+    bits, ratio, rotate = (2, 0.02, 0) if mistral else (4, 0.01, 256)
+    trainer = build_trainer("mistral_7b" if mistral else "llama2_7b", layers=args.step_layers, bits=bits,
+                            outlier_ratio=ratio, rotate=rotate, device=dev)
     ids_host = synthetic.token_ids(3, batch, seq, vocab, salt=rank).pin_memory()
     ids = torch.empty_like(ids_host, device=dev)
     loss_host = torch.empty((), dtype=torch.float32).pin_memory()
@@ -401,9 +406,10 @@ def train_step_bench(args, world, rank, dev, barrier):
     return {"metric": "7B HyC-LoRA train tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s",
             "ms_per_step": ms / steps, "steps": steps, "loss": float(loss_host.item()), "cuda_graph": bool(graphed),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
-            "config": {"model": "LLaMA-2-7B shape, random init, 4-bit codebook base (block 64)",
+            "config": {"model": ("Mistral-7B" if mistral else "LLaMA-2-7B") + " shape, random init, 4-bit codebook base (block 64)",
                        "layers": trainer.model.config.layers, "lora_r": 64, "trainable_params": trainer.trainable(),
-                       "batch_per_gpu": batch, "seq_len": seq, "activations": "INT4, 1% outlier channels, rotate 256",
+                       "batch_per_gpu": batch, "seq_len": seq,
+                       "activations": f"INT{bits}, {ratio:.0%} outlier channels, " + (f"rotate {rotate}" if rotate else "no rotation"),
                        "parallelism": f"dp{world}", "attention": "torch scaled_dot_product_attention (causal)",
                        "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": 4}}
 
@@ -540,6 +546,8 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="add per-kernel numbers for the operator sweep")
     ap.add_argument("--no-step", action="store_true", help="skip the 7B-shaped training step")
     ap.add_argument("--step-layers", type=int, default=None, help="decoder layers of the step model (default 32)")
+    ap.add_argument("--step-config", default="llama2_7b", choices=["llama2_7b", "mistral_7b"],
+                    help="training-step configuration: 3 (LLaMA-2-7B shape, default) or 4 (Mistral-7B shape)")
     ap.add_argument("--step-steps", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true", help="run the training step eagerly instead of from a CUDA graph")
     ap.add_argument("--case", default=None, help="profiling aid: run only this kernel (see run_case)")
