@@ -420,25 +420,38 @@ def sweep(packed, synthetic, oc, x, w, peak):
     rows_all, d = x.shape
     out = []
 
-    def timed(fn, nbytes, name, reps=10):
-        for _ in range(3):
-            fn()
+    def timed(fn, nbytes, name, reps=16):
+        """fn(i): one call on input set i.  The calls are recorded in a CUDA graph (so that host overhead of the
+        Python wrappers does not hide short kernels) and cycle through input sets whose total size exceeds L2."""
+        for i in range(3):
+            fn(i)
         torch.cuda.synchronize()
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            fn(0)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(reps):
+                    fn(i)
+        torch.cuda.synchronize()
+        graph.replay()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(reps):
-            fn()
+        for _ in range(3):
+            graph.replay()
         b.record()
         torch.cuda.synchronize()
-        ms = a.elapsed_time(b) / reps
+        ms = a.elapsed_time(b) / (3 * reps)
         out.append({"kernel": name, "ms": round(ms, 4), "GBps": round(nbytes / ms / 1e6, 1),
                     "frac": round(nbytes / ms / 1e6 / peak, 3)})
 
     norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
     score = packed.channel_absmax(x)
-    dy = torch.randn(16384, d, device=x.device, dtype=torch.bfloat16)
     for rows in (4096, 16384, 65536):
-        xs = x[:rows]
+        # input sets: disjoint row ranges of x, 537 MB in total, visited round-robin
+        sets = [x[i * rows:(i + 1) * rows] for i in range(rows_all // rows)]
+        n = len(sets)
+        dys = [torch.randn(rows, d, device=x.device, dtype=torch.bfloat16) for _ in range(min(n, 4))] if rows != 65536 else []
         for frac in (0.005, 0.01, 0.02):
             k = oc.n_outlier_count(d, frac)
             ch = packed.select_channels(score, k)
@@ -449,17 +462,20 @@ def sweep(packed, synthetic, oc, x, w, peak):
                             continue
                         g = 1 if group == 0 else d // group
                         tag = f"T={rows} f={frac} b={bits} g={group} rot={rotate}"
-                        timed(lambda: packed.compress_n(xs, ch, bits, group, rotate, norm=norm),
+                        timed(lambda i: packed.compress_n(sets[i % n], ch, bits, group, rotate, norm=norm),
                               algorithmic_bytes_per_row(d, bits, k, g) * rows, "norm+compress " + tag)
                         if frac == 0.01:
-                            p = packed.compress_n(xs, ch, bits, group, rotate)
+                            ps = [packed.compress_n(s_, ch, bits, group, rotate) for s_ in sets]
                             base = d * bits // 8 + 2 * k + 4 * g
-                            timed(lambda: packed.decompress(p), (base + 2 * d) * rows, "decompress " + tag)
-                            if rows == 16384:
+                            timed(lambda i: packed.decompress(ps[i % n]), (base + 2 * d) * rows, "decompress " + tag)
+                            if rows != 65536:
                                 rstd = torch.ones(rows, device=x.device)
-                                timed(lambda: packed.norm_bwd(p, dy, w, rstd, None, "rms"), (base + 4 + 4 * d) * rows,
-                                      "norm_bwd " + tag)
-                                timed(lambda: packed.act_bwd("silu", p, dy), (base + 4 * d) * rows, "silu_bwd " + tag)
+                                timed(lambda i: packed.norm_bwd(ps[i % n], dys[i % len(dys)], w, rstd, None, "rms"),
+                                      (base + 4 + 4 * d) * rows, "norm_bwd " + tag)
+                                timed(lambda i: packed.act_bwd("silu", ps[i % n], dys[i % len(dys)]), (base + 4 * d) * rows,
+                                      "silu_bwd " + tag)
+                            del ps
+        del dys
     # dequant-fused tensor-core weight gradient vs. decompress + library GEMM
     for rows, bits, rank in ((65536, 4, 64), (65536, 4, 16), (65536, 2, 64), (65536, 8, 64), (2048, 4, 64)):
         xs = x[:rows]
@@ -469,8 +485,8 @@ def sweep(packed, synthetic, oc, x, w, peak):
         g = torch.randn(rows, rank, device=x.device, dtype=torch.bfloat16)
         nbytes = rows * (d * bits // 8 + 2 * rank + 4 + 2 * k) + 4 * rank * d
         before = len(out)
-        timed(lambda: packed.lora_wgrad(p, g), nbytes, f"lora_wgrad tcgen05 T={rows} b={bits} r={rank}")
-        timed(lambda: packed.lora_wgrad(p, g, force_library=True), nbytes,
+        timed(lambda i: packed.lora_wgrad(p, g), nbytes, f"lora_wgrad tcgen05 T={rows} b={bits} r={rank}")
+        timed(lambda i: packed.lora_wgrad(p, g, force_library=True), nbytes,
               f"lora_wgrad decompress+library GEMM T={rows} b={bits} r={rank}")
         for rec in out[before:]:
             rec["TFLOPs"] = round(2.0 * rows * rank * d / (rec["ms"] * 1e-3) / 1e12, 1)
@@ -481,8 +497,8 @@ def sweep(packed, synthetic, oc, x, w, peak):
         thr, L, R, scale = oc.r_calibrate(xc, 0.01, 1.0, bits, "per-channel", 0)
         thr, scale = thr.to(x.device), scale.to(x.device)
         nb = (2 * d + d * bits // 8 + 8) * 16384 + int(0.02 * 16384 * d) * 4
-        timed(lambda: packed.compress_r(xs, thr, scale, bits), nb, f"R-mode compress T=16384 b={bits} per-channel")
-        timed(lambda: packed.compress_r(xs, thr, scale, bits, norm=norm), nb + (2 * d + 4) * 16384,
+        timed(lambda i: packed.compress_r(xs, thr, scale, bits), nb, f"R-mode compress T=16384 b={bits} per-channel")
+        timed(lambda i: packed.compress_r(xs, thr, scale, bits, norm=norm), nb + (2 * d + 4) * 16384,
               f"R-mode norm+compress T=16384 b={bits} per-channel")
     return out
 
