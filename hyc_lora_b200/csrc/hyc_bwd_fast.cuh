@@ -361,6 +361,10 @@ __global__ void __launch_bounds__(512, 2) decompress_n_fast_kernel(const __grid_
   FeedSetup fs = feed_setup(smem, a.L);
   fs.feed.add(p.codes, static_cast<uint32_t>(D) * BITS / 8, 0);
   if (ROT == 3 && p.lowrank) fs.feed.add(p.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr, p.seq);
+  // the first rows start travelling before the per-CTA tables are set up
+  const long long rows = p.rows, stride = gridDim.x;
+  long long row = blockIdx.x;
+  fs.feed.prologue(row, rows, stride);
   __nv_bfloat16* csc = reinterpret_cast<__nv_bfloat16*>(smem + a.L.off_csc);
   if (ROT == 3) {
     if (p.scale_kind == kScaleChannel)
@@ -379,9 +383,6 @@ __global__ void __launch_bounds__(512, 2) decompress_n_fast_kernel(const __grid_
     ooff[r] = c * a.chunk_stride + (g.col[r] - c * clen);
   }
   __syncthreads();
-  const long long rows = p.rows, stride = gridDim.x;
-  long long row = blockIdx.x;
-  fs.feed.prologue(row, rows, stride);
   uint2 meta_pref = (ROT == 3 && row < rows) ? p.row_meta[row] : make_uint2(0u, 0u);
   int st = 0;
   uint32_t ph = 0;
@@ -467,11 +468,15 @@ __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_con
   fs.feed.add(p.codes, cb, 0);
   fs.feed.add(a.g, static_cast<uint32_t>(D) * sizeof(GT), off_g);
   if (PROD) fs.feed.add(a.p2.codes, cb, off_c2);
+  if (ROT == 3 && p.lowrank) fs.feed.add(p.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr, p.seq);
+  if (ROT == 3 && PROD && a.p2.lowrank) fs.feed.add(a.p2.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr2, a.p2.seq);
+  // the first rows start travelling before the per-CTA tables are set up
+  const long long rows = p.rows, stride = gridDim.x;
+  long long row = blockIdx.x;
+  fs.feed.prologue(row, rows, stride);
   __nv_bfloat16* csc = reinterpret_cast<__nv_bfloat16*>(smem + a.L.off_csc);
   __nv_bfloat16* csc2 = reinterpret_cast<__nv_bfloat16*>(smem + a.L.off_csc2);
   if (ROT == 3) {
-    if (p.lowrank) fs.feed.add(p.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr, p.seq);
-    if (PROD && a.p2.lowrank) fs.feed.add(a.p2.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr2, a.p2.seq);
     if (p.scale_kind == kScaleChannel)
       for (int c = threadIdx.x; c < D; c += blockDim.x) csc[c] = p.scale[c];
     if (PROD && a.p2.scale_kind == kScaleChannel)
@@ -483,9 +488,6 @@ __global__ void __launch_bounds__(512, 2) act_bwd_n_fast_kernel(const __grid_con
   Groups<BITS, UPT, ROT> g;
   g.init(D);
   __syncthreads();
-  const long long rows = p.rows, stride = gridDim.x;
-  long long row = blockIdx.x;
-  fs.feed.prologue(row, rows, stride);
   uint2 meta_pref = (ROT == 3 && row < rows) ? p.row_meta[row] : make_uint2(0u, 0u);
   uint2 meta_pref2 = (ROT == 3 && PROD && row < rows) ? a.p2.row_meta[row] : make_uint2(0u, 0u);
   int st = 0;
@@ -614,6 +616,10 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
   fs.feed.add(p.codes, cb, 0);
   fs.feed.add(a.dy, static_cast<uint32_t>(D) * sizeof(GT), off_g);
   if (ROT == 3 && p.lowrank) fs.feed.add(p.lowrank, static_cast<uint32_t>(D) * 2, a.L.off_lr, p.seq);
+  // the first rows start travelling before the per-CTA tables are set up
+  const long long rows = p.rows, stride = gridDim.x;
+  long long row = blockIdx.x;
+  fs.feed.prologue(row, rows, stride);
   __nv_bfloat16* csc = reinterpret_cast<__nv_bfloat16*>(smem + a.L.off_csc);
   if (ROT == 3 && p.scale_kind == kScaleChannel)
     for (int c = threadIdx.x; c < D; c += blockDim.x) csc[c] = p.scale[c];
@@ -635,9 +641,6 @@ __global__ void __launch_bounds__(256, 3) norm_bwd_n_fast_kernel(const __grid_co
   __syncthreads();
   if (ROT == 1 || ROT == 2) g.init_masks(fs.chan, k);
   const float inv_d = 1.0f / static_cast<float>(D);
-  const long long rows = p.rows, stride = gridDim.x;
-  long long row = blockIdx.x;
-  fs.feed.prologue(row, rows, stride);
   uint2 meta_pref = (ROT == 3 && row < rows) ? p.row_meta[row] : make_uint2(0u, 0u);
   int st = 0;
   uint32_t ph = 0;

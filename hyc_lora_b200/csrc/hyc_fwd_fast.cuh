@@ -162,6 +162,15 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
   const float eps = a.eps;
   RowRing ring{reinterpret_cast<uint64_t*>(smem), smem + a.L.off_slots, a.L.slot_bytes, a.L.stages};
   ring.init();
+  // the first rows start travelling before the per-CTA tables are set up
+  const long long rows = p.rows, stride = gridDim.x;
+  long long row = blockIdx.x;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ring.stages; ++s) {
+      const long long r = row + s * stride;
+      if (r < rows) issue_x_row<XT>(a, ring, s, r);
+    }
+  }
   const Work w = make_work(smem, a.L);
   setup_packed(p, w);
   float* wsm = reinterpret_cast<float*>(smem + a.L.off_wsm);
@@ -176,14 +185,6 @@ __global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constan
       if (ln)
         bsm[split_index(c, D)] = a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[c])
                               : static_cast<const float*>(a.bias)[c];
-    }
-  }
-  const long long rows = p.rows, stride = gridDim.x;
-  long long row = blockIdx.x;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < ring.stages; ++s) {
-      const long long r = row + s * stride;
-      if (r < rows) issue_x_row<XT>(a, ring, s, r);
     }
   }
   // row 0 of this CTA
