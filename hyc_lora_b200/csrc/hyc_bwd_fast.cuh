@@ -836,6 +836,13 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
   int u = 1;
   while (u < b.upt) u *= 2;
   b.upt = u;
+  // units per thread round up to an instantiated count: give the spare slots back as threads (whole warps),
+  // e.g. 688 units at 4 per thread run on 192 threads instead of 256
+  if (b.rot != 1 && !g_tune_threads) {
+    const int U = D / nseg / 8;
+    const int fit = ((U + b.upt - 1) / b.upt + 31) / 32 * 32;
+    if (fit < b.threads) b.threads = fit;
+  }
   uint32_t off = 64;  // mbarriers
   auto take = [&](uint32_t bytes) { uint32_t o = off; off = align_up(off + bytes, 16); return o; };
   b.L.off_red = take(2 * 64 * 4);

@@ -472,6 +472,13 @@ inline FastPlan plan_fast(const hyc_packed* q, int elem_size) {
     int u = 1;
     while (u < f.upt) u *= 2;
     f.upt = u;
+    // units per thread round up to an instantiated count: give the spare slots back as threads (whole warps),
+    // e.g. 688 units at 4 per thread run on 192 threads instead of 256
+    if (f.rot != 1 && !g_tune_threads) {
+      const int U = q->cols / (8 / q->bits) / 8;
+      const int fit = ((U + f.upt - 1) / f.upt + 31) / 32 * 32;
+      if (fit < f.threads) f.threads = fit;
+    }
   }
   return f;
 }
