@@ -168,10 +168,28 @@ def default_pool_entries(rows: int, cols: int, outlier_ratio: float) -> int:
     return min(int(math.ceil(rows * cols * min(frac, 1.0))) + 1024, 2 ** 32 - 2)
 
 
+_STATUS_CHUNK = 1024
+_status_chunks = {}
+
+
+def _new_status(device) -> torch.Tensor:
+    """A zeroed int32 status word.  Outside stream capture the words are handed out from a chunk zeroed by one
+    fill, so that a compression call does not cost an extra fill kernel; a word is never handed out twice.
+    During capture every record gets its own zeroed tensor (a chunk made inside one graph's memory pool must not
+    be shared with work outside that graph)."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.zeros(1, dtype=torch.int32, device=device)
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    chunk, used = _status_chunks.get(key, (None, _STATUS_CHUNK))
+    if used >= _STATUS_CHUNK:
+        chunk, used = torch.zeros(_STATUS_CHUNK, dtype=torch.int32, device=device), 0
+    _status_chunks[key] = (chunk, used + 1)
+    return chunk[used:used + 1]
+
+
 def _alloc_common(rows, cols, bits, device):
     codes = torch.empty((rows, cols * bits // 8), dtype=torch.uint8, device=device)
-    status = torch.zeros(1, dtype=torch.int32, device=device)
-    return codes, status
+    return codes, _new_status(device)
 
 
 def _new_r(x, rows, cols, seq, shape, thr, scale, scale_kind, bits, lowrank, pool_entries) -> Packed:
@@ -410,7 +428,7 @@ def softmax_compact(y: torch.Tensor, thr: torch.Tensor, capacity_ratio: float = 
                    val=torch.empty(cap, dtype=y.dtype, device=dev), col=torch.empty(cap, dtype=torch.int16, device=dev),
                    used=torch.empty(1, dtype=torch.int32, device=dev),
                    row_meta=torch.empty((rows, 2), dtype=torch.int32, device=dev),
-                   status=torch.zeros(1, dtype=torch.int32, device=dev))
+                   status=_new_status(dev))
     thr32 = thr.reshape(1).to(device=dev, dtype=torch.float32)
     rec = s.record()
     check(lib.hyc_softmax_compact(_ptr(y), _ptr(thr32), C.byref(rec), _stream()), "hyc_softmax_compact")
