@@ -387,10 +387,14 @@ def test_lora_weight_gradient_from_codes(pk, rows, d, bits, group, rotate, rank,
 
 # ------------------------------------------------------------------ full-size properties (configuration 5 shapes)
 
-@pytest.mark.parametrize("bits,group,rotate", [(4, 0, 0), (2, 128, 256), (8, 0, 256)])
-def test_full_size_roundtrip_properties(pk, bits, group, rotate):
-    rows, d = 16384, 4096
-    x, planted = synthetic.sweep_activation(rows, d, 0.01, salt=40 + bits)
+@pytest.mark.parametrize("bits,group,rotate,rows", [(4, 0, 0, 65536), (2, 128, 256, 16384), (8, 0, 256, 16384)])
+def test_full_size_roundtrip_properties(pk, bits, group, rotate, rows):
+    """Configuration 5 at its sizes (the first case is the benchmark's own [65536, 4096] tensor): exact outlier
+    channels, row slices bit for bit against the oracle, and size-independent error bounds over the whole tensor."""
+    d = 4096
+    x = torch.cat([synthetic.sweep_activation(8192, d, 0.01, salt=40 + bits)[0] * (1.0 + 0.01 * i)
+                   for i in range(rows // 8192)]).to(torch.bfloat16)
+    planted = synthetic.sweep_activation(8192, d, 0.01, salt=40 + bits)[1]
     xd = x.to(DEV)
     ch = pk.select_channels(pk.channel_absmax(xd), oc.n_outlier_count(d, 0.01))
     assert set(planted.tolist()) == set(ch.cpu().tolist())
@@ -400,11 +404,12 @@ def test_full_size_roundtrip_properties(pk, bits, group, rotate):
     xh = pk.decompress(p).reshape(rows, d)
     # outlier channels are carried exactly
     assert torch.equal(xh[:, ch.long()], xd[:, ch.long()])
-    # a slice of rows against the oracle, bit for bit
-    sl = slice(5000, 5256)
-    c = oc.n_compress(x[sl], ch.cpu(), bits, group, rotate)
-    assert torch.equal(p.codes[sl].cpu().view(torch.uint8), c.codes.view(torch.uint8))
-    assert torch.equal(xh[sl].cpu(), oc.n_decompress(c))
+    # slices of rows (first, middle, last) against the oracle, bit for bit
+    for sl in (slice(0, 96), slice(rows // 2 + 8, rows // 2 + 264), slice(rows - 96, rows)):
+        c = oc.n_compress(x[sl], ch.cpu(), bits, group, rotate)
+        assert torch.equal(p.codes[sl].cpu().view(torch.uint8), c.codes.view(torch.uint8))
+        assert torch.equal(xh[sl].cpu(), oc.n_decompress(c))
+    sl = slice(rows // 2 + 8, rows // 2 + 264)
     # checksum of checksums over the whole tensor: recompressing the reconstruction
     # keeps the scales within one bf16 rounding and the error bounded by half a step
     body = xd.float()
