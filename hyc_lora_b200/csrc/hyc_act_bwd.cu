@@ -106,6 +106,8 @@ int hyc_act_bwd(int op, const hyc_packed* s1, const hyc_packed* s2, const void* 
                 void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (op < HYC_ACT_SILU || op > HYC_ACT_PRODUCT) return HYC_ERR_MODE;
+  const int empty = packed_is_empty(s1);
+  if (empty) return empty < 0 ? empty : HYC_OK;
   int rc = check_packed(s1, false);
   if (rc) return rc;
   if (!g || !dx1) return HYC_ERR_NULL;

@@ -8,6 +8,8 @@ thread_local char g_cuda_error[256] = "";
 int g_tune_threads = 0, g_tune_stages = 0, g_tune_ctas = 0;
 
 static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, cudaStream_t stream) {
+  const int empty = packed_is_empty(out);
+  if (empty) return empty < 0 ? empty : HYC_OK;
   int rc = check_packed(out, true);
   if (rc) return rc;
   rc = check_dense(x, out->cols, norm != nullptr);

@@ -67,6 +67,8 @@ extern "C" {
 
 int hyc_decompress(const hyc_packed* in, const hyc_dense* o, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int empty = packed_is_empty(in);
+  if (empty) return empty < 0 ? empty : HYC_OK;
   int rc = check_packed(in, false);
   if (rc) return rc;
   rc = check_dense(o, in->cols, false);

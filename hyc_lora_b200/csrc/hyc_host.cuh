@@ -197,6 +197,18 @@ __device__ __forceinline__ void dequant_row(const PackedDev& p, const Work& w, c
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// An empty activation (rows == 0) has no buffers to speak of: the caller's pointers may be null.  Returns 1 when
+// the record is a well-formed empty one (nothing to do), 0 when it is not empty, a negative code when malformed.
+inline int packed_is_empty(const hyc_packed* q) {
+  if (!q) return HYC_ERR_NULL;
+  if (q->rows != 0) return 0;
+  if (q->mode != HYC_MODE_R && q->mode != HYC_MODE_N) return HYC_ERR_MODE;
+  if (q->cols <= 0 || q->cols % 128 != 0 || q->cols > 65408) return HYC_ERR_SHAPE;
+  if (q->bits != 1 && q->bits != 2 && q->bits != 4 && q->bits != 8) return HYC_ERR_BITS;
+  if (q->mode == HYC_MODE_N && q->bits == 1) return HYC_ERR_BITS;
+  return 1;
+}
+
 inline int check_packed(const hyc_packed* q, bool for_compress) {
   if (!q || !q->codes) return HYC_ERR_NULL;
   if (q->mode != HYC_MODE_R && q->mode != HYC_MODE_N) return HYC_ERR_MODE;

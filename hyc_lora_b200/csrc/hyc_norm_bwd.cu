@@ -144,6 +144,14 @@ int hyc_norm_bwd_partial_rows(void) { return kPartialRowsMax; }
 
 int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int empty = packed_is_empty(saved);
+  if (empty < 0) return empty;
+  if (empty) {
+    // no rows: the parameter gradients are zero
+    if (g && g->dweight && cudaMemsetAsync(g->dweight, 0, sizeof(float) * saved->cols, stream) != cudaSuccess) return HYC_ERR_CUDA;
+    if (g && g->dbias && cudaMemsetAsync(g->dbias, 0, sizeof(float) * saved->cols, stream) != cudaSuccess) return HYC_ERR_CUDA;
+    return HYC_OK;
+  }
   int rc = check_packed(saved, false);
   if (rc) return rc;
   if (!g || !g->weight || !g->dy || !g->rstd || !g->dx) return HYC_ERR_NULL;

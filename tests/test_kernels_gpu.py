@@ -428,3 +428,33 @@ def test_full_size_roundtrip_properties(pk, bits, group, rotate, rows):
     assert ((y[sl].float().cpu() - y_o.float()).abs() <= 1e-2 * y_o.float().abs() + 1e-3).all()
     assert _rel_err(rstd[sl], rstd_o) < 1e-5
     assert not p.wait_expired()
+
+
+# ------------------------------------------------------------------ empty and refused inputs
+
+def test_empty_batches_and_refused_arguments(pk):
+    from hyc_lora_b200._lib import HycError
+    d = 1024
+    ch = torch.tensor([3, 77], dtype=torch.int32, device=DEV)
+    empty = torch.empty(0, d, dtype=torch.bfloat16, device=DEV)
+    p = pk.compress_n(empty, ch, 4, 0, 0)
+    assert p.codes.shape == (0, d // 2) and pk.decompress(p).numel() == 0
+    w = torch.ones(d, dtype=torch.bfloat16, device=DEV)
+    p2, y, rstd, _ = pk.compress_n(empty, ch, 4, 0, 0, norm=dict(kind="rms", weight=w, bias=None, eps=1e-5))
+    assert y.numel() == 0 and rstd.numel() == 0
+    assert pk.act_bwd("silu", p, empty).numel() == 0
+    # a single row, and a row count that is no multiple of anything
+    for rows in (1, 7):
+        x, _ = synthetic.sweep_activation(rows, d, 0.01, salt=rows)
+        c = oc.n_compress(x, ch.cpu(), 4, 0, 0)
+        q = pk.compress_n(x.to(DEV), ch, 4, 0, 0)
+        assert torch.equal(q.codes.cpu().view(torch.uint8), c.codes.view(torch.uint8))
+    # refused before anything is launched
+    with pytest.raises(HycError):
+        pk.compress_n(torch.zeros(4, 192, dtype=torch.bfloat16, device=DEV), None, 4, 0, 0)      # cols % 128 != 0
+    with pytest.raises(HycError):
+        pk.compress_n(torch.zeros(4, d, dtype=torch.bfloat16, device=DEV), None, 3, 0, 0)        # bit width
+    with pytest.raises(HycError):
+        pk.compress_n(torch.zeros(4, d, dtype=torch.bfloat16, device=DEV), None, 4, 0, 96)       # rotation block
+    with pytest.raises((RuntimeError, ValueError)):
+        pk.compress_n(torch.zeros(4, d, dtype=torch.bfloat16), None, 4, 0, 0)                    # CPU tensor: no fallback
