@@ -12,7 +12,10 @@
  *     are returned BEFORE anything is enqueued; hyc_strerror() names a code;
  *   - conditions only the device can see (outlier pool overflow, an expired
  *     wait) are OR-ed into the caller-owned `status` word of the hyc_packed
- *     record, never trapped.
+ *     record, never trapped;
+ *   - an activation of zero rows is valid input everywhere: the call returns
+ *     HYC_OK without enqueueing anything (norm backward zeroes the parameter
+ *     gradients it was given) and the record's buffer pointers may be NULL.
  *
  * Citations name the reference implementation each entry replaces
  * (paths inside thu-ee-acts-lab/HyC-LoRA).
