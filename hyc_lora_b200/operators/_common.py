@@ -68,6 +68,40 @@ def site_options(extra) -> Optional[SiteOptions]:
     return extra[0] if extra else None
 
 
+# ---------------------------------------------------------------------------------------------
+# One compressed copy for sites that save the same tensor (channel mode).  The q, k and v LoRA-A
+# linears of a layer all save the layer's normalised input, gate and up save the same tensor too: the
+# reference compresses it once per module.  Here a site that is handed the very tensor object the
+# previous site compressed (same object, same version counter, same format) takes that site's
+# record instead of making its own; during calibration it also adopts that site's channel
+# statistics, so that afterwards "same record" can be decided by object identity, without a look at
+# the device.  Records are read-only in backward, so sharing is invisible in the results.
+# ---------------------------------------------------------------------------------------------
+SHARE_SITES = True
+_shared = []     # most recent first: (weakref to x, version, format key, record, calibration of the producer)
+
+
+def _shared_lookup(x, key, opts, iteration):
+    if not SHARE_SITES:
+        return None
+    for ref, version, k, rec, calib in _shared:
+        if ref() is x and version == x._version and k == key:
+            if iteration < 2:
+                opts.calib.score, opts.calib.channels = calib.score, calib.channels
+                return rec
+            if opts.calib.channels is not None and opts.calib.channels is calib.channels:
+                return rec
+    return None
+
+
+def _shared_store(x, key, rec, opts):
+    if not SHARE_SITES:
+        return
+    import weakref
+    _shared.insert(0, (weakref.ref(x), x._version, key, rec, opts.calib))
+    del _shared[2:]
+
+
 @torch.no_grad()
 def compress_site(x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, method, rank, iteration, static_value,
                   opts: Optional[SiteOptions], norm: Optional[dict] = None):
@@ -76,12 +110,18 @@ def compress_site(x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, method, 
     if not x.is_cuda:
         raise RuntimeError("hyc_lora_b200 operators run on CUDA tensors only (there is no CPU path)")
     if opts is not None and opts.channel:
-        channels = opts.calib.channels_for(x, iteration)
         cols = x.shape[-1] if x.dim() != 4 else x.shape[1] * x.shape[3]
-        res = cf.channel_compress(x, channels, sub_outlier_bit, opts.group_size, opts.rotate_for(cols, sub_outlier_bit),
-                                  norm=norm)
+        rotate = opts.rotate_for(cols, sub_outlier_bit)
         stats = opts.dummy_stats(x.device)
+        key = (sub_outlier_bit, opts.group_size, rotate, opts.calib.outlier_ratio, iteration < 2)
         if norm is None:
+            shared = _shared_lookup(x, key, opts, iteration)
+            if shared is not None:
+                return shared, stats, None
+        channels = opts.calib.channels_for(x, iteration)
+        res = cf.channel_compress(x, channels, sub_outlier_bit, opts.group_size, rotate, norm=norm)
+        if norm is None:
+            _shared_store(x, key, res, opts)
             return res, stats, None
         return res[0], stats, res[1:]
     if iteration < 2:

@@ -290,6 +290,45 @@ def test_channel_mode_wide_site_uses_fitting_rotation_block():
     assert ((xd.grad.float().cpu() - o.float()).abs() <= 1e-2 * o.float().abs() + 1e-4).all()
 
 
+def test_sites_saving_the_same_tensor_share_one_record():
+    """Three LoRA-A style linears fed the same tensor object compress it once (per call) and get the
+    gradients they get when every site compresses for itself."""
+    from hyc_lora_b200.operators import _common, compress_function as cf
+    from hyc_lora_b200.operators.efficient_linear import EfficientMemoryLinear
+    d, r = 1024, 16
+    x = _act(2, 40, d, salt=70, gain=20.0)
+    g = [_rand((2, 40, r), 71 + i) for i in range(3)]
+    ws = [(0.02 * _rand((r, d), 75 + i, torch.float32)).to(torch.bfloat16) for i in range(3)]
+    grads = {}
+    for share in (True, False):
+        _common.SHARE_SITES = share
+        _common._shared.clear()
+        lins = []
+        for w in ws:
+            lin = EfficientMemoryLinear(d, r, bias=False, outlier_ratio=0.01, sub_outlier_ratio=1.0, sub_outlier_bit=4,
+                                        rank=0, outlier_mode="channel", rotate=64).to(DEV).to(torch.bfloat16)
+            lin.weight.data.copy_(w)
+            lins.append(lin)
+        calls, real = [0], cf.channel_compress
+        def counted(*a, **k):
+            calls[0] += 1
+            return real(*a, **k)
+        cf.channel_compress = counted
+        try:
+            for it in range(3):                      # two calibration calls, one steady-state call
+                for lin in lins:
+                    lin.weight.grad = None
+                xd = x.to(DEV).requires_grad_(True)
+                sum((lin(xd) * gi.to(DEV)).sum() for lin, gi in zip(lins, g)).backward()
+        finally:
+            cf.channel_compress = real
+        assert calls[0] == (3 if share else 9)
+        grads[share] = [lin.weight.grad.clone() for lin in lins] + [xd.grad.clone()]
+    _common.SHARE_SITES = True
+    for a, b in zip(grads[True], grads[False]):
+        assert torch.equal(a, b)
+
+
 def test_low_rank_site_and_calibration_state_roundtrip():
     """rank > 0: the randomized SVD differs between devices, so the check is against the exact
     derivative; then a second module restored from the first one's calibration state reproduces
