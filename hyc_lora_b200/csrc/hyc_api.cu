@@ -122,7 +122,7 @@ const char* hyc_last_cuda_error(void) { return g_cuda_error; }
 int hyc_version(void) { return 100; }
 
 int hyc_set_tuning(int threads, int stages, int ctas_per_sm) {
-  if (threads != 0 && (threads < 32 || threads > 256 || threads % 32 != 0)) return HYC_ERR_SHAPE;
+  if (threads != 0 && (threads < 32 || threads > 512 || threads % 32 != 0)) return HYC_ERR_SHAPE;
   if (stages < 0 || stages > kMaxStages || ctas_per_sm < 0 || ctas_per_sm > 16) return HYC_ERR_SHAPE;
   g_tune_threads = threads; g_tune_stages = stages; g_tune_ctas = ctas_per_sm;
   return HYC_OK;

@@ -143,7 +143,7 @@ __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { re
 // that saved it and stored one barrier after the vector stores of the row, which orders the
 // two stores to the same address.
 template <typename XT, int BITS, bool NORM, int UPT, int ROT>
-__global__ void __launch_bounds__(256, 3) fwd_n_fast_kernel(const __grid_constant__ FwdArgs a) {
+__global__ void __launch_bounds__(384, 2) fwd_n_fast_kernel(const __grid_constant__ FwdArgs a) {
   using C = CodeTraits<BITS>;
   constexpr int NSEG = C::kSeg;
   constexpr int NR = ROT == 1 ? UPT : UPT * NSEG;
@@ -462,7 +462,7 @@ inline FastPlan plan_fast(const hyc_packed* q, int elem_size) {
     if (q->group && (D / nseg) % 128 != 0) return f;
     const int U = D / nseg / 8;
     while (threads > 32 && threads / 2 >= U) threads /= 2;   // a thread owns whole units
-    for (; threads <= 256; threads *= 2) {
+    for (; threads <= 384; threads *= 2) {
       const int upt = (U + threads - 1) / threads;
       if (upt * nseg <= reg_cap) { f.ok = true; f.threads = threads; f.upt = upt; break; }
     }
