@@ -91,7 +91,8 @@ int hyc_decompress(const hyc_packed* in, const hyc_dense* o, void* stream_) {
     auto kern = decompress_n_fast_kernel<B, UP, RT>;                                            \
     rc = set_smem(kern, bp.L.total);                                                            \
     if (rc) return rc;                                                                          \
-    kern<<<bp.grid, bp.threads, bp.L.total, stream>>>(fa);                                      \
+    const int g = bp.rot == 2 ? bp.grid : resident_grid(kern, bp.threads, bp.L.total, bp.grid);    \
+    kern<<<g, bp.threads, bp.L.total, stream>>>(fa);                                            \
   }
       HYC_BWD_DISPATCH(bp, in->bits, 4, HYC_DECF)
 #undef HYC_DECF

@@ -182,18 +182,21 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
       fa.rstd = g->rstd; fa.mean = g->mean; fa.dx = static_cast<__nv_bfloat16*>(g->dx);
       fa.partials = g->partials; fa.need_dw = g->dweight != nullptr; fa.need_db = g->dbias != nullptr;
       fa.L = bp.L;
+      int grid_used = bp.grid;   // partial rows of the weight gradient: one per CTA
 #define HYC_NBF(B, UP, RT)                                                                      \
   {                                                                                             \
     if (g->dy_dtype == HYC_BF16) {                                                              \
       auto kern = norm_bwd_n_fast_kernel<B, UP, RT, __nv_bfloat16>;                             \
       rc = set_smem(kern, bp.L.total);                                                          \
       if (rc) return rc;                                                                        \
-      kern<<<bp.grid, bp.threads, bp.L.total, stream>>>(fa);                                    \
+      grid_used = resident_grid(kern, bp.threads, bp.L.total, bp.grid);                         \
+      kern<<<grid_used, bp.threads, bp.L.total, stream>>>(fa);                                  \
     } else {                                                                                    \
       auto kern = norm_bwd_n_fast_kernel<B, UP, RT, float>;                                     \
       rc = set_smem(kern, bp.L.total);                                                          \
       if (rc) return rc;                                                                        \
-      kern<<<bp.grid, bp.threads, bp.L.total, stream>>>(fa);                                    \
+      grid_used = resident_grid(kern, bp.threads, bp.L.total, bp.grid);                         \
+      kern<<<grid_used, bp.threads, bp.L.total, stream>>>(fa);                                  \
     }                                                                                           \
   }
       HYC_BWD_DISPATCH(bp, saved->bits, 4, HYC_NBF)
@@ -201,7 +204,7 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
       cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return cuda_fail(e, "norm_bwd_n_fast_kernel launch");
       if (g->dweight) {
-        reduce_partials_kernel<<<(D + 127) / 128, 128, 0, stream>>>(g->partials, bp.grid, D, g->dweight, g->dbias);
+        reduce_partials_kernel<<<(D + 127) / 128, 128, 0, stream>>>(g->partials, grid_used, D, g->dweight, g->dbias);
         e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(e, "reduce_partials_kernel launch");
       }
