@@ -139,12 +139,15 @@ int hyc_act_bwd(int op, const hyc_packed* s1, const hyc_packed* s2, const void* 
       fa.dx1 = static_cast<unsigned char*>(dx1);
       fa.dx2 = static_cast<unsigned char*>(dx2);
       fa.L = bp.L;
+      // These CTAs set up no tables, and on long inputs four short waves measured 5 % faster than one
+      // persistent wave (65 536 rows of 4096 channels: 0.234 against 0.246 ms); each CTA keeps 8 rows or more.
+      const int grid_l = (!g_tune_ctas && s1->rows >= 32LL * bp.grid) ? bp.grid * 4 : bp.grid;
 #define HYC_ACTF_OP(B, UP, RT, GT, OPV)                                                         \
   {                                                                                             \
     auto kern = act_bwd_n_fast_kernel<B, UP, RT, GT, OPV>;                                      \
     rc = set_smem(kern, bp.L.total);                                                            \
     if (rc) return rc;                                                                          \
-    kern<<<bp.grid, bp.threads, bp.L.total, stream>>>(fa);                                      \
+    kern<<<grid_l, bp.threads, bp.L.total, stream>>>(fa);                                       \
   }
 #define HYC_ACTF(B, UP, RT)                                                                     \
   {                                                                                             \

@@ -134,6 +134,7 @@ inline int plan_launch(const LayoutReq& r, long long rows, LaunchPlan* out, int 
 // evens out SMs of unequal speed), which therefore launch the planned grid.
 template <typename K>
 inline int resident_grid(K kernel, int threads, uint32_t smem_bytes, int grid) {
+  if (g_tune_ctas) return grid;   // an explicit tuning request is taken as given
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem_bytes) != cudaSuccess || per_sm < 1) {
     cudaGetLastError();
