@@ -101,6 +101,23 @@ def test_r_mode_against_oracle_ragged_rows(pk, dtype, bits, method):
     assert torch.equal(pk.decompress(p).cpu(), oc.r_decompress(c))
 
 
+@pytest.mark.parametrize("cols,bits,method", [
+    (11008, 4, "per-channel"), (11008, 8, "per-tensor"), (11008, 2, "per-channel"),
+    (14336, 4, "per-channel"), (8192, 4, "per-token"), (5120, 4, "per-channel")])
+def test_r_mode_wide_rows(pk, cols, bits, method):
+    # FFN-wide rows take other thread counts and units per thread (and a helper warp) than 4096 channels
+    x, _ = synthetic.roundtrip_activation(2, 150, cols, planted=7, gain=20.0, dtype=torch.bfloat16, salt=cols + bits)
+    thr, L, R, scale = oc.r_calibrate(x, 0.01, 1.0, bits, method, 0)
+    c = oc.r_compress(x, thr, scale, bits, 1.0)
+    p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), bits)
+    assert int(p.status.item()) == 0
+    assert torch.equal(p.codes.cpu().reshape(c.codes.shape).view(torch.uint8), c.codes.view(torch.uint8))
+    flat, val = p.outlier_coo()
+    o_flat, o_val = _oracle_coo_flat(c)
+    assert torch.equal(flat, o_flat) and torch.equal(val, o_val)
+    assert torch.equal(pk.decompress(p).cpu(), oc.r_decompress(c))
+
+
 def test_r_mode_rows_with_more_outliers_than_the_shared_list(pk):
     """A threshold far inside the distribution gives rows with thousands of element outliers: more than the
     kernel's per-row shared list holds, so warp 0 regenerates the row's entries straight into the pool."""
