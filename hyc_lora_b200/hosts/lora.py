@@ -116,6 +116,28 @@ class FrozenLinear(nn.Module):
         return nn.functional.linear(x, self.weight)
 
 
+class _LoraMergeFunc(torch.autograd.Function):
+    """``base += scaling * h @ B^T`` in place, the scale and the add in the GEMM's epilogue; backward keeps the
+    scale in the two small GEMMs' epilogues too (autograd's own addmm backward multiplies in separate kernels)."""
+
+    @staticmethod
+    def forward(ctx, base, h, weight_b, scaling):
+        ctx.scaling = scaling
+        ctx.save_for_backward(h, weight_b)
+        base.addmm_(h, weight_b.t(), alpha=scaling)
+        ctx.mark_dirty(base)
+        return base
+
+    @staticmethod
+    def backward(ctx, grad):
+        h, weight_b = ctx.saved_tensors
+        grad = grad.contiguous()
+        # beta = 0: the first argument only gives shape and dtype, its contents are not read
+        grad_h = torch.addmm(torch.empty_like(h), grad, weight_b, beta=0, alpha=ctx.scaling)
+        grad_b = torch.addmm(torch.empty_like(weight_b), grad.t(), h, beta=0, alpha=ctx.scaling)
+        return grad, grad_h, grad_b, None
+
+
 class LoRALinear(nn.Module):
     """``base(x) + lora_B(lora_A(x)) * scaling`` with B initialised to zero."""
 
@@ -140,7 +162,7 @@ class LoRALinear(nn.Module):
         # which autograd would undo with full-size copies in backward)
         base = self.base_layer(x.reshape(-1, x.shape[-1]))
         h = self.lora_A(x)
-        base.addmm_(h.reshape(-1, h.shape[-1]), self.lora_B.weight.t(), alpha=self.scaling)
+        base = _LoraMergeFunc.apply(base, h.reshape(-1, h.shape[-1]), self.lora_B.weight, self.scaling)
         return base.view(*x.shape[:-1], base.shape[-1])
 
 

@@ -20,6 +20,9 @@ class EfficientMemoryGELUFunc(torch.autograd.Function):
             x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, sub_outlier_quantize_method, rank, iteration,
             static_value, site_options(extra))
         ctx.x_outlier_compressed = packed
+        # the statistics carry no gradient: without this autograd would fill a zero tensor for each of them
+        # on every backward call
+        ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(outlier, L, R, scale)
         return result, outlier, L, R, scale
 

@@ -28,6 +28,9 @@ class EfficientMemoryGEMMFunc(torch.autograd.Function):
             x2.mT, outlier_ratio_2, sub_outlier_ratio_2, sub_outlier_bit_2, sub_outlier_quantize_method_2, rank,
             iteration, static_value_2, o2)
         ctx.x_outlier_compressed = (p1, p2)
+        # the statistics carry no gradient: without this autograd would fill a zero tensor for each of them
+        # on every backward call
+        ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(outlier_1, outlier_2, L_1, R_1, scale_1, L_2, R_2, scale_2)
         return result, outlier_1, L_1, R_1, scale_1, outlier_2, L_2, R_2, scale_2
 
@@ -86,6 +89,9 @@ class EfficientMemoryGEMMWithSoftmaxFunc(torch.autograd.Function):
             x2, outlier_ratio_2, sub_outlier_ratio_2, sub_outlier_bit_2, sub_outlier_quantize_method_2, rank,
             iteration, static_value_2, extra[0] if extra else None)
         ctx.x_outlier_compressed = p2
+        # the statistics carry no gradient: without this autograd would fill a zero tensor for each of them
+        # on every backward call
+        ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(outlier_1, outlier_2, L_2, R_2, scale_2)
         return result, outlier_1, outlier_2, L_2, R_2, scale_2
 

@@ -22,6 +22,9 @@ class EfficientMemoryLinearFunc(torch.autograd.Function):
         packed, (outlier, L, R, scale), _ = compress_site(
             x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, sub_outlier_quantize_method, rank, iteration,
             static_value, site_options(extra))
+        # the statistics carry no gradient: without this autograd would fill a zero tensor for each of them
+        # on every backward call
+        ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(outlier, L, R, scale)
         ctx.x_outlier_compressed = packed
         ctx.save_for_backward(w)

@@ -25,6 +25,9 @@ class EfficientMemoryRMSNormFunc(torch.autograd.Function):
         packed, (outlier, L, R, scale), (y, rstd, mean) = compress_site(
             x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, sub_outlier_quantize_method, rank, iteration,
             static_value, site_options(extra), norm=norm)
+        # the statistics carry no gradient: without this autograd would fill a zero tensor for each of them
+        # on every backward call
+        ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(outlier, L, R, scale)
         ctx.x_outlier_compressed = packed
         ctx.save_for_backward(weight, mean if mean is not None else rstd, rstd)

@@ -15,6 +15,9 @@ class EfficientMemorySoftmaxFunc(torch.autograd.Function):
         y_return = F.softmax(x, dim=-1)
         outlier = get_statistics_softmax(y_return, iteration, outlier_ratio) if iteration < 2 else static_value
         ctx.y_sparse = true_compress_softmax(y_return, outlier, outlier_ratio)
+        # the statistics carry no gradient: without this autograd would fill a zero tensor for each of them
+        # on every backward call
+        ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(outlier)
         return y_return, outlier
 
