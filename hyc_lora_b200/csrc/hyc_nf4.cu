@@ -12,28 +12,41 @@
 
 namespace hyc {
 
-// one thread rebuilds 16 values (8 bytes) -> two 16-byte stores
-__global__ void nf4_dequant_kernel(const uint2* codes, const float* absmax, const float* codebook, long long n16,
-                                   uint4* out) {
+// One thread rebuilds 8 values (4 bytes) per step -> one 16-byte store; a warp reads 128 and writes 512
+// contiguous bytes per instruction.  Four independent steps per loop trip keep several loads in flight.
+constexpr int kNf4Unroll = 4;
+
+__device__ __forceinline__ uint4 nf4_expand8(uint32_t c, float s, const float* cbk) {
+  float f[8];
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const uint32_t byte = (c >> (8 * b)) & 0xffu;
+    f[2 * b] = cbk[byte >> 4] * s;
+    f[2 * b + 1] = cbk[byte & 15u] * s;
+  }
+  return pack_bf16x8(f);
+}
+
+__global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint32_t* codes, const float* absmax,
+                                                          const float* codebook, long long n8, uint4* out) {
   __shared__ float cbk[16];
   if (threadIdx.x < 16) cbk[threadIdx.x] = codebook[threadIdx.x];
   __syncthreads();
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const uint2 c = codes[i];
-    const float s = absmax[i >> 2];  // 16 values per thread, 64 per block
-    float f[16];
+  const long long span = static_cast<long long>(blockDim.x) * kNf4Unroll;
+  for (long long base = blockIdx.x * span + threadIdx.x; base < n8; base += gridDim.x * span) {
+    uint32_t c[kNf4Unroll];
+    float s[kNf4Unroll];
 #pragma unroll
-    for (int b = 0; b < 8; ++b) {
-      const uint32_t byte = ((b < 4 ? c.x >> (8 * b) : c.y >> (8 * (b - 4))) & 0xffu);
-      f[2 * b] = cbk[byte >> 4] * s;
-      f[2 * b + 1] = cbk[byte & 15u] * s;
+    for (int u = 0; u < kNf4Unroll; ++u) {
+      const long long i = base + static_cast<long long>(u) * blockDim.x;
+      c[u] = i < n8 ? __ldg(codes + i) : 0u;
+      s[u] = i < n8 ? __ldg(absmax + (i >> 3)) : 0.f;   // 8 values per step, 64 per scale
     }
-    float lo[8], hi[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) { lo[e] = f[e]; hi[e] = f[8 + e]; }
-    out[2 * i] = pack_bf16x8(lo);
-    out[2 * i + 1] = pack_bf16x8(hi);
+    for (int u = 0; u < kNf4Unroll; ++u) {
+      const long long i = base + static_cast<long long>(u) * blockDim.x;
+      if (i < n8) out[i] = nf4_expand8(c[u], s[u], cbk);
+    }
   }
 }
 
@@ -43,12 +56,13 @@ extern "C" int hyc_nf4_dequant(const void* codes, const float* absmax, const flo
                                void* out_bf16, void* stream) {
   if (!codes || !absmax || !codebook || !out_bf16) return HYC_ERR_NULL;
   if (n < 0 || n % 64 != 0) return HYC_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(codes) & 7u) || (reinterpret_cast<uintptr_t>(out_bf16) & 15u)) return HYC_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(codes) & 3u) || (reinterpret_cast<uintptr_t>(out_bf16) & 15u)) return HYC_ERR_ALIGN;
   if (n == 0) return HYC_OK;
-  const long long n16 = n / 16;
-  long long blocks = (n16 + 255) / 256;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  const long long n8 = n / 8;
+  const long long per_block = 256LL * hyc::kNf4Unroll;
+  long long blocks = (n8 + per_block - 1) / per_block;
+  if (blocks > 148 * 16) blocks = 148 * 16;
   hyc::nf4_dequant_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint2*>(codes), absmax, codebook, n16, static_cast<uint4*>(out_bf16));
+      static_cast<const uint32_t*>(codes), absmax, codebook, n8, static_cast<uint4*>(out_bf16));
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
