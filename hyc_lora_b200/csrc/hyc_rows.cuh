@@ -368,7 +368,7 @@ __device__ void r_quant_row(const PackedDev& p, const Work& w, const XT* xs, lon
         if (extract && fabsf(x) > thr) {
           const uint32_t at = atomicAdd(&w.misc[0], 1u);
           w.list[at] = (float_to_bf16_bits(x) << 16) | static_cast<uint32_t>(col + e);
-          x = 0.f;
+          x = x - x;   // the reference's x - x * mask: 0, or NaN for an infinite input
         }
         const float sc = per_channel ? w.cscale[col + e] : sc_row;
         float q = __fdiv_rn(x, sc);

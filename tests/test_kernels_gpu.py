@@ -118,6 +118,32 @@ def test_r_mode_wide_rows(pk, cols, bits, method):
     assert torch.equal(pk.decompress(p).cpu(), oc.r_decompress(c))
 
 
+@pytest.mark.parametrize("bits,norm_kind", [(4, None), (8, None), (2, None), (4, "rms")])
+def test_r_mode_scales_outside_the_reciprocal_shortcut(pk, bits, norm_kind):
+    # channels with a tiny or a huge scale, and infinite inputs: the quotient from the rounded reciprocal is
+    # not valid there and the unit is redone with a true division; codes must still match the reference
+    x, _ = synthetic.roundtrip_activation(2, 40, 768, planted=5, gain=20.0, dtype=torch.bfloat16, salt=70 + bits)
+    x[0, 3, 5] = float("inf")
+    x[1, 7, 700] = float("-inf")
+    thr, L, R, scale = oc.r_calibrate(x, 0.01, 1.0, bits, "per-channel", 0)
+    scale = scale.clone()
+    scale.view(-1)[[2, 130, 385]] = 1e-30
+    scale.view(-1)[[9, 131, 767]] = 1e30
+    scale.view(-1)[[64, 65]] = -0.37          # a negative scale flips the codes
+    c = oc.r_compress(x, thr, scale, bits, 1.0)
+    if norm_kind is None:
+        p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), bits)
+    else:
+        w = synthetic.norm_weight(768, 0.1).to(DEV)
+        p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), bits,
+                          norm=dict(kind=norm_kind, weight=w, bias=None, eps=1e-5))[0]
+    assert int(p.status.item()) == 0
+    assert torch.equal(p.codes.cpu().reshape(c.codes.shape).view(torch.uint8), c.codes.view(torch.uint8))
+    flat, val = p.outlier_coo()
+    o_flat, o_val = _oracle_coo_flat(c)
+    assert torch.equal(flat, o_flat) and torch.equal(val, o_val)
+
+
 def test_r_mode_rows_with_more_outliers_than_the_shared_list(pk):
     """A threshold far inside the distribution gives rows with thousands of element outliers: more than the
     kernel's per-row shared list holds, so warp 0 regenerates the row's entries straight into the pool."""
