@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "../../include/hyc_b200.h"
 #include "hyc_common.cuh"
 
@@ -46,33 +48,74 @@ __global__ void __launch_bounds__(256) channel_absmax_kernel(const XT* x, long l
   }
 }
 
+// Scores are ordered through an integer key so that the order is total whatever the bits are:
+// finite values and infinities keep their numeric order, -0 counts as +0, and every NaN sits
+// above +inf (where a descending sort puts it).  With a total order exactly k channels have a
+// rank below k, which is what lets the gather below write a k-entry list.
+__device__ __forceinline__ unsigned int score_key(float s) {
+  if (s != s) return 0xFFFFFFFFu;
+  const unsigned int u = __float_as_uint(s + 0.f);  // -0 + 0 = +0
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 // rank[c] = number of channels that come before c when ordering by
 // (score descending, index ascending)
 __global__ void __launch_bounds__(256) channel_rank_kernel(const float* score, int D, int* rank) {
-  __shared__ float tile[1024];
+  __shared__ unsigned int tile[1024];
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const float mine = c < D ? score[c] : 0.f;
+  const unsigned int mine = c < D ? score_key(score[c]) : 0u;
   int before = 0;
   for (int j0 = 0; j0 < D; j0 += 1024) {
     __syncthreads();
-    for (int j = threadIdx.x; j < 1024; j += blockDim.x) tile[j] = (j0 + j < D) ? score[j0 + j] : -1.f;
+    for (int j = threadIdx.x; j < 1024; j += blockDim.x) tile[j] = (j0 + j < D) ? score_key(score[j0 + j]) : 0u;
     __syncthreads();
     const int n = min(1024, D - j0);
     for (int j = 0; j < n; ++j) {
-      const float s = tile[j];
+      const unsigned int s = tile[j];
       before += (s > mine || (s == mine && (j0 + j) < c)) ? 1 : 0;
     }
   }
   if (c < D) rank[c] = before;
 }
 
-// ascending list of the channels whose rank is below k
-__global__ void __launch_bounds__(256) channel_gather_kernel(const int* rank, int D, int k, int* channels) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D || rank[c] >= k) return;
-  int pos = 0;
-  for (int j = 0; j < c; ++j) pos += rank[j] < k ? 1 : 0;
-  channels[pos] = c;
+// Ascending list of the channels whose rank is below k.  One CTA: thread t owns a contiguous
+// run of channels, counts its selected ones, a block-wide exclusive scan of the counts gives
+// the run's first output slot, and the run is walked once more to write.  A slot at or beyond
+// k is never written (it cannot occur with the ranks of channel_rank_kernel; the check keeps
+// the store inside the caller's list for any rank array).
+constexpr int kGatherThreads = 1024;
+__global__ void __launch_bounds__(kGatherThreads) channel_gather_kernel(const int* rank, int D, int k, int* channels) {
+  __shared__ int warp_sum[kGatherThreads / 32];
+  const int per = (D + kGatherThreads - 1) / kGatherThreads;
+  const int c0 = min(D, static_cast<int>(threadIdx.x) * per), c1 = min(D, c0 + per);
+  int mine = 0;
+  for (int c = c0; c < c1; ++c) mine += rank[c] < k ? 1 : 0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  if (lane == 31) warp_sum[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_sum[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += up;
+    }
+    warp_sum[lane] = w;  // inclusive over warps
+  }
+  __syncthreads();
+  int pos = incl - mine + (warp ? warp_sum[warp - 1] : 0);
+  for (int c = c0; c < c1; ++c) {
+    if (rank[c] < k) {
+      if (pos < k) channels[pos] = c;
+      ++pos;
+    }
+  }
 }
 
 // Scratch of the allocation-free selection entry point: one rank per channel.  The array
@@ -125,7 +168,7 @@ int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* ch
   if (k == 0) return HYC_OK;
   const int blocks = (cols + 255) / 256;
   channel_rank_kernel<<<blocks, 256, 0, stream>>>(score, cols, rank_scratch);
-  channel_gather_kernel<<<blocks, 256, 0, stream>>>(rank_scratch, cols, k, channels);
+  channel_gather_kernel<<<1, kGatherThreads, 0, stream>>>(rank_scratch, cols, k, channels);
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
 
@@ -139,20 +182,24 @@ int hyc_select_channels_noalloc(const float* score, int32_t cols, int32_t k, int
   if (k == 0) return HYC_OK;
   // In host code the array's name is only a handle: the device address has to be asked for,
   // once per device, with that device current.  The first call on a device does it.
-  static int* scratch_of_device[64] = {nullptr};
+  // The cache is read and written by any host thread: entries are atomics, and two threads that
+  // both miss simply look the same address up twice.  cudaDeviceReset() invalidates the address;
+  // a process that resets a device must not call this entry point on it afterwards.
+  static std::atomic<int*> scratch_of_device[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HYC_ERR_CUDA;
-  if (!scratch_of_device[dev]) {
+  int* rank = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (!rank) {
     int* ptr = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_select_rank_scratch) != cudaSuccess || !ptr)
       return HYC_ERR_CUDA;
-    scratch_of_device[dev] = ptr;
+    scratch_of_device[dev].store(ptr, std::memory_order_release);
+    rank = ptr;
   }
-  int* rank = scratch_of_device[dev];
   const int blocks = (cols + 255) / 256;
   // every rank in [0, cols) is rewritten by the first kernel, so nothing has to start at zero
   channel_rank_kernel<<<blocks, 256, 0, stream>>>(score, cols, rank);
-  channel_gather_kernel<<<blocks, 256, 0, stream>>>(rank, cols, k, channels);
+  channel_gather_kernel<<<1, kGatherThreads, 0, stream>>>(rank, cols, k, channels);
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
 

@@ -187,7 +187,9 @@ int hyc_act_bwd(int op, const hyc_packed* saved1, const hyc_packed* saved2, cons
  * score[cols] (caller zeroes it first; repeated calls accumulate the max), then
  * the k best channels, ties to the lower index, written ascending.  Plays the
  * role get_statistics (compress_function.py:292-340) plays for the reference
- * mode.  `rank_scratch` holds cols int32. */
+ * mode.  `rank_scratch` holds cols int32.  Any score bits are accepted: -0 counts
+ * as +0 and a NaN orders above +inf (as a descending sort places it), so exactly
+ * k entries of `channels` are written. */
 int hyc_channel_absmax(const hyc_dense* x, int64_t rows, int32_t cols, int32_t seq, float* score, void* stream);
 int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* channels,
                         int32_t* rank_scratch, void* stream);
@@ -259,7 +261,9 @@ int hyc_rope(void* q, void* k, const float* cos_sin, int64_t tokens, int32_t seq
  *   - all calls on a device share the one array: two calls whose kernels can overlap on the
  *     GPU (different streams) race; keep them on one stream or order them with events;
  *   - the array keeps the previous call's ranks, which is harmless: every rank below cols is
- *     rewritten before it is read. */
+ *     rewritten before it is read;
+ *   - the looked-up address is cached per device (host threads may call concurrently); it does
+ *     not survive cudaDeviceReset(), so do not call this entry point on a device after resetting it. */
 int hyc_select_channels_static_max_cols(void);
 int hyc_select_channels_noalloc(const float* score, int32_t cols, int32_t k, int32_t* channels, void* stream);
 
