@@ -84,6 +84,7 @@ SYMBOLS = {
     "hyc_strerror": (C.c_char_p, [C.c_int]),
     "hyc_last_cuda_error": (C.c_char_p, []),
     "hyc_version": (C.c_int, []),
+    "hyc_launch_count": (C.c_uint64, []),
     "hyc_set_tuning": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "hyc_compress": (C.c_int, [C.POINTER(HycDense), C.POINTER(HycPacked), C.c_void_p]),
     "hyc_decompress": (C.c_int, [C.POINTER(HycPacked), C.POINTER(HycDense), C.c_void_p]),

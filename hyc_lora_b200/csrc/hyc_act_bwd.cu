@@ -147,7 +147,7 @@ int hyc_act_bwd(int op, const hyc_packed* s1, const hyc_packed* s2, const void* 
     auto kern = act_bwd_n_fast_kernel<B, UP, RT, GT, OPV>;                                      \
     rc = set_smem(kern, bp.L.total);                                                            \
     if (rc) return rc;                                                                          \
-    kern<<<grid_l, bp.threads, bp.L.total, stream>>>(fa);                                       \
+    kern<<<grid_l, bp.threads, bp.L.total, stream>>>(fa); HYC_LAUNCHED();                                       \
   }
 #define HYC_ACTF(B, UP, RT)                                                                     \
   {                                                                                             \
@@ -196,7 +196,7 @@ int hyc_act_bwd(int op, const hyc_packed* s1, const hyc_packed* s2, const void* 
     auto kern = act_bwd_kernel<MODE, BITS, GT, OP>;                         \
     rc = set_smem(kern, plan.L.total);                                      \
     if (rc) return rc;                                                      \
-    kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a);             \
+    kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a); HYC_LAUNCHED();             \
   }
 #define HYC_ACT_CASE(MODE, BITS)                                            \
   {                                                                         \

@@ -6,6 +6,7 @@ namespace hyc {
 
 thread_local char g_cuda_error[256] = "";
 int g_tune_threads = 0, g_tune_stages = 0, g_tune_ctas = 0;
+std::atomic<unsigned long long> g_launch_count{0};
 
 static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, cudaStream_t stream) {
   const int empty = packed_is_empty(out);
@@ -120,6 +121,8 @@ const char* hyc_strerror(int code) {
 const char* hyc_last_cuda_error(void) { return g_cuda_error; }
 
 int hyc_version(void) { return 100; }
+
+uint64_t hyc_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
 
 int hyc_set_tuning(int threads, int stages, int ctas_per_sm) {
   if (threads != 0 && (threads < 32 || threads > 512 || threads % 32 != 0)) return HYC_ERR_SHAPE;

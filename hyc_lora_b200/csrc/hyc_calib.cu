@@ -150,12 +150,12 @@ int hyc_channel_absmax(const hyc_dense* x, int64_t rows, int32_t cols, int32_t s
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<static_cast<int>(grid), 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(x->base), rows, cols, seq,
                                                         x->chunks, x->row_stride, x->batch_stride, x->chunk_stride,
-                                                        score);
+                                                        score); HYC_LAUNCHED();
   } else {
     auto kern = channel_absmax_kernel<float>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<static_cast<int>(grid), 256, smem, stream>>>(static_cast<const float*>(x->base), rows, cols, seq, x->chunks,
-                                                        x->row_stride, x->batch_stride, x->chunk_stride, score);
+                                                        x->row_stride, x->batch_stride, x->chunk_stride, score); HYC_LAUNCHED();
   }
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
@@ -167,8 +167,8 @@ int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* ch
   if (cols <= 0 || k < 0 || k > cols) return HYC_ERR_SHAPE;
   if (k == 0) return HYC_OK;
   const int blocks = (cols + 255) / 256;
-  channel_rank_kernel<<<blocks, 256, 0, stream>>>(score, cols, rank_scratch);
-  channel_gather_kernel<<<1, kGatherThreads, 0, stream>>>(rank_scratch, cols, k, channels);
+  channel_rank_kernel<<<blocks, 256, 0, stream>>>(score, cols, rank_scratch); HYC_LAUNCHED();
+  channel_gather_kernel<<<1, kGatherThreads, 0, stream>>>(rank_scratch, cols, k, channels); HYC_LAUNCHED();
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
 
@@ -198,8 +198,8 @@ int hyc_select_channels_noalloc(const float* score, int32_t cols, int32_t k, int
   }
   const int blocks = (cols + 255) / 256;
   // every rank in [0, cols) is rewritten by the first kernel, so nothing has to start at zero
-  channel_rank_kernel<<<blocks, 256, 0, stream>>>(score, cols, rank);
-  channel_gather_kernel<<<1, kGatherThreads, 0, stream>>>(rank, cols, k, channels);
+  channel_rank_kernel<<<blocks, 256, 0, stream>>>(score, cols, rank); HYC_LAUNCHED();
+  channel_gather_kernel<<<1, kGatherThreads, 0, stream>>>(rank, cols, k, channels); HYC_LAUNCHED();
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
 

@@ -13,7 +13,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace hyc {
+
+// Kernels this library has launched in this process (host-side bookkeeping, read through
+// hyc_launch_count(); a benchmark uses the difference across its timed region).
+extern std::atomic<unsigned long long> g_launch_count;
+#define HYC_LAUNCHED() ((void)::hyc::g_launch_count.fetch_add(1ull, std::memory_order_relaxed))
 
 constexpr int kMaxStages = 4;
 constexpr uint32_t kStatusPoolOverflow = 1u;

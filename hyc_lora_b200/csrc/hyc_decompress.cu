@@ -92,7 +92,7 @@ int hyc_decompress(const hyc_packed* in, const hyc_dense* o, void* stream_) {
     rc = set_smem(kern, bp.L.total);                                                            \
     if (rc) return rc;                                                                          \
     const int g = bp.rot == 2 ? bp.grid : resident_grid(kern, bp.threads, bp.L.total, bp.grid);    \
-    kern<<<g, bp.threads, bp.L.total, stream>>>(fa);                                            \
+    kern<<<g, bp.threads, bp.L.total, stream>>>(fa); HYC_LAUNCHED();                                            \
   }
       HYC_BWD_DISPATCH(bp, in->bits, 4, HYC_DECF)
 #undef HYC_DECF
@@ -119,7 +119,7 @@ int hyc_decompress(const hyc_packed* in, const hyc_dense* o, void* stream_) {
     auto kern = decompress_kernel<MODE, BITS>;                              \
     rc = set_smem(kern, plan.L.total);                                      \
     if (rc) return rc;                                                      \
-    kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a);             \
+    kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a); HYC_LAUNCHED();             \
   }
   HYC_DISPATCH_MODE_BITS(a.p.mode, a.p.bits, HYC_DEC_CASE)
 #undef HYC_DEC_CASE

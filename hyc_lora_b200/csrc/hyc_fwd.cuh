@@ -150,7 +150,7 @@ static int launch_fwd(const FwdArgs& a, const LaunchPlan& plan, cudaStream_t str
     auto kern = fwd_kernel<XT, MODE, BITS, NORM>;                                                    \
     int rc = set_smem(kern, plan.L.total);                                                           \
     if (rc) return rc;                                                                               \
-    kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a);                                      \
+    kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a); HYC_LAUNCHED();                                      \
     break;                                                                                           \
   }
   if (a.p.mode == kModeN) {

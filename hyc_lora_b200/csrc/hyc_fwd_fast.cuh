@@ -492,7 +492,7 @@ static int launch_fwd_fast(const FwdArgs& a, const LaunchPlan& plan, const FastP
       auto kern = fwd_n_fast_kernel<XT, BITS, NORM, UPT, ROT>;              \
       int rc = set_smem(kern, plan.L.total);                                \
       if (rc) return rc;                                                    \
-      kern<<<resident_grid(kern, plan.threads, plan.L.total, plan.grid), plan.threads, plan.L.total, stream>>>(a); \
+      kern<<<resident_grid(kern, plan.threads, plan.L.total, plan.grid), plan.threads, plan.L.total, stream>>>(a); HYC_LAUNCHED(); \
     } else {                                                                \
       return HYC_ERR_SMEM;                                                  \
     }                                                                       \

@@ -63,6 +63,6 @@ extern "C" int hyc_nf4_dequant(const void* codes, const float* absmax, const flo
   long long blocks = (n8 + per_block - 1) / per_block;
   if (blocks > 148 * 16) blocks = 148 * 16;
   hyc::nf4_dequant_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint32_t*>(codes), absmax, codebook, n8, static_cast<uint4*>(out_bf16));
+      static_cast<const uint32_t*>(codes), absmax, codebook, n8, static_cast<uint4*>(out_bf16)); HYC_LAUNCHED();
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }

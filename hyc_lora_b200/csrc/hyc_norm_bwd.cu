@@ -190,13 +190,13 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
       rc = set_smem(kern, bp.L.total);                                                          \
       if (rc) return rc;                                                                        \
       grid_used = resident_grid(kern, bp.threads, bp.L.total, bp.grid);                         \
-      kern<<<grid_used, bp.threads, bp.L.total, stream>>>(fa);                                  \
+      kern<<<grid_used, bp.threads, bp.L.total, stream>>>(fa); HYC_LAUNCHED();                                  \
     } else {                                                                                    \
       auto kern = norm_bwd_n_fast_kernel<B, UP, RT, float>;                                     \
       rc = set_smem(kern, bp.L.total);                                                          \
       if (rc) return rc;                                                                        \
       grid_used = resident_grid(kern, bp.threads, bp.L.total, bp.grid);                         \
-      kern<<<grid_used, bp.threads, bp.L.total, stream>>>(fa);                                  \
+      kern<<<grid_used, bp.threads, bp.L.total, stream>>>(fa); HYC_LAUNCHED();                                  \
     }                                                                                           \
   }
       HYC_BWD_DISPATCH(bp, saved->bits, 4, HYC_NBF)
@@ -204,7 +204,7 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
       cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return cuda_fail(e, "norm_bwd_n_fast_kernel launch");
       if (g->dweight) {
-        reduce_partials_kernel<<<(D + 127) / 128, 128, 0, stream>>>(g->partials, grid_used, D, g->dweight, g->dbias);
+        reduce_partials_kernel<<<(D + 127) / 128, 128, 0, stream>>>(g->partials, grid_used, D, g->dweight, g->dbias); HYC_LAUNCHED();
         e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(e, "reduce_partials_kernel launch");
       }
@@ -234,12 +234,12 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
       auto kern = norm_bwd_kernel<MODE, BITS, __nv_bfloat16>;               \
       rc = set_smem(kern, plan.L.total);                                    \
       if (rc) return rc;                                                    \
-      kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a);           \
+      kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a); HYC_LAUNCHED();           \
     } else {                                                                \
       auto kern = norm_bwd_kernel<MODE, BITS, float>;                       \
       rc = set_smem(kern, plan.L.total);                                    \
       if (rc) return rc;                                                    \
-      kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a);           \
+      kern<<<plan.grid, plan.threads, plan.L.total, stream>>>(a); HYC_LAUNCHED();           \
     }                                                                       \
   }
   HYC_DISPATCH_MODE_BITS(a.p.mode, a.p.bits, HYC_NB_CASE)
@@ -247,7 +247,7 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "norm_bwd_kernel launch");
   if (g->dweight) {
-    reduce_partials_kernel<<<(D + 127) / 128, 128, 0, stream>>>(g->partials, plan.grid, D, g->dweight, g->dbias);
+    reduce_partials_kernel<<<(D + 127) / 128, 128, 0, stream>>>(g->partials, plan.grid, D, g->dweight, g->dbias); HYC_LAUNCHED();
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "reduce_partials_kernel launch");
   }

@@ -63,6 +63,6 @@ extern "C" int hyc_rope(void* q, void* k, const float* cos_sin, int64_t tokens, 
   if (blocks > 148 * 16) blocks = 148 * 16;
   hyc::rope_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), cos_sin, tokens, seq, heads_q, heads_k, head_dim,
-      inverse ? -1.f : 1.f);
+      inverse ? -1.f : 1.f); HYC_LAUNCHED();
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }

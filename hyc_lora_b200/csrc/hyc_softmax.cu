@@ -138,6 +138,7 @@ int hyc_softmax_compact(const void* p, const float* thr, const hyc_sparse_rows* 
     softmax_compact_kernel<__nv_bfloat16><<<grid_for(out->rows), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(p), out->rows, out->cols, thr, static_cast<__nv_bfloat16*>(out->val),
         out->col, out->cap, out->used, meta, out->status);
+  HYC_LAUNCHED();
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
 
@@ -155,6 +156,7 @@ int hyc_softmax_expand(const hyc_sparse_rows* in, void* dense, void* stream_) {
     softmax_expand_kernel<__nv_bfloat16><<<grid_for(in->rows), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(in->val), in->col, meta, in->rows, in->cols,
         static_cast<__nv_bfloat16*>(dense));
+  HYC_LAUNCHED();
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
 
@@ -177,6 +179,7 @@ int hyc_softmax_bwd(const hyc_sparse_rows* in, const void* g, int g_dtype, void*
   else if (g_dtype == HYC_F32) HYC_SM_BWD(__nv_bfloat16, float, float);
   else HYC_SM_BWD(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
 #undef HYC_SM_BWD
+  HYC_LAUNCHED();
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }
 

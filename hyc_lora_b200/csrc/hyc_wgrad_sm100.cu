@@ -604,7 +604,7 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) !=       \
         cudaSuccess)                                                                                      \
       return HYC_ERR_CUDA;                                                                                \
-    kern<<<grid, kWgThreads, smem_bytes, stream>>>(a);                                                    \
+    kern<<<grid, kWgThreads, smem_bytes, stream>>>(a); HYC_LAUNCHED();                                                    \
   }
   if (saved->bits == 2) HYC_WG(2) else if (saved->bits == 4) HYC_WG(4) else HYC_WG(8)
 #undef HYC_WG
@@ -621,7 +621,7 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
       if (cudaFuncSetAttribute(wgrad_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
         return HYC_ERR_CUDA;
     wgrad_finish_kernel<<<dim3(rank, parts), 256, sm, stream>>>(partials, splits, side, pl.side_slices, saved->channels,
-                                                               pl.side_slices > 0 ? k : 0, rank, D, saved->rotate, out);
+                                                               pl.side_slices > 0 ? k : 0, rank, D, saved->rotate, out); HYC_LAUNCHED();
   }
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }

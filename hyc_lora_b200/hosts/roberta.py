@@ -105,15 +105,17 @@ class EncoderLayer(nn.Module):
 class EncoderClassifier(nn.Module):
     """Sequence classifier host; ``forward(ids, labels)`` returns the cross-entropy loss."""
 
-    def __init__(self, c: EncoderConfig, device="cuda", seed: int = 0):
+    def __init__(self, c: EncoderConfig, device="cuda", seed: int = 0, init_on_cpu: bool = False):
         super().__init__()
-        gen = torch.Generator(device=device)
+        # init_on_cpu draws every weight from a CPU generator (identical on any machine) and moves it
+        gen = torch.Generator(device="cpu" if init_on_cpu else device)
         gen.manual_seed(seed)
         self.config = c
         self.word = nn.Embedding(c.vocab, c.hidden, device=device, dtype=c.dtype)
         self.pos = nn.Embedding(c.max_pos, c.hidden, device=device, dtype=c.dtype)
         for e in (self.word, self.pos):
-            e.weight.data.normal_(0, 0.02, generator=gen)
+            w = torch.empty(e.weight.shape, device=gen.device, dtype=torch.float32).normal_(0, 0.02, generator=gen)
+            e.weight.data.copy_(w)
             e.weight.requires_grad_(False)
         self.emb_LayerNorm = nn.LayerNorm(c.hidden, eps=c.eps, device=device, dtype=c.dtype)
         self.emb_LayerNorm.weight.requires_grad_(False)
@@ -122,6 +124,11 @@ class EncoderClassifier(nn.Module):
         # the head trains, as in the reference (its dense layer is renamed so LoRA skips it)
         self.class_intermediate = nn.Linear(c.hidden, c.hidden, device=device, dtype=c.dtype)
         self.out_proj = nn.Linear(c.hidden, c.labels, device=device, dtype=c.dtype)
+        if init_on_cpu:
+            for lin in (self.class_intermediate, self.out_proj):
+                bound = 1.0 / math.sqrt(lin.in_features)
+                for p in (lin.weight, lin.bias):
+                    p.data.copy_(torch.empty(p.shape, dtype=torch.float32).uniform_(-bound, bound, generator=gen))
 
     def forward(self, ids, labels):
         s = ids.shape[1]

@@ -116,9 +116,14 @@ const char* hyc_strerror(int code);
 /* text of the last CUDA error seen by this library on the calling thread */
 const char* hyc_last_cuda_error(void);
 int hyc_version(void);
+/* Number of kernels this library has launched in this process so far (all threads, all streams;
+ * a launch recorded into a CUDA graph counts once, its replays do not).  Diagnostic only. */
+uint64_t hyc_launch_count(void);
 
-/* Optional launch tuning for experiments (0 = library default):
- * threads per row-CTA, staging depth, resident CTAs per SM. */
+/* Optional launch tuning for experiments (0 = library default): threads per row-CTA, staging
+ * depth, resident CTAs per SM.  The setting is PROCESS-GLOBAL and unsynchronised: it changes the
+ * launches of every thread and stream from then on, so set it before the threads that launch are
+ * started (or not at all); every other entry point keeps no mutable state. */
 int hyc_set_tuning(int threads, int stages, int ctas_per_sm);
 
 /* Compress-only (the sites that are not norms: LoRA-A linear input, SiLU/GELU

@@ -1,8 +1,9 @@
 """Import the reference's own ``operators`` package for pinning the oracle.
 
-TEST INFRASTRUCTURE ONLY.  The reference tree is present only on the
-development machine; ``load()`` returns ``None`` elsewhere, and callers skip.
-Nothing is copied: the modules are imported in place from the read-only tree.
+TEST INFRASTRUCTURE ONLY.  The modules are imported, unmodified, from the
+reference checkout when this machine has one, else from the staged copy that
+``oracle/make_ref.py`` leaves under ``oracle/_ref`` (not under version control);
+``load()`` returns ``None`` when neither exists, and callers skip.
 
 Two unused imports of the reference need stand-ins to import on a CPU box:
 ``bitsandbytes.functional`` (operators/efficient_linear.py:2) and the
@@ -16,9 +17,13 @@ import os
 import sys
 import types
 
-# the reference checkout: HYC_REFERENCE_ROOT, else a directory named "reference" next to this repository
-_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# the reference checkout: HYC_REFERENCE_ROOT, else a directory named "reference" next to this repository,
+# else the staged copy under oracle/_ref
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_REPO = os.path.dirname(_HERE)
 REFERENCE_ROOT = os.environ.get("HYC_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference"))
+if not os.path.isdir(os.path.join(REFERENCE_ROOT, "operators")) and os.path.isdir(os.path.join(_HERE, "_ref", "operators")):
+    REFERENCE_ROOT = os.path.join(_HERE, "_ref")
 
 _cached = None
 
@@ -49,6 +54,22 @@ def load():
                 "efficient_hadamard", "efficient_softmax", "efficient_gemm"):
         setattr(pkg, sub, importlib.import_module(f"hyc_reference_operators.{sub}"))
     _cached = pkg
+    return pkg
+
+
+def load_norms():
+    """The reference's three norm modules (Triton kernels inside; importing them needs no GPU, running
+    them does), or None when the reference or Triton is absent."""
+    pkg = load()
+    if pkg is None:
+        return None
+    import importlib
+    try:
+        for sub in ("efficient_rmsnorm", "efficient_rmsnorm_gemma", "efficient_layernorm"):
+            if not hasattr(pkg, sub):
+                setattr(pkg, sub, importlib.import_module(f"hyc_reference_operators.{sub}"))
+    except ImportError:
+        return None
     return pkg
 
 

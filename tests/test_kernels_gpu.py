@@ -291,10 +291,13 @@ def test_n_mode_ties_zero_rows_and_nonfinite_values(pk):
     ch = pk.select_channels(score, 3)
     assert ch.cpu().tolist() == [5, 100, 300]
     # codes of a row that holds a non-finite value outside the outlier channels are unspecified,
-    # but the call must stay inside its buffers and leave every other row exact
-    codes_guarded = torch.full((16 * 256 + 4096,), 0x5A, dtype=torch.uint8, device=DEV)
-    p = pk.compress_n(xd, ch, 4, 128, 0)
-    assert bool((codes_guarded == 0x5A).all())
+    # but the call must stay inside its buffers (every output is a view into one guarded allocation)
+    # and leave every other row exact
+    arena = _Arena(1 << 20)
+    p = _packed_n_in(arena, pk, 16, 512, 4, 128, 0, ch)
+    _compress_into(pk, xd, p)
+    torch.cuda.synchronize()
+    arena.check()
     xh = pk.decompress(p).cpu().reshape(16, 512)
     rows = [r for r in range(16) if r != 10]
     keep = [c for c in range(512) if c != 101]
@@ -501,3 +504,156 @@ def test_empty_batches_and_refused_arguments(pk):
         pk.compress_n(torch.zeros(4, d, dtype=torch.bfloat16, device=DEV), None, 4, 0, 96)       # rotation block
     with pytest.raises((RuntimeError, ValueError)):
         pk.compress_n(torch.zeros(4, d, dtype=torch.bfloat16), None, 4, 0, 0)                    # CPU tensor: no fallback
+
+
+# ------------------------------------------------------------------ guarded outputs
+
+
+class _Arena:
+    """One device allocation filled with a pattern.  Outputs are carved from its middle, 256-byte aligned
+    and a guard band apart; ``check`` asserts that every byte outside the carved regions still holds the
+    pattern, so a store that leaves its buffer on either side is seen."""
+    BAND, FILL = 4096, 0x5A
+
+    def __init__(self, nbytes):
+        self.buf = torch.full((nbytes,), self.FILL, dtype=torch.uint8, device=DEV)
+        self.pos, self.taken = self.BAND, []
+
+    def take(self, shape, dtype, zero=False):
+        n = 1
+        for v in shape:
+            n *= v
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = self.pos
+        assert start + nbytes + self.BAND <= self.buf.numel(), "arena too small"
+        self.pos = (start + nbytes + self.BAND + 255) // 256 * 256
+        self.taken.append((start, start + nbytes))
+        t = self.buf[start:start + nbytes].view(dtype).view(*shape)
+        if zero:
+            t.zero_()
+        return t
+
+    def check(self):
+        mask = torch.ones(self.buf.numel(), dtype=torch.bool, device=DEV)
+        for a, b in self.taken:
+            mask[a:b] = False
+        bad = (self.buf != self.FILL) & mask
+        assert not bool(bad.any()), f"bytes written outside the outputs at {bad.nonzero()[:8].flatten().tolist()}"
+
+
+def _packed_n_in(arena, pk, rows, d, bits, group, rotate, ch):
+    k = 0 if ch is None else ch.numel()
+    return pk.Packed(mode="N", bits=bits, rows=rows, cols=d, seq=rows, shape=(1, rows, d),
+                     codes=arena.take((rows, d * bits // 8), torch.uint8), status=arena.take((1,), torch.int32, zero=True),
+                     channels=ch, group=group, rotate=rotate,
+                     out_value=arena.take((rows, k), torch.bfloat16) if k else None,
+                     scales=arena.take((rows, d // group if group else 1), torch.float32))
+
+
+def _packed_r_in(arena, pk, rows, d, bits, thr, scale, pool_entries):
+    return pk.Packed(mode="R", bits=bits, rows=rows, cols=d, seq=rows, shape=(1, rows, d),
+                     codes=arena.take((rows, d * bits // 8), torch.uint8), status=arena.take((1,), torch.int32, zero=True),
+                     scale=scale.contiguous(), scale_kind=pk.scale_kind_of(scale), thr=thr.reshape(1).float(),
+                     pool=arena.take((pool_entries,), torch.int32), pool_used=arena.take((1,), torch.int32),
+                     row_meta=arena.take((rows, 2), torch.int32))
+
+
+def _dense(t, d):
+    from hyc_lora_b200 import _lib
+    r = _lib.HycDense()
+    r.base, r.dtype, r.chunks, r.row_stride = t.data_ptr(), (_lib.HYC_BF16 if t.dtype == torch.bfloat16 else _lib.HYC_F32), 1, d
+    return r
+
+
+def _compress_into(pk, x, p, norm=None):
+    """hyc_compress / hyc_norm_compress with every output already placed by the caller."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    rec, dn = p.record(), _dense(x, p.cols)
+    if norm is None:
+        _lib.check(_lib.lib.hyc_compress(C.byref(dn), C.byref(rec), pk._stream()), "hyc_compress")
+        return
+    n = _lib.HycNormFwd()
+    n.kind, n.eps = pk._NORM_KIND[norm["kind"]], 1e-5
+    n.weight, n.bias, n.param_dtype = norm["weight"].data_ptr(), None, _lib.HYC_BF16
+    n.y, n.rstd, n.mean = norm["y"].data_ptr(), norm["rstd"].data_ptr(), None
+    _lib.check(_lib.lib.hyc_norm_compress(C.byref(dn), C.byref(n), C.byref(rec), pk._stream()), "hyc_norm_compress")
+
+
+@pytest.mark.parametrize("d,bits,rotate,mode", [(768, 4, 0, "N"), (768, 4, 64, "N"), (11008, 4, 0, "N"), (11008, 2, 256, "N"),
+                                               (768, 4, 0, "R"), (11008, 4, 0, "R"), (4096, 8, 256, "N")])
+def test_kernels_write_nothing_outside_their_outputs(pk, d, bits, rotate, mode):
+    """Compress (alone and fused with the norm), decompress and norm backward with every output a view
+    into the middle of one guarded allocation: results equal the ordinary calls', both flanks of every
+    output stay untouched.  Row counts are odd so that the last CTA's walk ends mid-grid."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    rows = 301
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, salt=d + bits + rotate)
+    xd = x.to(DEV)
+    w = synthetic.norm_weight(d, 0.1).to(DEV)
+    dy = torch.randn(rows, d, generator=torch.Generator().manual_seed(d)).to(torch.bfloat16).to(DEV)
+    arena = _Arena(rows * d * 12 + (1 << 20))
+    if mode == "N":
+        ch = pk.select_channels(pk.channel_absmax(xd), oc.n_outlier_count(d, 0.01))
+        make = lambda: _packed_n_in(arena, pk, rows, d, bits, 0, rotate, ch)
+        plain = pk.compress_n(xd, ch, bits, 0, rotate)
+    else:
+        thr, _, _, scale = oc.r_calibrate(x.reshape(1, rows, d), 0.01, 1.0, bits, "per-channel", 0)
+        thr, scale = thr.to(DEV), scale.to(DEV)
+        entries = pk.default_pool_entries(rows, d, 0.01)
+        make = lambda: _packed_r_in(arena, pk, rows, d, bits, thr, scale, entries)
+        plain = pk.compress_r(xd.reshape(1, rows, d), thr, scale, bits)
+    p1, p2 = make(), make()
+    y, rstd = arena.take((rows, d), torch.bfloat16), arena.take((rows,), torch.float32)
+    _compress_into(pk, xd, p1)
+    _compress_into(pk, xd, p2, norm=dict(kind="rms", weight=w, y=y, rstd=rstd))
+    for p in (p1, p2):
+        assert torch.equal(p.codes, plain.codes) and int(p.status.item()) == 0
+    # decompress and norm backward into guarded outputs
+    xh = arena.take((rows, d), torch.bfloat16)
+    rec, out = p1.record(), _dense(xh, d)
+    _lib.check(_lib.lib.hyc_decompress(C.byref(rec), C.byref(out), pk._stream()), "hyc_decompress")
+    assert torch.equal(xh.reshape(-1), pk.decompress(plain).reshape(-1))
+    dx = arena.take((rows, d), torch.bfloat16)
+    a = _lib.HycNormBwdArgs()
+    a.kind, a.ref_compat_c2 = _lib.HYC_NORM_RMS, 1
+    a.weight, a.param_dtype, a.dy, a.dy_dtype = w.data_ptr(), _lib.HYC_BF16, dy.data_ptr(), _lib.HYC_BF16
+    a.rstd, a.mean, a.dx = rstd.data_ptr(), None, dx.data_ptr()
+    _lib.check(_lib.lib.hyc_norm_bwd(C.byref(rec), C.byref(a), pk._stream()), "hyc_norm_bwd")
+    want_dx, _, _ = pk.norm_bwd(plain, dy, w, rstd, None, "rms")
+    assert torch.equal(dx, want_dx)
+    torch.cuda.synchronize()
+    arena.check()
+
+
+def test_config1_in_channel_mode_on_its_own_tensor(pk):
+    """Configuration 1 as written: LayerNorm of the [8,128,768] fp32 activation, the top 1 % absmax
+    channels (8 of 768 -- they must be the planted ones) kept in full precision, the rest INT4 with one
+    absmax scale per token; then the LoRA-A gradients from the packed record against the oracle."""
+    x, planted = synthetic.roundtrip_activation()
+    a, grad = synthetic.lora_a_problem()
+    w, b = torch.ones(768), torch.zeros(768)
+    xd = x.to(DEV)
+    k = oc.n_outlier_count(768, 0.01)
+    assert k == 8
+    ch = pk.select_channels(pk.channel_absmax(xd), k)
+    assert torch.equal(ch.cpu().long(), planted)
+    p, y, rstd, mean = pk.compress_n(xd, ch, 4, 0, 0, norm=dict(kind="ln", weight=w.to(DEV), bias=b.to(DEV), eps=1e-5))
+    c = oc.n_compress(x.reshape(-1, 768), ch.cpu(), 4, 0, 0)
+    assert torch.equal(p.codes.cpu().reshape(c.codes.shape).view(torch.uint8), c.codes.view(torch.uint8))
+    assert torch.equal(p.scales.cpu(), c.scales) and torch.equal(p.out_value.cpu(), c.out_value)
+    y_o, mean_o, rstd_o = oc.norm_forward(x, w, b, 1e-5, "ln")
+    assert _rel_err(y, y_o) < 1e-4 and _rel_err(rstd, rstd_o) < 1e-5
+    xh_o = oc.n_decompress(c).reshape(x.shape)
+    assert torch.equal(pk.decompress(p).cpu(), xh_o)
+    # check (i): an upstream gradient applied at the LoRA-A output
+    dx_o, da_o = oc.linear_backward(xh_o, a.to(torch.bfloat16), grad)
+    da = pk.lora_wgrad(p, grad.to(DEV))
+    assert pk.lora_wgrad_supported(p, 16)
+    assert _cos(da, da_o) > 0.9999 and _rel_err(da, da_o.float()) < 1e-2
+    # LayerNorm backward from the packed record
+    g = torch.randn(8, 128, 768, generator=torch.Generator().manual_seed(5))
+    dxn, _, _ = pk.norm_bwd(p, g.to(DEV).reshape(-1, 768), w.to(DEV), rstd, mean, "ln")
+    dxn_o, _, _ = oc.norm_backward(xh_o, g, w, mean_o, rstd_o, "ln")
+    assert _rel_err(dxn.reshape(x.shape), dxn_o) < 1e-2

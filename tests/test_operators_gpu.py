@@ -355,3 +355,31 @@ def test_low_rank_site_and_calibration_state_roundtrip():
     x3 = x.to(DEV).requires_grad_(True)
     m(x3).backward(g.to(DEV))
     assert torch.equal(x2.grad, x3.grad)
+
+
+@pytest.mark.parametrize("extra", [{}, dict(outlier_mode="channel")])
+def test_config1_adapter_with_zero_b_gives_zero_da_and_the_oracles_db(extra):
+    """Configuration 1, check (ii): the full adapter ``base(x) + B(A(x)) * s`` with ``B = 0`` and an
+    upstream gradient G ~ N(0,1) on its output.  The chain rule gives dA = s * (G B)^T X = 0 exactly
+    (the weight-gradient kernel contracts an all-zero gradient with the packed input) and
+    dB = s * G^T (A x), which does not depend on the compressed copy at all."""
+    from hyc_lora_b200.hosts.lora import LoRALinear
+    from hyc_lora_b200.hosts.replace import replace_module, uniform_config
+    x, _ = synthetic.roundtrip_activation()
+    a, _ = synthetic.lora_a_problem()
+    g = _rand((8, 128, 768), 9, torch.float32)
+    m = LoRALinear(768, 768, r=16, alpha=16.0, quant="bf16", device=DEV, dtype=torch.float32)
+    m.base_layer.weight.data = m.base_layer.weight.data.float()
+    m.lora_A.weight.data.copy_(a)
+    assert replace_module(m, uniform_config(sub_outlier_bit=4, sub_outlier_quantize_method="per-token"), extra) == 1
+    assert float(m.lora_B.weight.abs().max()) == 0.0
+    for _ in range(3):                                   # two calibration calls, then the steady state
+        m.zero_grad(set_to_none=True)
+        xd = x.to(DEV).requires_grad_(True)
+        m(xd).backward(g.to(DEV))
+    da, db = m.lora_A.weight.grad, m.lora_B.weight.grad
+    assert da is not None and float(da.abs().max()) == 0.0
+    db_o = m.scaling * torch.einsum("bso,bsr->or", g, x @ a.T)
+    assert _cos(db, db_o) > 0.99999 and _rel(db, db_o) < 1e-3
+    # dX has no adapter share either: it is the frozen base's alone
+    assert _rel(xd.grad, g @ m.base_layer.weight.detach().cpu().float()) < 1e-3
