@@ -16,10 +16,15 @@ The JSON line also carries
   e2e           the same metric through the C ABI with HOST buffers: pinned
                 host -> device copy of the rows, kernel, device -> host copy of
                 everything the kernel produced, all inside the timed region
-  cpu_baseline  the CPU oracle (a PyTorch port of the reference's eager chain)
-                timed on this box's host cores on a bounded sample
+  cpu_baseline  the reference's own CPU chain for a norm site -- the RMSNorm formula of its
+                model file, then its unmodified true_divide_outlier_suboutlier_svd_compress
+                (per-channel INT4 static scale, element outliers) -- on the same tensor, on
+                this box's host cores (kind "reference" when the staged copy of the reference
+                is present, else the CPU oracle's bit-exact restatement, kind "port")
+  r_mode        this library's kernel doing that same reference arithmetic on the GPU
+  kernels       per-kernel GB/s of the backward-side kernels (CUDA-graph replay)
   clocks        SM clocks / throttle reasons sampled during the timed region
-``--impl reference`` times that CPU path alone, as its own arm.
+``--impl reference`` times the CPU chain alone, as its own arm.
 """
 from __future__ import annotations
 
@@ -134,50 +139,120 @@ class ClockSampler:
 
 # ------------------------------------------------------------------ CPU arm
 
-def cpu_arm(sample_rows: int, repeats: int):
-    """The oracle's norm + channel-outlier compression on the host cores (all threads)."""
+CPU_PIECE_ROWS = 16384        # rows handed to the reference chain per call (bounds its temporaries)
+SEQ = 512                     # the [T, D] rows are seen as [T / 512, 512, D], as a training batch would be
+
+
+def rank_rows(rank: int):
+    """The seeded rows of one rank, bf16 [ROWS, COLS] (generated in 8192-row pieces), and the planted channels."""
     import torch
     from hyc_lora_b200 import synthetic
+    pieces = [synthetic.sweep_activation(8192, COLS, FRACTION, salt=1000 * rank + i)[0] for i in range(ROWS // 8192)]
+    planted = synthetic.sweep_activation(8192, COLS, FRACTION, salt=1000 * rank)[1].to(torch.int32)
+    return torch.cat(pieces), planted
+
+
+def cpu_chain():
+    """The reference's CPU work at one norm site in steady state, as ``(calibrate, step, kind, what)``.
+
+    ``step(x3, w, stats)`` runs the RMSNorm formula of the reference's model file
+    (models/modeling_llama.py:136-141) and then the compression of the norm input exactly as
+    EfficientMemoryRMSNormFunc.forward does after its norm kernel (operators/efficient_rmsnorm.py:193-201):
+    per-channel INT4 static scale, element outliers above the calibrated threshold, rank 0.  With the staged
+    copy of the reference present the compression is its own, unmodified
+    true_divide_outlier_suboutlier_svd_compress (operators/compress_function.py:136-200); otherwise the CPU
+    oracle's restatement of it, which is pinned bit for bit to that function."""
+    import torch
+    from oracle import ref_loader
+    ref = ref_loader.load()
+
+    def rmsnorm(x3, w):
+        v = x3.to(torch.float32).pow(2).mean(-1, keepdim=True)
+        return w * (x3.to(torch.float32) * torch.rsqrt(v + 1e-5)).to(x3.dtype)
+
+    if ref is not None:
+        cf = ref.compress_function
+
+        def calibrate(x3):
+            return cf.get_statistics(x3[:1], 0, FRACTION, 1.0, BITS, "per-channel", 0)
+
+        def step(x3, w, stats):
+            thr, L, R, scale = stats
+            y = rmsnorm(x3, w)
+            return y, cf.true_divide_outlier_suboutlier_svd_compress(x3, thr, scale, BITS, 1.0, L, R)
+
+        return calibrate, step, "reference", ("the reference's own operators/compress_function.py, imported unmodified, "
+                                              "after the RMSNorm formula of its model file")
     from oracle import hyc_oracle as oc
+
+    def calibrate(x3):
+        return oc.r_calibrate(x3[:1], FRACTION, 1.0, BITS, "per-channel", 0)
+
+    def step(x3, w, stats):
+        thr, L, R, scale = stats
+        y = rmsnorm(x3, w)
+        return y, oc.r_compress(x3, thr, scale, BITS, 1.0)
+
+    return calibrate, step, "port", ("CPU restatement of the reference's compress chain (bit-exact against it), "
+                                     "after the RMSNorm formula of its model file; the reference tree is not on this box")
+
+
+def cpu_arm(x, rows_per_step: int, repeats: int, budget_s: float = 150.0):
+    """Time ``repeats`` steps of the CPU chain over the first ``rows_per_step`` rows of ``x`` (bf16 [T, D]) with all
+    host threads.  If the first step says the run would not fit ``budget_s`` the rows per step are cut (in whole
+    pieces) and the figure says so.  Returns (bytes per step, per-step seconds, cores, kind, description, rows)."""
+    import torch
+    from hyc_lora_b200 import synthetic
+    from hyc_lora_b200.operators.compress_function import outlier_channel_count
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    x, _ = synthetic.sweep_activation(sample_rows, COLS, FRACTION)
+    calibrate, step, kind, what = cpu_chain()
     w = synthetic.norm_weight(COLS)
-    k = oc.n_outlier_count(COLS, FRACTION)
-    ch = oc.n_select_channels(oc.n_channel_scores(x), k)
+    k = outlier_channel_count(COLS, FRACTION)
     groups = 1 if GROUP == 0 else COLS // GROUP
-    nbytes = algorithmic_bytes_per_row(COLS, BITS, k, groups) * sample_rows
+    from oracle import ref_loader
+    with ref_loader.cpu_cuda_noop():
+        stats = calibrate(x[:CPU_PIECE_ROWS].reshape(-1, SEQ, COLS))
 
-    def one():
-        oc.norm_forward(x, w, None, 1e-5, "rms")
-        oc.n_compress(x, ch, BITS, GROUP, ROTATE)
+        def one(rows):
+            for r0 in range(0, rows, CPU_PIECE_ROWS):
+                step(x[r0:min(rows, r0 + CPU_PIECE_ROWS)].reshape(-1, SEQ, COLS), w, stats)
 
-    one()
-    times = []
-    for _ in range(repeats):
         t = time.perf_counter()
-        one()
-        times.append(time.perf_counter() - t)
-    return nbytes, times, cores
+        one(min(rows_per_step, CPU_PIECE_ROWS))                       # warm-up on one piece, also the speed probe
+        probe = (time.perf_counter() - t) / min(rows_per_step, CPU_PIECE_ROWS)
+        fit = int(budget_s / max(repeats, 1) / probe) // CPU_PIECE_ROWS * CPU_PIECE_ROWS
+        rows = max(CPU_PIECE_ROWS, min(rows_per_step, fit)) if rows_per_step > CPU_PIECE_ROWS else rows_per_step
+        times = []
+        for _ in range(repeats):
+            t = time.perf_counter()
+            one(rows)
+            times.append(time.perf_counter() - t)
+    # the same nominal bytes per row as the GPU arm, so that the ratio of the two figures is a ratio of times
+    nbytes = algorithmic_bytes_per_row(COLS, BITS, k, groups) * rows
+    return nbytes, times, cores, kind, what, rows
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 2048
-    nbytes, times, cores = cpu_arm(sample, args.warmup + args.steps)
+    x, _ = rank_rows(0)
+    nbytes, times, cores, kind, what, rows = cpu_arm(x, ROWS, args.warmup + args.steps)
     times = times[args.warmup:]
     total = sum(times)
     value = nbytes * len(times) / total / 1e9
+    sample = f"{rows} of {ROWS} rows per step x {len(times)} steps" + ("" if rows == ROWS else " (cut to fit the time budget)")
     line = {
         "impl": "reference", "metric": "fused norm+compress HBM GB/s", "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": workload_name(), "sample": f"{sample} of {ROWS} rows per step"},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"{sample} rows x {len(times)} steps of the same workload; PyTorch CPU port of the "
-                                   "reference's eager norm + compress chain (the reference tree is not on this box)"},
+        "config": {"workload": workload_name(), "rows_per_step": rows, "cols": COLS, "bits": BITS,
+                   "cpu_arithmetic": "the reference's own: element outliers above a calibrated threshold, static "
+                                     "per-channel INT4 scale (the GPU arm's default line is the channel-outlier mode; its "
+                                     "r_mode record is this arithmetic on the GPU)",
+                   "bytes_per_row": nbytes // rows},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample + "; " + what},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -185,6 +260,99 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------ GPU arm
+
+def graph_timed(fn, nbytes, name, peak, reps=16, replays=3):
+    """fn(i): one call on input set i.  The calls are recorded in a CUDA graph (so that host overhead of the
+    Python wrappers does not hide short kernels) and cycle through input sets whose total size exceeds L2."""
+    import torch
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fn(0)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(reps):
+                fn(i)
+    torch.cuda.synchronize()
+    graph.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(replays):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / (replays * reps)
+    return {"kernel": name, "ms": round(ms, 4), "bytes": int(nbytes), "GBps": round(nbytes / ms / 1e6, 1),
+            "frac": round(nbytes / ms / 1e6 / peak, 3)}
+
+
+def kernel_list(packed, x, w, channels, k, peak):
+    """Metric 1 beyond the headline kernel: the backward-side kernels (decompress, decompress + SiLU backward,
+    decompress + norm backward) and the forward at the smaller size, with and without the 256-wide rotation,
+    INT4, per-token scale, 1 % outlier channels; CUDA-graph replay over input sets larger than L2."""
+    import torch
+    d = x.shape[1]
+    out = []
+    norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
+    base = d * BITS // 8 + 2 * k + 4
+    for rows in (65536, 16384):
+        sets = [x[i * rows:(i + 1) * rows] for i in range(x.shape[0] // rows)]
+        n = len(sets)
+        dys = [torch.randn(rows, d, device=x.device, dtype=torch.bfloat16) for _ in range(max(1, min(n, 4)))]
+        rstd = torch.ones(rows, device=x.device)
+        for rotate in (0, 256):
+            tag = f"T={rows} b={BITS} rot={rotate}"
+            if rows != ROWS or rotate:
+                out.append(graph_timed(lambda i: packed.compress_n(sets[i % n], channels, BITS, 0, rotate, norm=norm),
+                                       algorithmic_bytes_per_row(d, BITS, k, 1) * rows, "norm+compress " + tag, peak))
+            ps = [packed.compress_n(s_, channels, BITS, 0, rotate) for s_ in sets]
+            out.append(graph_timed(lambda i: packed.decompress(ps[i % n]), (base + 2 * d) * rows, "decompress " + tag, peak))
+            out.append(graph_timed(lambda i: packed.act_bwd("silu", ps[i % n], dys[i % len(dys)]), (base + 4 * d) * rows,
+                                   "silu_bwd " + tag, peak))
+            out.append(graph_timed(lambda i: packed.norm_bwd(ps[i % n], dys[i % len(dys)], w, rstd, None, "rms"),
+                                   (base + 4 + 4 * d) * rows, "norm_bwd " + tag, peak))
+            del ps
+        del dys
+    # the one dense contraction of the path: LoRA-A weight gradient from the packed codes (tensor roofline)
+    p = packed.compress_n(x, channels, BITS, 0, 0)
+    g = torch.randn(x.shape[0], 64, device=x.device, dtype=torch.bfloat16)
+    rec = graph_timed(lambda i: packed.lora_wgrad(p, g), x.shape[0] * (d * BITS // 8 + 2 * 64 + 4 + 2 * k) + 4 * 64 * d,
+                      f"lora_wgrad tcgen05 T={x.shape[0]} b={BITS} r=64", peak)
+    rec["TFLOPs"] = round(2.0 * x.shape[0] * 64 * d / (rec["ms"] * 1e-3) / 1e12, 1)
+    rec["bound"] = "tensor"
+    out.append(rec)
+    return out
+
+
+def r_mode_record(packed, x, w, peak, steps):
+    """The reference's own arithmetic on the GPU, on the same tensor: hyc_norm_compress in reference mode with a
+    static per-channel INT4 scale and element outliers above the calibrated threshold (statistics as the reference
+    calibrates them, from batch element 0 of the [T/512, 512, D] view; not timed)."""
+    import torch
+    from hyc_lora_b200.operators import compress_function as cf
+    x3 = x.reshape(-1, SEQ, COLS)
+    thr, _, _, scale = cf.get_statistics(x3[:1], 0, FRACTION, 1.0, BITS, "per-channel", 0)
+    norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
+    for _ in range(3):
+        p, y, rstd, _ = packed.compress_r(x3, thr, scale, BITS, outlier_ratio=FRACTION, norm=norm)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        p, y, rstd, _ = packed.compress_r(x3, thr, scale, BITS, outlier_ratio=FRACTION, norm=norm)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    stored = int(p.pool_used.item())
+    # read x, write y, codes, 4 B per stored outlier, 8 B row record, rstd
+    nbytes = (4 * COLS + COLS * BITS // 8 + 8 + 4) * ROWS + 4 * stored
+    return {"kernel": "hyc::fwd_r_fast_kernel (fused RMSNorm + reference-mode compress)", "ms": round(ms, 4),
+            "bytes": nbytes, "GBps": round(nbytes / ms / 1e6, 1), "frac": round(nbytes / ms / 1e6 / peak, 3),
+            "stored_outliers": stored, "status": int(p.status.item()),
+            "scale": "static per-channel INT4 (calibrated)", "outliers": "elements above the calibrated threshold"}
+
 
 def run_ours(args):
     import torch
@@ -199,19 +367,17 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    from hyc_lora_b200 import packed, synthetic
-    from oracle import hyc_oracle as oc
+    from hyc_lora_b200 import _lib, packed, synthetic
+    from hyc_lora_b200.operators.compress_function import outlier_channel_count
 
-    k = oc.n_outlier_count(COLS, FRACTION)
+    k = outlier_channel_count(COLS, FRACTION)
     groups = 1 if GROUP == 0 else COLS // GROUP
-    # seeded rows of this rank (different salt per rank); generated in 8192-row pieces
-    pieces = [synthetic.sweep_activation(8192, COLS, FRACTION, salt=1000 * rank + i)[0] for i in range(ROWS // 8192)]
-    x_host = torch.cat(pieces).pin_memory()
-    del pieces
-    channels_host = synthetic.sweep_activation(8192, COLS, FRACTION, salt=1000 * rank)[1].to(torch.int32)
+    # seeded rows of this rank (different salt per rank)
+    x_cpu, _planted = rank_rows(rank)
+    x_host = x_cpu.pin_memory()
     x = x_host.to(dev, non_blocking=True)
     w = synthetic.norm_weight(COLS).to(dev)
-    # calibration (not timed): column absmax + top-k on the GPU; the planted set must come back
+    # calibration (not timed): column absmax + top-k on the GPU
     channels = packed.select_channels(packed.channel_absmax(x), k)
     norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
     bytes_per_step = algorithmic_bytes_per_row(COLS, BITS, k, groups) * ROWS
@@ -224,7 +390,7 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    warm = max(args.warmup, 10)              # clocks and caches settle within the first few launches
+    warm = max(args.warmup, 3)               # at least three untimed launches (clocks, caches)
     for _ in range(warm):
         out = step()
     barrier()
@@ -235,10 +401,12 @@ def run_ours(args):
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.time()
+    launches0 = int(_lib.lib.hyc_launch_count())
     start.record()
     for _ in range(args.steps):
         out = step()
     stop.record()
+    launches = int(_lib.lib.hyc_launch_count()) - launches0     # counted by the library, one per kernel it launched
     barrier()
     t1 = time.time()
     ms = start.elapsed_time(stop)
@@ -322,27 +490,37 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": workload_name(), "rows_per_gpu": ROWS, "cols": COLS, "bits": BITS,
                        "outlier_channels": k, "scale": "per-token absmax", "l2": "inputs (537 MB per step) exceed the 126 MB L2",
-                       "algorithmic_bytes_per_row": bytes_per_step // ROWS},
+                       "algorithmic_bytes_per_row": bytes_per_step // ROWS,
+                       "mode": "channel-outlier mode (the north star's arithmetic; the reference has no counterpart, so "
+                               "the CPU arm runs the reference's own element-outlier arithmetic on the same tensor and "
+                               "`r_mode` is this library doing that arithmetic on the GPU)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": committed_traffic(), "peak_source": f"of {which}",
+                         "traffic_note": "lower bound (>=): ncu capture of 16384 rows scaled x4; the tail of y still in L2 "
+                                         "when the kernel ends is not counted as a DRAM write",
                          "kernel": "hyc::fwd_n_fast_kernel<bf16, 4, norm, 2, 0>"},
             "e2e": {"value": (bytes_per_step * e2e_steps * world) / (e2e_ms / 1e3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "pipeline": f"{len(pieces)} pieces of {piece} rows; H2D, kernel and D2H on three streams"},
-            "gpu_launches": args.steps,
+            "gpu_launches": launches,
             "clocks": clocks,
         }
-        # bounded CPU sample of the same workload (about 10-20 s); single-GPU runs only, so that the
-        # host cores are not shared with other ranks
-        if world == 1:
-            nbytes, times, cores = cpu_arm(2048, 5)
-            line["cpu_baseline"] = {"value": nbytes / statistics.median(times) / 1e9, "unit": "GB/s", "cores": cores,
-                                    "kind": "port", "sample": "2048 of 65536 rows, median of 5 runs, PyTorch CPU port of "
-                                                              "the reference's eager norm + compress chain"}
-        if args.sweep:
-            line["sweep"] = sweep(packed, synthetic, oc, x, w, peak)
+    del xin, out, y, rstd, y_host, codes_host, oval_host, scales_host, rstd_host
+    if rank == 0 and world == 1:
+        # single-GPU runs only: the other kernels of metric 1, the reference's arithmetic on the GPU, and the
+        # reference's CPU chain on the same tensor (the host cores are not shared with other ranks)
+        try:
+            line["r_mode"] = r_mode_record(packed, x, w, peak, max(5, min(args.steps, 20)))
+            line["kernels"] = kernel_list(packed, x, w, channels, k, peak)
+        except Exception as e:  # the headline must still be printed
+            line["kernels_error"] = f"{type(e).__name__}: {e}"[:300]
+        nbytes, times, cores, kind, what, rows = cpu_arm(x_cpu, ROWS, 5, budget_s=40.0)
+        line["cpu_baseline"] = {"value": nbytes / statistics.median(times) / 1e9, "unit": "GB/s", "cores": cores,
+                                "kind": kind, "sample": f"{rows} of {ROWS} rows, median of 5 runs; {what}"}
+    if rank == 0 and args.sweep:
+        line["sweep"] = sweep(packed, synthetic, x, w, peak)
     # free the operator benchmark's buffers before the model is built
-    del x, xin, out, p, y, rstd, x_host, y_host, codes_host
+    del x, p, x_host, x_cpu
     torch.cuda.empty_cache()
     step = None
     if not args.no_step:
@@ -403,7 +581,25 @@ def train_step_bench(args, world, rank, dev, barrier):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     tokens = batch * seq * world * steps
-    return {"metric": "7B HyC-LoRA train tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s",
+    # model flops per token: frozen base linears forward + input gradient (4 per weight), adapters forward +
+    # both gradients (6 per weight), causal attention forward + backward (6 * seq * hidden per layer)
+    from hyc_lora_b200.hosts.lora import FrozenLinear
+    cfg = trainer.model.config
+    p_base = sum(m.in_features * m.out_features for m in trainer.model.modules() if isinstance(m, FrozenLinear))
+    p_lora = trainer.trainable()
+    flops_token = 4 * p_base + 6 * p_lora + 6 * seq * cfg.hidden * cfg.layers
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    tensor_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    achieved_tf = tokens / world / (ms / 1e3) * flops_token / 1e12      # per GPU
+    roof = {"bound": "tensor", "achieved": round(achieved_tf, 1), "peak": tensor_peak, "unit": "TFLOP/s",
+            "frac": round(achieved_tf / tensor_peak, 3), "per": "GPU",
+            "peak_source": "of measured (sustained bf16 GEMM)" if "bf16_tflops_sustained" in peaks else "of fallback",
+            "flops_per_token": flops_token, "base_params": p_base, "lora_params": p_lora}
+    return {"metric": "7B HyC-LoRA train tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s", "roofline": roof,
             "ms_per_step": ms / steps, "steps": steps, "loss": float(loss_host.item()), "cuda_graph": bool(graphed),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
             "config": {"model": ("Mistral-7B" if mistral else "LLaMA-2-7B") + " shape, random init, 4-bit codebook base (block 64)",
@@ -414,9 +610,10 @@ def train_step_bench(args, world, rank, dev, barrier):
                        "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": 4}}
 
 
-def sweep(packed, synthetic, oc, x, w, peak):
+def sweep(packed, synthetic, x, w, peak):
     """Per-kernel GB/s for the operator sweep of configuration 5 (informational)."""
     import torch
+    from hyc_lora_b200.operators import compress_function as cf
     rows_all, d = x.shape
     out = []
 
@@ -453,7 +650,7 @@ def sweep(packed, synthetic, oc, x, w, peak):
         n = len(sets)
         dys = [torch.randn(rows, d, device=x.device, dtype=torch.bfloat16) for _ in range(min(n, 4))] if rows != 65536 else []
         for frac in (0.005, 0.01, 0.02):
-            k = oc.n_outlier_count(d, frac)
+            k = cf.outlier_channel_count(d, frac)
             ch = packed.select_channels(score, k)
             for bits in (2, 4, 8):
                 for group in (0, 128):
@@ -479,7 +676,7 @@ def sweep(packed, synthetic, oc, x, w, peak):
     # dequant-fused tensor-core weight gradient vs. decompress + library GEMM
     for rows, bits, rank in ((65536, 4, 64), (65536, 4, 16), (65536, 2, 64), (65536, 8, 64), (2048, 4, 64)):
         xs = x[:rows]
-        k = oc.n_outlier_count(d, 0.01)
+        k = cf.outlier_channel_count(d, 0.01)
         ch = packed.select_channels(score, k)
         p = packed.compress_n(xs, ch, bits, 0, 0)
         g = torch.randn(rows, rank, device=x.device, dtype=torch.bfloat16)
@@ -492,10 +689,8 @@ def sweep(packed, synthetic, oc, x, w, peak):
             rec["TFLOPs"] = round(2.0 * rows * rank * d / (rec["ms"] * 1e-3) / 1e12, 1)
     # reference mode, one line per bit width (static per-channel scales)
     xs = x[:16384]
-    xc = xs.float().cpu()[:512].to(torch.bfloat16).reshape(1, 512, d)
     for bits in (2, 4, 8):
-        thr, L, R, scale = oc.r_calibrate(xc, 0.01, 1.0, bits, "per-channel", 0)
-        thr, scale = thr.to(x.device), scale.to(x.device)
+        thr, L, R, scale = cf.get_statistics(xs[:512].reshape(1, 512, d), 0, 0.01, 1.0, bits, "per-channel", 0)
         nb = (2 * d + d * bits // 8 + 8) * 16384 + int(0.02 * 16384 * d) * 4
         timed(lambda i: packed.compress_r(xs, thr, scale, bits), nb, f"R-mode compress T=16384 b={bits} per-channel")
         timed(lambda i: packed.compress_r(xs, thr, scale, bits, norm=norm), nb + (2 * d + 4) * 16384,
@@ -507,12 +702,12 @@ def run_case(args):
     """A few launches of one kernel on a small case (inputs still larger than L2), for profilers."""
     import torch
     from hyc_lora_b200 import packed, synthetic
-    from oracle import hyc_oracle as oc
+    from hyc_lora_b200.operators import compress_function as cf
     torch.cuda.set_device(0)
     rows = args.rows
     x = synthetic.sweep_activation(rows, COLS, FRACTION)[0].to("cuda")
     w = synthetic.norm_weight(COLS).to("cuda")
-    k = oc.n_outlier_count(COLS, FRACTION)
+    k = cf.outlier_channel_count(COLS, FRACTION)
     ch = packed.select_channels(packed.channel_absmax(x), k)
     norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
     dy = torch.randn(rows, COLS, device="cuda", dtype=torch.bfloat16)
@@ -521,8 +716,7 @@ def run_case(args):
     if args.mode == "R":
         # reference mode: statistics as the reference calibrates them (batch element 0 of a [T/512, 512, D] view)
         x3 = x.reshape(rows // 512, 512, COLS)
-        thr, _, _, scale = oc.r_calibrate(x3[:1].cpu(), 0.01, 1.0, BITS, "per-channel", 0, 0)
-        thr, scale = thr.cuda(), scale.cuda()
+        thr, _, _, scale = cf.get_statistics(x3[:1], 0, 0.01, 1.0, BITS, "per-channel", 0)
         p = packed.compress_r(x3, thr, scale, BITS, outlier_ratio=0.01)
         dy3 = dy.reshape(x3.shape)
         fns = {

@@ -86,6 +86,7 @@ SYMBOLS = {
     "hyc_version": (C.c_int, []),
     "hyc_launch_count": (C.c_uint64, []),
     "hyc_set_tuning": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "hyc_debug_wait": (C.c_int, [C.c_int64, C.c_uint32]),
     "hyc_compress": (C.c_int, [C.POINTER(HycDense), C.POINTER(HycPacked), C.c_void_p]),
     "hyc_decompress": (C.c_int, [C.POINTER(HycPacked), C.POINTER(HycDense), C.c_void_p]),
     "hyc_norm_compress": (C.c_int, [C.POINTER(HycDense), C.POINTER(HycNormFwd), C.POINTER(HycPacked), C.c_void_p]),

@@ -7,6 +7,8 @@ namespace hyc {
 thread_local char g_cuda_error[256] = "";
 int g_tune_threads = 0, g_tune_stages = 0, g_tune_ctas = 0;
 std::atomic<unsigned long long> g_launch_count{0};
+long long g_debug_wait_cycles = 0;
+unsigned int g_debug_tx_pad = 0;
 
 static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, cudaStream_t stream) {
   const int empty = packed_is_empty(out);
@@ -128,6 +130,13 @@ int hyc_set_tuning(int threads, int stages, int ctas_per_sm) {
   if (threads != 0 && (threads < 32 || threads > 512 || threads % 32 != 0)) return HYC_ERR_SHAPE;
   if (stages < 0 || stages > kMaxStages || ctas_per_sm < 0 || ctas_per_sm > 16) return HYC_ERR_SHAPE;
   g_tune_threads = threads; g_tune_stages = stages; g_tune_ctas = ctas_per_sm;
+  return HYC_OK;
+}
+
+int hyc_debug_wait(int64_t wait_cycles, uint32_t tx_pad_bytes) {
+  if (wait_cycles < 0 || wait_cycles > kWaitCycles || tx_pad_bytes > 4096 || tx_pad_bytes % 16 != 0) return HYC_ERR_SHAPE;
+  g_debug_wait_cycles = wait_cycles;
+  g_debug_tx_pad = tx_pad_bytes;
   return HYC_OK;
 }
 

@@ -79,6 +79,8 @@ struct BwdSmem {
   uint32_t off_csc, off_csc2;   // reference mode: per-channel scales (bf16 [D]) of the operands
   uint32_t off_lr, off_lr2;     // reference mode: low-rank rows inside a staging slot
   int stages;
+  uint32_t debug_tx_pad;        // test hook: bytes a row announces beyond what is copied (0 in normal use)
+  long long wait_cycles;        // limit of the waits on staged rows
 };
 
 // Per-thread register groups: NR groups of 8 channels; col[r] < 0 marks an idle group.
@@ -272,6 +274,7 @@ struct RowFeed {
   const unsigned char* base[5];
   int period[5];   // 0: one source row per row; n: source row = row % n (low-rank rows repeat every sequence)
   int streams;
+  uint32_t tx_pad;
   __device__ __forceinline__ void add(const void* src, uint32_t nbytes, uint32_t off, int per = 0) {
     base[streams] = static_cast<const unsigned char*>(src);
     bytes[streams] = nbytes; offset[streams] = off; period[streams] = per;
@@ -280,7 +283,7 @@ struct RowFeed {
   __device__ __forceinline__ void issue(int stage, long long row) {
     uint32_t total = 0;
     for (int q = 0; q < streams; ++q) total += bytes[q];
-    mbar_expect_tx(&ring.bars[stage], total);
+    mbar_expect_tx(&ring.bars[stage], total + tx_pad);
     for (int q = 0; q < streams; ++q) {
       const long long src_row = period[q] ? row % period[q] : row;
       bulk_g2s(ring.slot(stage) + offset[q], base[q] + src_row * bytes[q], bytes[q], &ring.bars[stage]);
@@ -313,8 +316,10 @@ struct FeedSetup {
 __device__ __forceinline__ FeedSetup feed_setup(unsigned char* smem, const BwdSmem& L) {
   FeedSetup s;
   s.feed.ring = RowRing{reinterpret_cast<uint64_t*>(smem), smem + L.off_slots, L.slot_bytes, L.stages};
+  s.feed.ring.wait_cycles = L.wait_cycles;
   s.feed.ring.init();
   s.feed.streams = 0;
+  s.feed.tx_pad = L.debug_tx_pad;
   s.chan = reinterpret_cast<int*>(smem + L.off_chan);
   s.chan2 = reinterpret_cast<int*>(smem + L.off_chan2);
   s.w_rot = reinterpret_cast<float*>(smem + L.off_rot);
@@ -325,7 +330,7 @@ __device__ __forceinline__ FeedSetup feed_setup(unsigned char* smem, const BwdSm
 
 // bounded wait on slot `st` in barrier phase `ph`; an expired wait raises the CTA's sticky flag
 __device__ __forceinline__ void feed_wait(FeedSetup& s, int st, uint32_t ph) {
-  if (!mbar_wait_bounded(&s.feed.ring.bars[st], ph)) s.misc[0] = 1;
+  if (!mbar_wait_bounded(&s.feed.ring.bars[st], ph, s.feed.ring.wait_cycles)) s.misc[0] = 1;
 }
 
 // next ring position / barrier phase (counters instead of divisions by the run-time stage count)
@@ -867,6 +872,8 @@ inline BwdPlan plan_bwd_fast(const hyc_packed* q, const hyc_packed* q2, int reg_
   if (b.L.stages > kMaxStages) b.L.stages = kMaxStages;
   while (b.L.stages > 2 && off + b.L.slot_bytes * b.L.stages > 64 * 1024) --b.L.stages;
   b.L.total = off + b.L.slot_bytes * b.L.stages;
+  b.L.debug_tx_pad = g_debug_tx_pad;
+  b.L.wait_cycles = g_debug_wait_cycles > 0 ? g_debug_wait_cycles : kWaitCycles;
   if (b.L.total > kSmemPerCtaMax) { b.ok = false; return b; }
   int ctas = g_tune_ctas ? g_tune_ctas : 2048 / b.threads;
   while (ctas > 1 && (static_cast<uint32_t>(ctas) * (b.L.total + 1024) > kSmemBudget || ctas * b.threads > 2048)) --ctas;

@@ -74,12 +74,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: gives up after about a second of SM clocks and reports false.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+// Bounded wait: gives up after `limit` SM clocks (by default about a second) and reports false.
+constexpr long long kWaitCycles = 2000000000LL;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, long long limit = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > 2000000000LL) return false;
+    if (clock64() - start > limit) return false;
   }
   return true;
 }
@@ -210,6 +211,7 @@ struct RowRing {
   unsigned char* slots;  // stages * slot_bytes, 128-byte aligned
   uint32_t slot_bytes;
   int stages;
+  long long wait_cycles = kWaitCycles;   // limit of every wait on this ring's barriers
 
   __device__ __forceinline__ unsigned char* slot(int s) const { return slots + static_cast<size_t>(s) * slot_bytes; }
 

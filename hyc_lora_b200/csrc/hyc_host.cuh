@@ -16,6 +16,8 @@ namespace hyc {
 
 extern thread_local char g_cuda_error[256];
 extern int g_tune_threads, g_tune_stages, g_tune_ctas;
+extern long long g_debug_wait_cycles;   // 0: default limit
+extern unsigned int g_debug_tx_pad;     // bytes added to what a staged row announces (test of the give-up path)
 
 inline int cuda_fail(cudaError_t e, const char* what) {
   snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", what, cudaGetErrorString(e));
@@ -196,7 +198,7 @@ __device__ inline void drain_ring(RowRing& ring, int i_done, long long next_row,
   for (int s = 1; s <= last; ++s) {
     const int i = i_done + s;
     if (next_row + static_cast<long long>(s - 1) * stride >= rows) break;
-    (void)mbar_wait_bounded(&ring.bars[i % ring.stages], (i / ring.stages) & 1);
+    (void)mbar_wait_bounded(&ring.bars[i % ring.stages], (i / ring.stages) & 1, ring.wait_cycles);
   }
 }
 

@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import packed
 from ..ddp import FlatGradSync
 from .llama import DecoderConfig, DecoderLM
 from .lora import lora_parameters
@@ -42,6 +43,7 @@ class Trainer:
         loss.backward()
         self.sync.sync()
         self.opt.step()
+        packed.fold_status(loss.device)      # OR this step's status words into the device accumulator
         return loss.detach()
 
     def capture(self, ids: torch.Tensor) -> bool:
@@ -63,6 +65,8 @@ class Trainer:
             return False
 
     def step(self, ids: torch.Tensor) -> torch.Tensor:
+        # what the device flagged during earlier steps (pool overflow: warning; expired wait: error); no blocking
+        packed.poll_status()
         if self.graph is not None:
             self.static_ids.copy_(ids, non_blocking=True)
             self.graph.replay()

@@ -138,13 +138,26 @@ def true_divide_outlier_suboutlier_svd_compress(x: torch.Tensor, outlier, scale,
                                   "(compress_function.py:167-168,200); use 1, 2, 4 or 8 bits")
     seq = x.shape[-2]
     lowrank = lowrank_product(L, R, seq, rank, cache)
+    # Outlier-pool capacity.  With frozen statistics (``cache`` is the site's, i.e. from the third call on)
+    # the site counts once how many elements its threshold actually selects and sizes its pool from that:
+    # one host synchronisation per site (the reference synchronises on every call, in to_sparse).
+    density = None
+    if cache is not None:
+        density = cache.get("pool_density")
+        if density is None and not torch.cuda.is_current_stream_capturing():
+            resid = head_to_hidden_shape(x) if x.dim() == 4 else x
+            if lowrank is not None:
+                resid = resid - lowrank
+            density = float((resid.abs() > outlier).float().mean().item())
+            cache["pool_density"] = density
     if sub_outlier_ratio == 0.0:
         use_scale = torch.full((), _NOTHING_QUANTISED, device=x.device, dtype=BF16)
         bits = 8 if sub_outlier_bit == 16 else sub_outlier_bit
         out_scale = torch.tensor(1.0, device=x.device)
     else:
         use_scale, bits, out_scale = scale, sub_outlier_bit, scale
-    res = _pk.compress_r(x, outlier, use_scale, bits, lowrank=lowrank, outlier_ratio=outlier_ratio, norm=norm)
+    res = _pk.compress_r(x, outlier, use_scale, bits, lowrank=lowrank, outlier_ratio=outlier_ratio, norm=norm,
+                         density=density)
     if norm is None:
         p = res
         return p, p.codes.view(p.shape[0], p.shape[1], -1), out_scale

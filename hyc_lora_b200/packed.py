@@ -160,31 +160,160 @@ def _dense_record(x: torch.Tensor, cols: int):
     return d, rows, seq, shape, x
 
 
-def default_pool_entries(rows: int, cols: int, outlier_ratio: float) -> int:
-    """Capacity of the element-outlier pool: four times the calibrated two-sided
-    density (the reference's signed quantile keeps about 2 * ratio of the
-    elements), at least 1/64 of the tensor."""
-    frac = max(8.0 * outlier_ratio, 1.0 / 64.0)
-    return min(int(math.ceil(rows * cols * min(frac, 1.0))) + 1024, 2 ** 32 - 2)
+_pool_growth = 1.0      # doubled by poll_status() each time it sees an overflowed pool
 
 
+def default_pool_entries(rows: int, cols: int, outlier_ratio: float, density: Optional[float] = None) -> int:
+    """Capacity of the element-outlier pool (4 bytes per entry).
+
+    Without a measurement: eight times ``outlier_ratio`` of the tensor -- four times the density the
+    reference's calibration produces (its signed quantile keeps about ``2 * ratio`` of the elements).
+    With ``density``, the fraction of elements above the frozen threshold that the site measured on its
+    first steady-state call: twice that plus one percent.  Either way at least 1/64 of the tensor, and
+    multiplied by the growth factor that :func:`poll_status` raises after an overflow."""
+    frac = 8.0 * outlier_ratio if density is None else 2.0 * density + 0.01
+    frac = min(max(frac, 1.0 / 64.0) * _pool_growth, 1.0)
+    return min(int(math.ceil(rows * cols * frac)) + 1024, 2 ** 32 - 2)
+
+
+# ---------------------------------------------------------------------------
+# Status words.  Every record carries one device word into which kernels OR what only the device can
+# see: an outlier pool (or sparse-probability list) that was too small, a bounded wait that ran out.
+# Nothing on the hot path reads them.  fold_status() ORs every word handed out since the last fold into
+# one accumulator per device (a few tiny kernels; capturable, so a recorded training step folds its own
+# words), and poll_status() brings the accumulator to the host without blocking and reports the value
+# of the previous poll -- one step late, no synchronisation.
+# ---------------------------------------------------------------------------
 _STATUS_CHUNK = 1024
-_status_chunks = {}
+
+
+class _StatusBoard:
+    def __init__(self):
+        self.chunks = {}        # device key -> [chunk, words used]                (outside stream capture)
+        self.capture = {}       # device key -> [chunk, words used]                (inside the current capture)
+        self.dirty = {}         # device key -> tensors holding words handed out since the last fold
+        self.acc = {}           # device key -> int32[1] accumulator
+        self.pending = {}       # device key -> (pinned int32[1], event) of the last poll
+        self.reported = 0       # bits already warned about
+
+    @staticmethod
+    def key(device):
+        device = torch.device(device)
+        return (device.type, device.index if device.index is not None else torch.cuda.current_device())
+
+    def new(self, device) -> torch.Tensor:
+        key = self.key(device)
+        capturing = torch.cuda.is_current_stream_capturing()
+        book = self.capture if capturing else self.chunks
+        if not capturing:
+            self.capture.pop(key, None)      # a chunk made inside a graph's memory pool is never used outside it
+        slot = book.get(key)
+        if slot is None or slot[1] >= _STATUS_CHUNK:
+            slot = [torch.zeros(_STATUS_CHUNK, dtype=torch.int32, device=device), 0]
+            book[key] = slot
+            self.dirty.setdefault(key, []).append(slot[0])
+        word = slot[0][slot[1]:slot[1] + 1]
+        slot[1] += 1
+        return word
+
+    def fold(self, device=None):
+        keys = [self.key(device)] if device is not None else list(self.dirty)
+        for key in keys:
+            tensors = self.dirty.get(key, [])
+            if not tensors:
+                continue
+            if key not in self.acc:
+                if torch.cuda.is_current_stream_capturing():
+                    raise RuntimeError("fold_status(): call it once outside stream capture before recording a graph")
+                self.acc[key] = torch.zeros(1, dtype=torch.int32, device=tensors[0].device)
+            acc = self.acc[key]
+            for t in tensors:
+                acc.bitwise_or_((t & 1).amax() | (t & 2).amax())
+            if torch.cuda.is_current_stream_capturing():
+                self.capture.pop(key, None)              # the next recorded step starts a fresh chunk
+            # a partly used chunk stays under watch: its remaining words are still to be handed out
+            live = self.chunks.get(key)
+            self.dirty[key] = [live[0]] if live is not None and live[1] < _STATUS_CHUNK else []
+
+    def poll(self, wait: bool = False) -> int:
+        global _pool_growth
+        if not torch.cuda.is_current_stream_capturing():
+            self.fold()
+        seen = 0
+        for key, acc in self.acc.items():
+            host, ev = self.pending.get(key, (None, None))
+            if ev is not None:
+                if wait:
+                    ev.synchronize()
+                if not ev.query():
+                    continue                               # the previous copy is still in flight: look again next time
+                seen |= int(host.item())
+            if host is None:
+                host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            with torch.cuda.device(acc.device):
+                host.copy_(acc, non_blocking=True)         # stream-ordered after everything enqueued so far
+                ev = torch.cuda.Event()
+                ev.record()
+            self.pending[key] = (host, ev)
+            if wait:
+                ev.synchronize()
+                seen |= int(host.item())
+        fresh = seen & ~self.reported
+        if fresh & _lib.HYC_STATUS_WAIT_EXPIRED:
+            self.reported |= _lib.HYC_STATUS_WAIT_EXPIRED
+            raise RuntimeError("hyc_lora_b200: a kernel gave up waiting for its own staged copy "
+                               "(HYC_STATUS_WAIT_EXPIRED); results of that call are not valid")
+        if fresh & _lib.HYC_STATUS_POOL_OVERFLOW:
+            self.reported |= _lib.HYC_STATUS_POOL_OVERFLOW
+            _pool_growth *= 2.0
+            import warnings
+            warnings.warn("hyc_lora_b200: an outlier pool or sparse-probability list was too small "
+                          "(HYC_STATUS_POOL_OVERFLOW): some rows were stored without their outliers. Capacities are "
+                          "doubled from now on; a recorded CUDA graph keeps its old capacities until it is recorded again.")
+        return seen
+
+    def reset(self):
+        """Forget everything flagged so far: words handed out earlier are no longer watched."""
+        self.chunks.clear()
+        self.capture.clear()
+        self.dirty.clear()
+        for acc in self.acc.values():
+            acc.zero_()
+        self.pending.clear()
+        self.reported = 0
+
+
+_board = _StatusBoard()
 
 
 def _new_status(device) -> torch.Tensor:
-    """A zeroed int32 status word.  Outside stream capture the words are handed out from a chunk zeroed by one
-    fill, so that a compression call does not cost an extra fill kernel; a word is never handed out twice.
-    During capture every record gets its own zeroed tensor (a chunk made inside one graph's memory pool must not
-    be shared with work outside that graph)."""
-    if torch.cuda.is_current_stream_capturing():
-        return torch.zeros(1, dtype=torch.int32, device=device)
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    chunk, used = _status_chunks.get(key, (None, _STATUS_CHUNK))
-    if used >= _STATUS_CHUNK:
-        chunk, used = torch.zeros(_STATUS_CHUNK, dtype=torch.int32, device=device), 0
-    _status_chunks[key] = (chunk, used + 1)
-    return chunk[used:used + 1]
+    """A zeroed int32 status word, handed out from a chunk zeroed by one fill so that a compression call
+    does not cost a fill kernel of its own; a word is never handed out twice.  Words asked for during
+    stream capture come from a chunk that lives in that capture."""
+    return _board.new(device)
+
+
+def fold_status(device=None) -> None:
+    """OR every status word handed out since the last call into the per-device accumulator.  Cheap and
+    capturable: a training step calls it once, after backward (before recording a graph, call it once
+    outside the capture so that the accumulator exists)."""
+    _board.fold(device)
+
+
+def poll_status(wait: bool = False) -> int:
+    """Bring the accumulated status to the host.  Without ``wait`` nothing blocks: the call starts an
+    asynchronous copy and returns the value the PREVIOUS call fetched (0 the first time).  Raises on an
+    expired wait; on a pool overflow warns once and doubles the default capacities.  Returns the OR of
+    the HYC_STATUS_* bits seen."""
+    return _board.poll(wait)
+
+
+def reset_status() -> None:
+    """Clear the accumulated status and stop watching the words handed out so far (also restores the
+    default pool capacities)."""
+    global _pool_growth
+    _pool_growth = 1.0
+    _board.reset()
 
 
 def _alloc_common(rows, cols, bits, device):
@@ -226,7 +355,7 @@ def scale_kind_of(scale: torch.Tensor) -> str:
 
 def compress_r(x: torch.Tensor, thr: torch.Tensor, scale: torch.Tensor, bits: int,
                lowrank: Optional[torch.Tensor] = None, pool_entries: Optional[int] = None,
-               outlier_ratio: float = 0.01, norm: Optional[dict] = None):
+               outlier_ratio: float = 0.01, norm: Optional[dict] = None, density: Optional[float] = None):
     """Reference-mode compression of ``x`` ([B,S,D] or [B,H,S,hd]).  With
     ``norm`` (keys kind, weight, bias, eps) the norm forward is fused and
     ``(packed, y, rstd, mean)`` is returned, else ``packed``."""
@@ -239,7 +368,7 @@ def compress_r(x: torch.Tensor, thr: torch.Tensor, scale: torch.Tensor, bits: in
     if kind == "per-token" and scale.numel() != seq:
         raise ValueError(f"per-token scale has {scale.numel()} positions, the activation has {seq}")
     if pool_entries is None:
-        pool_entries = default_pool_entries(rows, cols, outlier_ratio)
+        pool_entries = default_pool_entries(rows, cols, outlier_ratio, density)
     p = _new_r(keep, rows, cols, seq, shape, thr, scale, kind, bits, lowrank, pool_entries)
     return _run_fwd(d, keep, p, norm)
 

@@ -126,6 +126,15 @@ uint64_t hyc_launch_count(void);
  * started (or not at all); every other entry point keeps no mutable state. */
 int hyc_set_tuning(int threads, int stages, int ctas_per_sm);
 
+/* Test hook for the give-up path of the bounded waits, PROCESS-GLOBAL like hyc_set_tuning and 0/0 in
+ * normal use.  It applies to the register-resident consumer kernels (hyc_decompress, hyc_act_bwd,
+ * hyc_norm_bwd on 2/4/8-bit records): every staged row announces `tx_pad_bytes` (a multiple of 16,
+ * at most 4096) more bytes than are copied, so its barrier never completes, and the wait gives up
+ * after `wait_cycles` SM clocks instead of about a second (0 = default limit).  The kernel then
+ * raises HYC_STATUS_WAIT_EXPIRED in the record's status word, waits (bounded) for the copies it
+ * started, and returns without faulting; its outputs are unspecified but inside their buffers. */
+int hyc_debug_wait(int64_t wait_cycles, uint32_t tx_pad_bytes);
+
 /* Compress-only (the sites that are not norms: LoRA-A linear input, SiLU/GELU
  * input, gate*up operands, Q/K/V).  Replaces the eager chain of
  * true_divide_outlier_suboutlier_svd_compress, operators/compress_function.py:136-200,

@@ -135,16 +135,25 @@ def test_graph_captured_step_matches_eager_step():
 
 @pytest.mark.parametrize("case", ["decoder", "decoder_bf16", "decoder_int2", "decoder_rank2", "encoder"])
 def test_lora_gradients_match_the_reference_operators(case):
-    """LoRA gradients of small hosts with this package's operators (reference mode) against fixtures made
-    with the reference's own operator classes on CPU (tests/golden/make_e2e_golden.py): the decoder in
-    fp32, in bf16 at 1 024 channels, at INT2 with 2 % outliers and with a rank-2 low-rank part (frozen
-    statistics loaded from the fixture), and the encoder with every eager-attention operator.
-    Bar: cosine >= 0.999 for every adapter matrix."""
+    """LoRA gradients of small hosts with this package's operators (reference mode) against the
+    reference's own operator classes: the decoder in fp32, in bf16 at 1 024 channels, at INT2 with 2 %
+    outliers and with a rank-2 low-rank part (frozen statistics loaded from the fixture), and the encoder
+    with every eager-attention operator.  Bar: cosine >= 0.999 for every adapter matrix.
+
+    Two comparisons.  (1) Against fixtures made on CPU (tests/golden/make_e2e_golden.py), which travel
+    everywhere.  (2) When the reference's sources are on this machine, against the same host with the
+    reference's classes installed and run on this very device, which takes the CPU-vs-GPU difference of
+    the library GEMMs out of the comparison.  That difference matters in bf16 only: there the reference's
+    own operators on the GPU reach just 0.9990 against themselves on CPU (activations that differ in their
+    last bf16 bit flip quantisation codes, and exact autograd on the two devices already differs at
+    0.99995), so the bf16 fixture is held to 0.998 and the bar proper is comparison (2)."""
     import os
     import numpy as np
     from hyc_lora_b200.hosts.replace import replace_module, uniform_config
+    from oracle import ref_loader
     from tests.golden import make_e2e_golden as gold
     c = gold.CASES[case]
+    bf16 = c["cfg"]["dtype"] == torch.bfloat16
     fix = np.load(os.path.join(os.path.dirname(gold.__file__), f"e2e_{case}.npz"))
     model = gold.build_host(device="cuda", case=case)
     cfg = uniform_config(softmax_outlier_ratio=c.get("softmax_ratio", 0.05), **c["site"])
@@ -153,16 +162,28 @@ def test_lora_gradients_match_the_reference_operators(case):
     assert n == (layers * 11 + 1 if c["kind"] == "decoder" else layers * 9 + 1)
     if c["calibrate"]:
         assert gold.load_calibration(model, fix, "cuda") == n
+    from hyc_lora_b200 import packed
+    packed.reset_status()
     args = tuple(a.cuda() for a in gold.inputs(case))
     loss = model(*args)
     loss.backward()
-    assert abs(loss.item() - float(fix["loss"])) < (2e-2 if c["cfg"]["dtype"] == torch.bfloat16 else 1e-3)
+    assert abs(loss.item() - float(fix["loss"])) < (2e-2 if bf16 else 1e-3)
     worst, seen = 1.0, 0
     for name, p in model.named_parameters():
         if "grad/" + name in fix.files:
             worst = min(worst, _cos(p.grad.cpu(), torch.from_numpy(fix["grad/" + name])))
             seen += 1
     assert seen == sum(1 for k in fix.files if k.startswith("grad/"))
+    assert worst >= (0.998 if bf16 else 0.999), worst
+    assert packed.poll_status(wait=True) == 0             # no outlier pool overflowed, no wait gave up
+
+    if ref_loader.load() is None or c["calibrate"]:
+        return      # (the calibrated case would need the reference's randomized SVD to repeat on this device)
+    ref = gold.build_host(device="cuda", case=case)
+    gold._install_reference(ref, case)
+    ref(*args).backward()
+    want = {k: p.grad for k, p in ref.named_parameters() if p.grad is not None}
+    worst = min(_cos(p.grad, want[k]) for k, p in model.named_parameters() if "grad/" + k in fix.files)
     assert worst >= 0.999, worst
 
 

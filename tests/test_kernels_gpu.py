@@ -657,3 +657,61 @@ def test_config1_in_channel_mode_on_its_own_tensor(pk):
     dxn, _, _ = pk.norm_bwd(p, g.to(DEV).reshape(-1, 768), w.to(DEV), rstd, mean, "ln")
     dxn_o, _, _ = oc.norm_backward(xh_o, g, w, mean_o, rstd_o, "ln")
     assert _rel_err(dxn.reshape(x.shape), dxn_o) < 1e-2
+
+
+def test_status_poll_reports_a_pool_overflow_without_blocking(pk):
+    """Nothing on the hot path reads a record's status word; the per-device accumulator does.  A pool that
+    is far too small overflows: the first poll only starts the copy to the host (and reports what the poll
+    before it fetched: nothing), the next one reports the overflow, warns and doubles the capacities."""
+    pk.reset_status()
+    x, _ = synthetic.roundtrip_activation(2, 64, 768, planted=5, gain=20.0, dtype=torch.bfloat16, salt=3)
+    thr, _, _, scale = oc.r_calibrate(x, 0.01, 1.0, 4, "per-channel", 0)
+    before = pk.default_pool_entries(128, 768, 0.01)
+    p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), 4, pool_entries=8)
+    assert pk.poll_status() == 0
+    torch.cuda.synchronize()
+    with pytest.warns(UserWarning, match="POOL_OVERFLOW"):
+        seen = pk.poll_status()
+    assert seen & 1 and p.overflowed()
+    assert pk.default_pool_entries(128, 768, 0.01) > before
+    pk.reset_status()
+    assert pk.default_pool_entries(128, 768, 0.01) == before and pk.poll_status(wait=True) == 0
+
+
+def test_expired_wait_is_reported_and_leaves_the_device_usable(pk):
+    """The give-up path of the bounded waits, made to run without any fault: through the test hook every
+    staged row of the consumer kernels announces 16 bytes more than it copies and waits end after about a
+    millisecond.  All copies land, no barrier ever completes, every CTA gives up: the call returns 0, the
+    record's status word carries HYC_STATUS_WAIT_EXPIRED, nothing is written outside the outputs, the
+    poll raises, and the very next ordinary call is exact."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    rows, d = 64, 1024
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, salt=77)
+    xd = x.to(DEV)
+    ch = pk.select_channels(pk.channel_absmax(xd), oc.n_outlier_count(d, 0.01))
+    pk.reset_status()
+    p = pk.compress_n(xd, ch, 4, 0, 0)
+    want = pk.decompress(p).reshape(rows, d).clone()
+    dy = torch.randn(rows, d, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
+    arena = _Arena(rows * d * 8 + (1 << 18))
+    xh, dx = arena.take((rows, d), torch.bfloat16), arena.take((rows, d), torch.bfloat16)
+    assert _lib.lib.hyc_debug_wait(2_000_000, 16) == 0
+    try:
+        rec, out = p.record(), _dense(xh, d)
+        rc1 = _lib.lib.hyc_decompress(C.byref(rec), C.byref(out), pk._stream())
+        rc2 = _lib.lib.hyc_act_bwd(_lib.HYC_ACT_SILU, C.byref(rec), None, C.c_void_p(dy.data_ptr()), _lib.HYC_BF16,
+                                   C.c_void_p(dx.data_ptr()), None, pk._stream())
+        torch.cuda.synchronize()
+    finally:
+        assert _lib.lib.hyc_debug_wait(0, 0) == 0
+    assert rc1 == 0 and rc2 == 0
+    assert p.wait_expired()
+    arena.check()
+    with pytest.raises(RuntimeError, match="WAIT_EXPIRED"):
+        pk.poll_status(wait=True)
+    p.status.zero_()
+    pk.reset_status()
+    assert torch.equal(pk.decompress(p).reshape(rows, d), want)
+    assert not p.wait_expired() and pk.poll_status(wait=True) == 0
+    assert _lib.lib.hyc_debug_wait(-1, 0) == -2 and _lib.lib.hyc_debug_wait(0, 8) == -2

@@ -32,7 +32,7 @@ def _reference_forward(kind, x, w, b, eps, bits, method, ratio):
     if ref is None:
         pytest.skip("reference operators (or Triton) not available on this machine")
     func = {"rms": lambda: ref.efficient_rmsnorm.EfficientMemoryRMSNormFunc,
-            "rms_gemma": lambda: ref.efficient_rmsnorm_gemma.EfficientMemoryRMSNormFunc,
+            "rms_gemma": lambda: ref.efficient_rmsnorm_gemma.EfficientMemoryRMSNormGemmaFunc,
             "ln": lambda: ref.efficient_layernorm.EfficientMemoryLayerNormFunc}[kind]()
     ctx = _Ctx()
     try:
