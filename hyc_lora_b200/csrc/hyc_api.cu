@@ -1,6 +1,9 @@
 // Library-wide state, error strings, tuning knobs and the forward entry points
 // (argument checks + launch planning; the kernels are instantiated elsewhere).
+#include <stdlib.h>
+
 #include "hyc_fwd_r_fast.cuh"
+#include "hyc_fwd_warp.cuh"
 
 namespace hyc {
 
@@ -46,6 +49,29 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
       if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(pool_used)");
       return x->dtype == HYC_BF16 ? launch_fwd_r_fast_bf16(ra, rf, norm != nullptr, stream)
                                   : launch_fwd_r_fast_f32(ra, rf, norm != nullptr, stream);
+    }
+  }
+  if (out->mode == HYC_MODE_N) {
+    // rows of up to 4096 bf16 channels: one warp per row, no CTA barrier in the row loop
+    static const bool warp_off = getenv("HYC_FWD_WARP") && getenv("HYC_FWD_WARP")[0] == '0';
+    const WarpPlan wp = warp_off ? WarpPlan{} : plan_warp_fwd(out, x, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER);
+    if (wp.ok) {
+      WarpFwdArgs wa;
+      memset(&wa, 0, sizeof(wa));
+      wa.p = to_dev(out);
+      wa.x = static_cast<const __nv_bfloat16*>(x->base);
+      wa.row_stride = x->row_stride;
+      if (norm) {
+        wa.kind = norm->kind; wa.eps = norm->eps; wa.weight = norm->weight; wa.bias = norm->bias;
+        wa.param_bf16 = norm->param_dtype == HYC_BF16;
+        wa.y = static_cast<__nv_bfloat16*>(norm->y); wa.rstd = norm->rstd; wa.mean = norm->mean;
+      }
+      wa.off_chan = wp.off_chan; wa.off_wsm = wp.off_wsm; wa.off_bsm = wp.off_bsm;
+      wa.off_slots = wp.off_slots; wa.slot_bytes = wp.slot_bytes;
+      wa.wait_cycles = g_debug_wait_cycles > 0 ? g_debug_wait_cycles : kWaitCycles;
+      return out->bits == 2 ? launch_fwd_warp_b2(wa, wp, norm != nullptr, stream)
+           : out->bits == 4 ? launch_fwd_warp_b4(wa, wp, norm != nullptr, stream)
+                            : launch_fwd_warp_b8(wa, wp, norm != nullptr, stream);
     }
   }
   FastPlan fast = plan_fast(out, es);

@@ -1,0 +1,8 @@
+// Warp-per-row forward kernel, 4-bit codes (one translation unit per bit width so they compile in parallel).
+#include "hyc_fwd_warp.cuh"
+
+namespace hyc {
+int launch_fwd_warp_b4(const WarpFwdArgs& a, const WarpPlan& w, bool norm, cudaStream_t stream) {
+  return launch_fwd_warp_bits<4>(a, w, norm, stream);
+}
+}  // namespace hyc
