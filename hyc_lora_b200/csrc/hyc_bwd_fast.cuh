@@ -44,8 +44,10 @@ __device__ __forceinline__ void dequant8(const uint2& cb, int s, float sc, float
   }
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
-    f[e] = (__uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7650 + e)) - bias) * sc;
-    f[e + 4] = (__uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7650 + e)) - bias) * sc;
+    // an explicit rounded multiply: the product must not be fused into a later addition (the rotation's
+    // butterflies), or the sums would round differently from a sequential evaluation
+    f[e] = __fmul_rn(__uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7650 + e)) - bias, sc);
+    f[e + 4] = __fmul_rn(__uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7650 + e)) - bias, sc);
   }
 }
 

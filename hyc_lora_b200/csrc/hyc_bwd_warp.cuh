@@ -1,0 +1,358 @@
+// Warp-per-row consumers of a channel-mode record (rows of up to 4096 channels): decompress, and
+// decompress + norm backward with a frozen norm weight and a bf16 gradient.
+//
+// Same walk as the warp-per-row forward kernel: a warp owns its rows; the packed codes (and the gradient
+// row) of a row land in the warp's own shared-memory slot by bulk asynchronous copies on the warp's own
+// mbarrier; reductions are warp shuffles, and there is no CTA barrier in the row loop.  The decompress
+// moves the codes into registers and hands the slot straight back to the copy engine; the norm backward
+// makes its two passes (the two row sums, then the result) over the slot itself and rebuilds the values
+// from the codes in both.  Outlier channels are streamed as the zero their code encodes and put right
+// afterwards by the lanes that look after them (after the inverse rotation they are cleared first, the
+// correction assumes a zero).  Arithmetic per element is that of the CTA-per-row kernels in
+// hyc_bwd_fast.cuh.  (The activation backward stays on those: with its exponentials it is bound by
+// instruction issue, not by the row barrier, and measured faster there.)
+#pragma once
+#include <stdlib.h>
+
+#include "hyc_bwd_fast.cuh"
+#include "hyc_fwd_warp.cuh"
+
+namespace hyc {
+
+struct WarpBwdArgs {
+  PackedDev p, p2;
+  const __nv_bfloat16* g;     // upstream gradient rows [rows, D] (activation / norm backward)
+  __nv_bfloat16* out1;        // decompress: reconstruction; activation: dx1; norm: dx
+  __nv_bfloat16* out2;        // product: dx2
+  long long out_stride;       // elements between rows of out1 (decompress follows the caller's layout)
+  int kind, ref_compat_c2, param_bf16;
+  const void* weight;
+  const float* rstd;
+  const float* mean;
+  uint32_t off_chan, off_chan2, off_wsm, off_slots, slot_bytes, off_c2, off_g;
+  uint32_t tx_pad;
+  long long wait_cycles;
+};
+
+// what every consumer sets up once per CTA and per lane
+template <int BITS, int NG>
+struct WarpRowCtx {
+  static constexpr int NSEG = 8 / BITS;
+  static constexpr int UPL = NG / NSEG;
+  int D, segw, U, k, lane, warp, W;
+  unsigned char* slot;
+  uint64_t* bar;
+  int* chan;
+  long long rows, stride, row;
+  uint32_t ph;
+  int oc[kWarpOutPerLane];
+
+  __device__ __forceinline__ void init(const WarpBwdArgs& a, unsigned char* smem) {
+    D = a.p.cols; segw = D / NSEG; U = segw >> 3; k = a.p.n_channels;
+    lane = threadIdx.x & 31; warp = threadIdx.x >> 5; W = blockDim.x >> 5;
+    slot = smem + a.off_slots + static_cast<size_t>(warp) * a.slot_bytes;
+    bar = reinterpret_cast<uint64_t*>(smem) + warp;
+    chan = reinterpret_cast<int*>(smem + a.off_chan);
+    rows = a.p.rows; stride = static_cast<long long>(gridDim.x) * W;
+    row = static_cast<long long>(blockIdx.x) * W + warp;
+    ph = 0;
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < W; ++i) mbar_init(reinterpret_cast<uint64_t*>(smem) + i, 1);
+      fence_barrier_init();
+    }
+    __syncthreads();
+  }
+  // column of register group r of this lane
+  __device__ __forceinline__ int col(int r) const { return (r % NSEG) * segw + ((lane + 32 * (r / NSEG)) << 3); }
+  __device__ __forceinline__ bool live(int r) const { return (lane + 32 * (r / NSEG)) < U; }
+  __device__ __forceinline__ void lanes_channels() {
+#pragma unroll
+    for (int q = 0; q < kWarpOutPerLane; ++q) oc[q] = (lane + 32 * q) < k ? chan[lane + 32 * q] : -1;
+  }
+};
+
+// one row's bytes into the warp's slot: codes (and the second operand's), then the gradient row
+__device__ __forceinline__ void warp_issue_row(const WarpBwdArgs& a, unsigned char* slot, uint64_t* bar, long long row,
+                                               uint32_t cb, bool second, bool grad, int D) {
+  const uint32_t total = cb + (second ? cb : 0u) + (grad ? static_cast<uint32_t>(D) * 2u : 0u);
+  mbar_expect_tx(bar, total + a.tx_pad);
+  bulk_g2s(slot, a.p.codes + row * cb, cb, bar);
+  if (second) bulk_g2s(slot + a.off_c2, a.p2.codes + row * cb, cb, bar);
+  if (grad) bulk_g2s(slot + a.off_g, a.g + row * D, static_cast<uint32_t>(D) * 2u, bar);
+}
+
+// the values of register group (iu, s): (code - offset) * scale, rotated back when the record is rotated,
+// rounded to bf16 when ROUND (what a reconstruction holds)
+template <int BITS, bool ROT, bool ROUND>
+__device__ __forceinline__ void warp_rebuild8(const uint2& cw, int s, float sc, int nrot, int lane, float (&f)[8]) {
+  dequant8<BITS>(cw, s, sc, f);
+  if (ROT) rotate_group(f, nrot, lane);
+  if (ROUND) round_bf16x8(f);
+}
+
+// ------------------------------------------------------------------ decompress
+
+template <int BITS, int NG, bool ROT>
+__global__ void __launch_bounds__(kWarpKernelThreads, 2) decompress_n_warp_kernel(const __grid_constant__ WarpBwdArgs a) {
+  using Ctx = WarpRowCtx<BITS, NG>;
+  constexpr int NSEG = Ctx::NSEG, UPL = Ctx::UPL;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const PackedDev& p = a.p;
+  Ctx c;
+  c.init(a, smem);
+  const uint32_t cb = static_cast<uint32_t>(c.D) * BITS / 8;
+  if (c.lane == 0 && c.row < c.rows) warp_issue_row(a, c.slot, c.bar, c.row, cb, false, false, c.D);
+  for (int j = threadIdx.x; j < c.k; j += blockDim.x) c.chan[j] = max(0, min(c.D - 1, p.channels[j]));
+  __syncthreads();
+  c.lanes_channels();
+  const int G = p.group ? (c.D >> 7) : 1;
+  for (; c.row < c.rows; c.row += c.stride, c.ph ^= 1u) {
+    const long long row = c.row;
+    // the stored originals of the outlier channels, fetched before the wait
+    __nv_bfloat16 ov[kWarpOutPerLane];
+#pragma unroll
+    for (int q = 0; q < kWarpOutPerLane; ++q)
+      ov[q] = c.oc[q] >= 0 ? p.out_value[row * c.k + c.lane + 32 * q] : __float2bfloat16_rn(0.f);
+    const float* sc_row = p.scales + row * G;
+    const float sc_tok = p.group ? 0.f : __ldg(sc_row);
+    if (!mbar_wait_bounded(c.bar, c.ph, a.wait_cycles)) {
+      if (c.lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
+      return;
+    }
+    uint2 cw[UPL];
+#pragma unroll
+    for (int iu = 0; iu < UPL; ++iu)
+      cw[iu] = (c.lane + 32 * iu) < c.U ? *reinterpret_cast<const uint2*>(c.slot + ((c.lane + 32 * iu) << 3)) : make_uint2(0u, 0u);
+    __syncwarp();
+    const long long next = row + c.stride;
+    if (c.lane == 0 && next < c.rows) {
+      fence_proxy_async();
+      warp_issue_row(a, c.slot, c.bar, next, cb, false, false, c.D);
+    }
+    __nv_bfloat16* orow = a.out1 + row * a.out_stride;
+#pragma unroll
+    for (int r = 0; r < NG; ++r) {
+      const int col = c.col(r);
+      float f[8];
+      const float sc = p.group ? __ldg(sc_row + (min(col, c.D - 8) >> 7)) : sc_tok;
+      warp_rebuild8<BITS, ROT, false>(cw[r / NSEG], r % NSEG, sc, p.rotate, c.lane, f);
+      if (c.live(r)) store8<__nv_bfloat16>(orow, col, f);
+    }
+    __syncwarp();   // the vector stores come before the originals of the outlier channels
+#pragma unroll
+    for (int q = 0; q < kWarpOutPerLane; ++q)
+      if (c.oc[q] >= 0) orow[c.oc[q]] = ov[q];
+  }
+}
+
+// ------------------------------------------------------------------ norm backward (frozen weight)
+
+constexpr int kNormBwdWarpThreads = 640;    // 20 warps, one CTA per SM: the slots of 20 rows fill the shared memory
+
+// Two passes over the row (the two row sums, then the result) read the codes and the gradient row from
+// the warp's slot both times, in short rolled loops, instead of holding them in registers: few registers,
+// twenty warps per SM to cover the arithmetic latencies, and the slot goes back to the copy engine when
+// the row is done (the other warps keep the memory system busy meanwhile).
+template <int BITS, bool ROT, bool LN>
+__global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel(const __grid_constant__ WarpBwdArgs a) {
+  constexpr int NSEG = 8 / BITS;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const PackedDev& p = a.p;
+  WarpRowCtx<BITS, NSEG> c;
+  c.init(a, smem);
+  const int D = c.D;
+  const int upl = (c.U + 31) >> 5;
+  const uint32_t cb = static_cast<uint32_t>(D) * BITS / 8;
+  if (c.lane == 0 && c.row < c.rows) warp_issue_row(a, c.slot, c.bar, c.row, cb, false, true, D);
+  float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
+  uint32_t* omask = reinterpret_cast<uint32_t*>(smem + a.off_chan2);   // ROT: one bit per channel, 1 = outlier channel
+  const float plus = a.kind == HYC_NORM_RMS_GEMMA ? 1.f : 0.f;
+  for (int j = threadIdx.x; j < c.k; j += blockDim.x) c.chan[j] = max(0, min(D - 1, p.channels[j]));
+  if (ROT)
+    for (int i = threadIdx.x; i < (D >> 5); i += blockDim.x) omask[i] = 0u;
+  for (int ch = threadIdx.x; ch < D; ch += blockDim.x)
+    wsm[split_index(ch, D)] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[ch])
+                                            : static_cast<const float*>(a.weight)[ch]) + plus;
+  __syncthreads();
+  if (ROT) {
+    for (int j = threadIdx.x; j < c.k; j += blockDim.x) atomicOr(&omask[c.chan[j] >> 5], 1u << (c.chan[j] & 31));
+    __syncthreads();
+  }
+  c.lanes_channels();
+  const int G = p.group ? (D >> 7) : 1;
+  const float inv_d = 1.0f / static_cast<float>(D);
+  const __nv_bfloat16* gs = reinterpret_cast<const __nv_bfloat16*>(c.slot + a.off_g);
+  for (; c.row < c.rows; c.row += c.stride, c.ph ^= 1u) {
+    const long long row = c.row;
+    const float rstd = __ldg(a.rstd + row);
+    const float mean = LN ? __ldg(a.mean + row) : 0.f;
+    float ov[kWarpOutPerLane];
+#pragma unroll
+    for (int q = 0; q < kWarpOutPerLane; ++q)
+      ov[q] = c.oc[q] >= 0 ? __bfloat162float(p.out_value[row * c.k + c.lane + 32 * q]) : 0.f;
+    const float* sc_row = p.scales + row * G;
+    const float sc_tok = p.group ? 0.f : __ldg(sc_row);
+    if (!mbar_wait_bounded(c.bar, c.ph, a.wait_cycles)) {
+      if (c.lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
+      return;
+    }
+    float gq[kWarpOutPerLane];
+#pragma unroll
+    for (int q = 0; q < kWarpOutPerLane; ++q) gq[q] = c.oc[q] >= 0 ? __bfloat162float(gs[c.oc[q]]) : 0.f;
+    // ---- pass 1: the two row sums
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll 2
+    for (int iu = 0; iu < upl; ++iu) {
+      const int u = c.lane + 32 * iu;
+      const bool live = u < c.U;
+      const uint2 cw = live ? *reinterpret_cast<const uint2*>(c.slot + (u << 3)) : make_uint2(0u, 0u);
+#pragma unroll
+      for (int s = 0; s < NSEG; ++s) {
+        const int col = s * c.segw + (u << 3);
+        float f[8];
+        warp_rebuild8<BITS, ROT, true>(cw, s, p.group ? __ldg(sc_row + (min(col, D - 8) >> 7)) : sc_tok, p.rotate, c.lane, f);
+        if (live) {
+          if (ROT) {
+            const uint32_t m = mask8(omask, col);
+            if (m) zero_masked(f, m);
+          }
+          float gv[8], wv[8];
+          load8<__nv_bfloat16>(gs, col, gv);
+          load8_split(wsm, D, col, wv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float xn = (f[e] - mean) * rstd;
+            const float wd = wv[e] * gv[e];
+            c1 = fmaf(xn, wd, c1);
+            c2 += wd;
+          }
+        }
+      }
+    }
+    // outlier channels: the true x-hat differs from the streamed one by o * rstd
+#pragma unroll
+    for (int q = 0; q < kWarpOutPerLane; ++q)
+      if (c.oc[q] >= 0) c1 = fmaf(ov[q] * rstd, wsm[split_index(c.oc[q], D)] * gq[q], c1);
+    c1 = warp_sum(c1) * inv_d;
+    c2 = (LN || a.ref_compat_c2) ? warp_sum(c2) * inv_d : 0.f;
+    // ---- pass 2: the result
+    __nv_bfloat16* dxrow = a.out1 + row * D;
+#pragma unroll 2
+    for (int iu = 0; iu < upl; ++iu) {
+      const int u = c.lane + 32 * iu;
+      const bool live = u < c.U;
+      const uint2 cw = live ? *reinterpret_cast<const uint2*>(c.slot + (u << 3)) : make_uint2(0u, 0u);
+#pragma unroll
+      for (int s = 0; s < NSEG; ++s) {
+        const int col = s * c.segw + (u << 3);
+        float f[8];
+        warp_rebuild8<BITS, ROT, true>(cw, s, p.group ? __ldg(sc_row + (min(col, D - 8) >> 7)) : sc_tok, p.rotate, c.lane, f);
+        if (live) {
+          if (ROT) {
+            const uint32_t m = mask8(omask, col);
+            if (m) zero_masked(f, m);
+          }
+          float gv[8], wv[8], d[8];
+          load8<__nv_bfloat16>(gs, col, gv);
+          load8_split(wsm, D, col, wv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) d[e] = (wv[e] * gv[e] - ((f[e] - mean) * rstd * c1 + c2)) * rstd;
+          store8<__nv_bfloat16>(dxrow, col, d);
+        }
+      }
+    }
+    __syncwarp();   // every lane is done with the slot; the vector stores come before the outlier channels' results
+    const long long next = row + c.stride;
+    if (c.lane == 0 && next < c.rows) {
+      fence_proxy_async();
+      warp_issue_row(a, c.slot, c.bar, next, cb, false, true, D);
+    }
+#pragma unroll
+    for (int q = 0; q < kWarpOutPerLane; ++q) {
+      if (c.oc[q] >= 0) {
+        const float xh = (ov[q] - mean) * rstd;
+        dxrow[c.oc[q]] = __float2bfloat16_rn((wsm[split_index(c.oc[q], D)] * gq[q] - (xh * c1 + c2)) * rstd);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host: eligibility and launch
+
+struct WarpBwdPlan {
+  bool ok;
+  int ng, grid, threads;
+  uint32_t off_chan, off_chan2, off_wsm, off_slots, slot_bytes, off_c2, off_g, total;
+};
+
+// channel-mode record(s) of up to 16 register groups per lane and 128 outlier channels; a rotation block of
+// at most 256 channels dividing a segment of whole 256-channel windows
+// threads / ctas: CTA size and CTAs per SM of the kernel to be launched
+inline WarpBwdPlan plan_warp_bwd(const hyc_packed* q, const hyc_packed* q2, bool grad, bool want_w,
+                                 int threads = kWarpKernelThreads, int ctas = 2) {
+  WarpBwdPlan w;
+  memset(&w, 0, sizeof(w));
+  static const bool off_env = getenv("HYC_BWD_WARP") && getenv("HYC_BWD_WARP")[0] == '0';
+  if (off_env || q->mode != HYC_MODE_N || (q2 && q2->mode != HYC_MODE_N)) return w;
+  if (q->bits != 2 && q->bits != 4 && q->bits != 8) return w;
+  if (q->n_channels > 32 * kWarpOutPerLane || (q2 && q2->n_channels > 32 * kWarpOutPerLane)) return w;
+  if (g_tune_threads || g_tune_stages || g_tune_ctas) return w;
+  const int D = q->cols, nseg = 8 / q->bits;
+  if (q->rotate && (q->rotate > 256 || (D / nseg) % 256 != 0)) return w;
+  if (q->group && (D / nseg) % 128 != 0) return w;
+  const int U = D / nseg / 8;
+  const int upl = (U + 31) / 32;
+  int ng = nseg;
+  while (ng < upl * nseg) ng *= 2;
+  if (ng > 16) return w;
+  if (ng < 2) ng = 2;
+  w.ng = ng;
+  uint32_t off = 64 * 8;
+  auto take = [&](uint32_t bytes) { uint32_t o = off; off = align_up(off + bytes, 16); return o; };
+  w.off_chan = take((q->n_channels > 0 ? q->n_channels : 1) * 4);
+  // second channel list (product), or the outlier-channel bitmap of the rotating norm backward
+  w.off_chan2 = take(want_w ? static_cast<uint32_t>(D) / 8u : (q2 && q2->n_channels > 0 ? q2->n_channels : 1) * 4);
+  if (want_w) w.off_wsm = take(D * 4);
+  off = align_up(off, 128);
+  w.off_slots = off;
+  const uint32_t cb = align_up(static_cast<uint32_t>(D) * q->bits / 8, 128);
+  w.off_c2 = cb;
+  w.off_g = q2 ? 2 * cb : cb;
+  w.slot_bytes = w.off_g + (grad ? align_up(static_cast<uint32_t>(D) * 2u, 128) : 0u);
+  const int warps = threads / 32;
+  w.threads = threads;
+  w.total = off + w.slot_bytes * warps;
+  if (w.total > (ctas == 1 ? kSmemPerCtaMax - 1024 : kSmemBudget / ctas)) return w;
+  long long grid = static_cast<long long>(sm_count()) * ctas;
+  const long long need = (q->rows + warps - 1) / warps;
+  if (grid > need) grid = need;
+  w.grid = static_cast<int>(grid);
+  w.ok = true;
+  return w;
+}
+
+inline void fill_warp_bwd(WarpBwdArgs* a, const WarpBwdPlan& w, const hyc_packed* q, const hyc_packed* q2) {
+  memset(a, 0, sizeof(*a));
+  a->p = to_dev(q);
+  if (q2) a->p2 = to_dev(q2);
+  a->off_chan = w.off_chan; a->off_chan2 = w.off_chan2; a->off_wsm = w.off_wsm; a->off_slots = w.off_slots;
+  a->slot_bytes = w.slot_bytes; a->off_c2 = w.off_c2; a->off_g = w.off_g;
+  a->tx_pad = g_debug_tx_pad;
+  a->wait_cycles = g_debug_wait_cycles > 0 ? g_debug_wait_cycles : kWaitCycles;
+}
+
+// BITS x NG dispatch shared by the three launchers; LAUNCH(B, NG) launches one instantiation
+#define HYC_WARP_BWD_DISPATCH(BITS_V, NG_V, LAUNCH)                         \
+  switch (BITS_V) {                                                         \
+    case 2:                                                                 \
+      switch (NG_V) { case 4: LAUNCH(2, 4) break; case 8: LAUNCH(2, 8) break; default: LAUNCH(2, 16) break; } break; \
+    case 4:                                                                 \
+      switch (NG_V) { case 2: LAUNCH(4, 2) break; case 4: LAUNCH(4, 4) break; case 8: LAUNCH(4, 8) break; default: LAUNCH(4, 16) break; } break; \
+    default:                                                                \
+      switch (NG_V) { case 2: LAUNCH(8, 2) break; case 4: LAUNCH(8, 4) break; case 8: LAUNCH(8, 8) break; default: LAUNCH(8, 16) break; } break; \
+  }
+
+int launch_decompress_warp(const WarpBwdArgs& a, const WarpBwdPlan& w, cudaStream_t stream);
+int launch_norm_bwd_warp(const WarpBwdArgs& a, const WarpBwdPlan& w, cudaStream_t stream);
+
+}  // namespace hyc

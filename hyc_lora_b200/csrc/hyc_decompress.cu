@@ -1,5 +1,5 @@
 // Packed activation -> bf16 rows.
-#include "hyc_bwd_fast.cuh"
+#include "hyc_bwd_warp.cuh"
 
 namespace hyc {
 
@@ -75,6 +75,17 @@ int hyc_decompress(const hyc_packed* in, const hyc_dense* o, void* stream_) {
   if (rc) return rc;
   if (o->dtype != HYC_BF16) return HYC_ERR_DTYPE;
   if (in->rows == 0) return HYC_OK;
+  if (o->chunks == 1) {
+    // plain output rows of up to 4096 channels: one warp per row
+    const WarpBwdPlan wp = plan_warp_bwd(in, nullptr, false, false);
+    if (wp.ok) {
+      WarpBwdArgs wa;
+      fill_warp_bwd(&wa, wp, in, nullptr);
+      wa.out1 = static_cast<__nv_bfloat16*>(o->base);
+      wa.out_stride = o->row_stride;
+      return launch_decompress_warp(wa, wp, stream);
+    }
+  }
   {
     // register-resident kernel for the channel-outlier mode
     const BwdPlan bp = plan_bwd_fast(in, nullptr, 4, false, 0, 512, 0, static_cast<uint32_t>(in->cols) * in->bits / 8, 0, 2);

@@ -65,6 +65,7 @@ __device__ __forceinline__ __nv_bfloat162 absmax_acc(__nv_bfloat162 m, const uin
 __device__ __forceinline__ void forget_unpacked(uint4& w) {
   asm volatile("" : "+r"(w.x), "+r"(w.y), "+r"(w.z), "+r"(w.w));
 }
+__device__ __forceinline__ void forget_unpacked2(uint2& w) { asm volatile("" : "+r"(w.x), "+r"(w.y)); }
 __device__ __forceinline__ float pair_max(__nv_bfloat162 m) {
   return fmaxf(__bfloat162float(__low2bfloat16(m)), __bfloat162float(__high2bfloat16(m)));
 }

@@ -1,5 +1,5 @@
 // Decompress + RMSNorm / LayerNorm backward, with the optional weight / bias gradient.
-#include "hyc_bwd_fast.cuh"
+#include "hyc_bwd_warp.cuh"
 
 namespace hyc {
 
@@ -168,6 +168,21 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
     return HYC_OK;
   }
   const int D = saved->cols;
+  if (g->dy_dtype == HYC_BF16 && !g->dweight && !saved->rotate) {
+    // frozen norm weight (the adapter case), bf16 gradient, no rotation: one warp per row (a rotated record
+    // would be rotated back in both of that kernel's passes; the shuffle pipe is its bound, so it stays on
+    // the kernel below, which rotates once and keeps the row in registers)
+    const WarpBwdPlan wp = plan_warp_bwd(saved, nullptr, true, true, kNormBwdWarpThreads, 1);
+    if (wp.ok) {
+      WarpBwdArgs wa;
+      fill_warp_bwd(&wa, wp, saved, nullptr);
+      wa.g = static_cast<const __nv_bfloat16*>(g->dy);
+      wa.out1 = static_cast<__nv_bfloat16*>(g->dx);
+      wa.kind = g->kind; wa.ref_compat_c2 = g->ref_compat_c2; wa.param_bf16 = g->param_dtype == HYC_BF16;
+      wa.weight = g->weight; wa.rstd = g->rstd; wa.mean = g->mean;
+      return launch_norm_bwd_warp(wa, wp, stream);
+    }
+  }
   {
     const BwdPlan bp = plan_bwd_fast(saved, nullptr, 4, true, g->dweight ? (g->dbias ? 2 : 1) : 0, 256, kPartialRowsMax,
                                      align_up(static_cast<uint32_t>(D) * saved->bits / 8, 128) +

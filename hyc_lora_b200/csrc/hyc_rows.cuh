@@ -111,7 +111,7 @@ __device__ __forceinline__ void rotate_group(float (&f)[8], int n, int lane) {
   }
   const float rs = rotate_norm(n);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) f[e] *= rs;
+  for (int e = 0; e < 8; ++e) f[e] = __fmul_rn(f[e], rs);   // exact (power of two) and never fused into what follows
 }
 
 // Normalised Walsh-Hadamard transform of every aligned block of n channels of
