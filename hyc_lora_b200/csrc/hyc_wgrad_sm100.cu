@@ -20,10 +20,20 @@
 // grad^T * out_value, come from extra CTAs of the same launch whose A operand is the stored
 // bf16 outlier values (128 outlier channels per CTA) instead of converted codes.
 //
-// Channel-outlier mode only.  Outlier channels carry the zero code, so their columns come out
-// as zero here; the caller adds G^T * out_value there.  With rotation the kernel contracts the
+// Channel-outlier mode: outlier channels carry the zero code, so their columns come out as zero
+// in the code tiles and are filled from the side CTAs.  With rotation the kernel contracts the
 // un-rotated codes and the rotation is applied to the `rank` output rows afterwards
 // (X_hat = Q H  =>  G^T X_hat = (G^T Q) H).
+//
+// Reference mode (static scale, element outliers; 2/4/8-bit codes).  The same tensor-core kernel
+// contracts the integer codes: a per-token or per-tensor scale is first written out as one fp32
+// scale per row (r_row_scale_kernel) and folded into the gradient rows exactly like the dynamic
+// per-token scale of the channel mode; a per-channel scale multiplies the columns of the summed
+// result in wgrad_finish_kernel.  The element outliers (their code is the zero code) are a sparse
+// side term, out[n, col] += G[t, n] * value over the pool entries of every row:
+// wgrad_pool_kernel accumulates it in shared memory, one CTA per (token slice, group of ranks),
+// and adds it into that slice's partial slab before the finish kernel runs.  A low-rank part is
+// left to the caller: it adds (sum over the batch of G)^T * lowrank, one small dense product.
 #include <mutex>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -412,7 +422,7 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
 // of the side partials, and writes the row.
 __global__ void wgrad_finish_kernel(const float* __restrict__ partials, int splits, const float* __restrict__ side,
                                     int slices, const int* __restrict__ channels, int k, int rank, int D, int rotate,
-                                    float* __restrict__ out) {
+                                    const __nv_bfloat16* __restrict__ colscale, float* __restrict__ out) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* rowbuf = reinterpret_cast<float*>(smem_raw);
   const int n = blockIdx.x;
@@ -424,6 +434,12 @@ __global__ void wgrad_finish_kernel(const float* __restrict__ partials, int spli
     for (int q = 0; q < splits; ++q) {
       const float4 v = __ldg(reinterpret_cast<const float4*>(src + q * slab + c));
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (colscale) {   // reference mode, per-channel scale: the codes were contracted as integers
+      acc.x *= __bfloat162float(colscale[d0 + c]);
+      acc.y *= __bfloat162float(colscale[d0 + c + 1]);
+      acc.z *= __bfloat162float(colscale[d0 + c + 2]);
+      acc.w *= __bfloat162float(colscale[d0 + c + 3]);
     }
     *reinterpret_cast<float4*>(rowbuf + c) = acc;
   }
@@ -443,6 +459,57 @@ __global__ void wgrad_finish_kernel(const float* __restrict__ partials, int spli
     *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(rowbuf + c);
 }
 
+// Reference mode: the scale of every row as fp32 (per-token scale: by sequence position; per-tensor: the one
+// scale; per-channel: 1, the columns are scaled at the end).
+__global__ void r_row_scale_kernel(const __nv_bfloat16* __restrict__ scale, int kind, int seq, long long rows,
+                                   float* __restrict__ row_scale) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= rows) return;
+  row_scale[t] = kind == kScaleToken ? __bfloat162float(scale[t % seq])
+                 : kind == kScaleTensor ? __bfloat162float(scale[0]) : 1.f;
+}
+
+// Reference mode: element outliers as a sparse side term.  CTA (x = group of `rpw` ranks, y = token slice)
+// walks the rows of its slice, one warp per row: lane = (entry e of 32/rpw taken at once, rank r of the
+// group); every entry (column, value) of the row adds G[t, n0 + r] * value (divided by the column's scale
+// when the result will be multiplied by it) to acc[column][r] in shared memory.  At the end the CTA adds its
+// accumulator into its own part of the slice's partial slab (one owner per part: no atomics in global
+// memory, the result stays reproducible up to the order of the shared-memory additions).
+__global__ void __launch_bounds__(512) wgrad_pool_kernel(const uint32_t* __restrict__ pool, const uint2* __restrict__ row_meta,
+                                                         const __nv_bfloat16* __restrict__ grad, int rank, int rpw, int D,
+                                                         long long rows, long long tokens_per_split,
+                                                         const __nv_bfloat16* __restrict__ colscale,
+                                                         float* __restrict__ partials) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* acc = reinterpret_cast<float*>(smem_raw);          // [D][rpw]
+  const int n0 = blockIdx.x * rpw;
+  const long long t0 = static_cast<long long>(blockIdx.y) * tokens_per_split;
+  const long long t1 = min(rows, t0 + tokens_per_split);
+  for (int i = threadIdx.x; i < D * rpw; i += blockDim.x) acc[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int per = 32 / rpw;                                  // entries taken at once
+  const int e = lane / rpw, r = lane % rpw;
+  for (long long t = t0 + warp; t < t1; t += nwarps) {
+    const uint2 meta = __ldg(row_meta + t);
+    if (meta.y == 0) continue;
+    const float g = (n0 + r) < rank ? __bfloat162float(grad[t * rank + n0 + r]) : 0.f;
+    for (uint32_t i = e; i < meta.y; i += per) {
+      const uint32_t ent = __ldg(pool + meta.x + i);
+      const int col = static_cast<int>(ent & 0xffffu);
+      float v = bf16_bits_to_float(ent >> 16);
+      if (colscale) v = __fdividef(v, __bfloat162float(colscale[col]));
+      atomicAdd(&acc[col * rpw + r], g * v);
+    }
+  }
+  __syncthreads();
+  float* slab = partials + static_cast<long long>(blockIdx.y) * rank * D;
+  for (int i = threadIdx.x; i < D * rpw; i += blockDim.x) {
+    const int rr = i / D, d = i - rr * D;
+    if (n0 + rr < rank) slab[static_cast<long long>(n0 + rr) * D + d] += acc[d * rpw + rr];
+  }
+}
+
 struct WgradPlan {
   int splits;          // token slices of the tensor-core kernel
   int side_slices;     // token slices holding outlier-channel partials (0: no outlier channels)
@@ -451,6 +518,8 @@ struct WgradPlan {
   uint32_t smem_bytes, tmem_cols;
   int npad;
   long long scratch_floats;
+  long long row_scale_at;   // reference mode: offset (floats) of the per-row scales in the scratch
+  int rpw;                  // reference mode: ranks per CTA of the pool kernel
 };
 
 // Resident CTAs per SM from the kernel's own resource use (registers, shared memory, threads).
@@ -483,7 +552,8 @@ static int wgrad_plan(const hyc_packed* saved, int rank, WgradPlan* pl) {
   while (cols < static_cast<uint32_t>(nseg * pl->npad)) cols *= 2;
   pl->tmem_cols = cols;
   const uint32_t b_stage = (kChunk / 8) * (pl->npad / 8) * 128u;
-  const uint32_t nb = (bits < 8 && saved->group) ? nseg : 1u;
+  const bool ref = saved->mode == HYC_MODE_R;
+  const uint32_t nb = (!ref && bits < 8 && saved->group) ? nseg : 1u;
   pl->smem_bytes = 1024 + 2u * nseg * kAStage + 2u * nb * b_stage;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -509,7 +579,7 @@ static int wgrad_plan(const hyc_packed* saved, int rank, WgradPlan* pl) {
   // A side CTA has no register prefetch and takes about as long per chunk as a 4-bit code CTA; with 8-bit codes
   // (one segment per chunk) the code CTAs are faster, so two side CTAs share a token slice.
   pl->side_split = bits == 8 ? 2 : 1;
-  const int side_tiles = saved->n_channels > 0 ? (saved->n_channels + kTileM - 1) / kTileM * pl->side_split : 0;
+  const int side_tiles = (!ref && saved->n_channels > 0) ? (saved->n_channels + kTileM - 1) / kTileM * pl->side_split : 0;
   pl->side_tiles = side_tiles;
   long long splits = static_cast<long long>(sms) * per_sm / (tiles + side_tiles);
   // every slice costs a partial slab (written, then read by the finish kernel) and a prologue/epilogue:
@@ -523,16 +593,31 @@ static int wgrad_plan(const hyc_packed* saved, int rank, WgradPlan* pl) {
   pl->side_slices = side_tiles ? pl->splits * pl->side_split : 0;
   pl->scratch_floats = static_cast<long long>(pl->splits) * rank * D +
                        static_cast<long long>(pl->side_slices) * saved->n_channels * rank;
+  // reference mode: one fp32 scale per row behind the slabs, and the ranks a pool CTA accumulates at once
+  pl->row_scale_at = pl->scratch_floats;
+  pl->rpw = 0;
+  if (ref) {
+    pl->scratch_floats += (saved->rows + 3) / 4 * 4;
+    int rpw = 8;
+    while (rpw > 1 && static_cast<long long>(rpw) * D * 4 > 160 * 1024) rpw >>= 1;
+    pl->rpw = rpw;
+  }
   return HYC_OK;
 }
 
 static int wgrad_check(const hyc_packed* saved, int rank) {
   if (!saved) return HYC_ERR_NULL;
-  if (saved->mode != HYC_MODE_N) return HYC_ERR_MODE;
+  if (saved->mode != HYC_MODE_N && saved->mode != HYC_MODE_R) return HYC_ERR_MODE;
   if (saved->bits != 2 && saved->bits != 4 && saved->bits != 8) return HYC_ERR_BITS;
   const int D = saved->cols;
   if (saved->rows < 0 || D <= 0 || D % 128 != 0 || (D * saved->bits / 8) % kTileM != 0) return HYC_ERR_SHAPE;
   if (rank < 8 || rank > 64 || rank % 8 != 0) return HYC_ERR_SHAPE;
+  if (saved->mode == HYC_MODE_R) {
+    if (saved->scale_kind < HYC_SCALE_TENSOR || saved->scale_kind > HYC_SCALE_TOKEN) return HYC_ERR_MODE;
+    if (saved->scale_dtype != HYC_BF16) return HYC_ERR_DTYPE;
+    if (saved->seq < 1 || saved->rows > 0xffffffffLL * 1) return HYC_ERR_SHAPE;
+    return HYC_OK;
+  }
   if (saved->group != 0 && saved->group != 128) return HYC_ERR_SHAPE;
   if (saved->rotate != 0 && saved->rotate != 16 && saved->rotate != 64 && saved->rotate != 256 &&
       saved->rotate != 1024 && saved->rotate != 4096)
@@ -562,8 +647,10 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int rc = wgrad_check(saved, rank);
   if (rc != HYC_OK) return rc;
-  if (!saved->codes || !grad || !out || !partials || !saved->scales) return HYC_ERR_NULL;
-  if (saved->n_channels > 0 && (!saved->channels || !saved->out_value)) return HYC_ERR_NULL;
+  const bool ref = saved->mode == HYC_MODE_R;
+  if (!saved->codes || !grad || !out || !partials) return HYC_ERR_NULL;
+  if (ref ? (!saved->scale || !saved->pool || !saved->row_meta) : !saved->scales) return HYC_ERR_NULL;
+  if (!ref && saved->n_channels > 0 && (!saved->channels || !saved->out_value)) return HYC_ERR_NULL;
   const int D = saved->cols;
   if ((reinterpret_cast<uintptr_t>(grad) & 15u) || (reinterpret_cast<uintptr_t>(saved->codes) & 15u) ||
       (reinterpret_cast<uintptr_t>(partials) & 15u))
@@ -582,8 +669,15 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
   a.p.mode = saved->mode; a.p.bits = saved->bits; a.p.rows = saved->rows; a.p.cols = D; a.p.seq = saved->seq;
   a.p.codes = static_cast<unsigned char*>(saved->codes);
   a.p.status = saved->status;
-  a.p.group = saved->group; a.p.rotate = saved->rotate;
+  a.p.group = ref ? 0 : saved->group; a.p.rotate = ref ? 0 : saved->rotate;
   a.p.scales = saved->scales;
+  if (ref) {
+    float* row_scale = partials + pl.row_scale_at;
+    r_row_scale_kernel<<<static_cast<unsigned int>((saved->rows + 255) / 256), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(saved->scale), saved->scale_kind, saved->seq, saved->rows, row_scale);
+    HYC_LAUNCHED();
+    a.p.scales = row_scale;
+  }
   a.grad = static_cast<const __nv_bfloat16*>(grad);
   a.rank = rank;
   a.npad = pl.npad;
@@ -593,7 +687,7 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
   a.tmem_cols = pl.tmem_cols;
   a.tiles = D * saved->bits / 8 / kTileM;
   a.side_split = pl.side_split;
-  a.k = saved->n_channels;
+  a.k = ref ? 0 : saved->n_channels;
   a.out_value = static_cast<const __nv_bfloat16*>(saved->out_value);
   a.side = partials + static_cast<long long>(splits) * slab;
   const uint32_t smem_bytes = pl.smem_bytes;
@@ -609,11 +703,24 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
   if (saved->bits == 2) HYC_WG(2) else if (saved->bits == 4) HYC_WG(4) else HYC_WG(8)
 #undef HYC_WG
   if (cudaGetLastError() != cudaSuccess) return HYC_ERR_CUDA;
-  const int k = saved->n_channels;
+  const __nv_bfloat16* colscale =
+      (ref && saved->scale_kind == HYC_SCALE_CHANNEL) ? static_cast<const __nv_bfloat16*>(saved->scale) : nullptr;
+  if (ref) {
+    // element outliers into the slabs
+    const size_t sm = static_cast<size_t>(pl.rpw) * D * 4;
+    if (cudaFuncSetAttribute(wgrad_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
+      return HYC_ERR_CUDA;
+    wgrad_pool_kernel<<<dim3((rank + pl.rpw - 1) / pl.rpw, splits), 512, sm, stream>>>(
+        saved->pool, reinterpret_cast<const uint2*>(saved->row_meta), a.grad, rank, pl.rpw, D, saved->rows,
+        a.tokens_per_split, colscale, partials);
+    HYC_LAUNCHED();
+    if (cudaGetLastError() != cudaSuccess) return HYC_ERR_CUDA;
+  }
+  const int k = ref ? 0 : saved->n_channels;
   const float* side = partials + static_cast<long long>(splits) * slab;
   {
     // parts of a row are independent when they hold whole rotation blocks
-    const int unit = saved->rotate ? saved->rotate : 128;
+    const int unit = (!ref && saved->rotate) ? saved->rotate : 128;
     int parts = 8;
     while (parts > 1 && (D % parts != 0 || (D / parts) % unit != 0 || (D / parts) % 128 != 0)) parts >>= 1;
     const size_t sm = static_cast<size_t>(D / parts) * 4;
@@ -621,7 +728,8 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
       if (cudaFuncSetAttribute(wgrad_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
         return HYC_ERR_CUDA;
     wgrad_finish_kernel<<<dim3(rank, parts), 256, sm, stream>>>(partials, splits, side, pl.side_slices, saved->channels,
-                                                               pl.side_slices > 0 ? k : 0, rank, D, saved->rotate, out); HYC_LAUNCHED();
+                                                               pl.side_slices > 0 ? k : 0, rank, D,
+                                                               ref ? 0 : saved->rotate, colscale, out); HYC_LAUNCHED();
   }
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }

@@ -487,20 +487,23 @@ def select_channels(score: torch.Tensor, k: int) -> torch.Tensor:
 
 
 def lora_wgrad_supported(p: Packed, rank: int) -> bool:
-    """Formats the tensor-core weight-gradient kernel takes."""
-    return (p.mode == "N" and rank % 8 == 0 and 8 <= rank <= 64 and (p.cols * p.bits // 8) % 128 == 0
+    """Formats the tensor-core weight-gradient kernel takes: channel-mode records, and reference-mode records
+    with 2-, 4- or 8-bit codes."""
+    return (p.bits in (2, 4, 8) and rank % 8 == 0 and 8 <= rank <= 64 and (p.cols * p.bits // 8) % 128 == 0
             and p.rows > 0)
 
 
 def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False) -> torch.Tensor:
     """``dW[r, D] = sum_t G[t, r] * X_hat[t, d]`` in fp32 from the packed input.
 
-    Channel-mode activations go to the dequant-fused tcgen05 kernel (the
-    reconstruction never touches HBM); the outlier channels' columns, the
-    skinny product ``G^T @ out_value``, come from a second kernel of the same call.  Other formats are rebuilt by the
-    decompress kernel and contracted by a library GEMM in bf16 with fp32
-    accumulation -- the arithmetic of the reference (efficient_linear.py:61-67)
-    followed by the autograd engine's sum over the batch."""
+    The packed codes go to the dequant-fused tcgen05 kernel (the reconstruction never touches HBM).  Channel
+    mode: the outlier channels' columns, the skinny product ``G^T @ out_value``, come from extra thread blocks
+    of the same launch.  Reference mode: static scales are folded into the gradient rows (per token / per
+    tensor) or into the result's columns (per channel), the element outliers are added as a sparse side term
+    by a second kernel, and a low-rank part adds ``(sum over the batch of G)^T @ lowrank`` here, one small
+    library GEMM.  1-bit codes (and ranks the kernel does not take) are rebuilt by the decompress kernel and
+    contracted by a library GEMM in bf16 with fp32 accumulation -- the arithmetic of the reference
+    (efficient_linear.py:61-67) followed by the autograd engine's sum over the batch."""
     _require_cuda(grad_output)
     rank = grad_output.shape[-1]
     g = grad_output.reshape(p.rows, rank).to(torch.bfloat16).contiguous()
@@ -514,6 +517,10 @@ def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False
     out = torch.empty((rank, p.cols), dtype=torch.float32, device=g.device)
     partials = torch.empty(need, dtype=torch.float32, device=g.device)
     check(lib.hyc_lora_wgrad(C.byref(rec), _ptr(g), rank, _ptr(out), _ptr(partials), _stream()), "hyc_lora_wgrad")
+    if p.mode == "R" and p.lowrank is not None:
+        # the low-rank rows repeat for every batch element: contract them with the batch sum of the gradient
+        gsum = g.view(-1, p.seq, rank).sum(dim=0, dtype=torch.float32).to(torch.bfloat16)
+        out.addmm_(gsum.t().float(), p.lowrank.float())
     return out
 
 

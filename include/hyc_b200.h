@@ -208,15 +208,20 @@ int hyc_channel_absmax(const hyc_dense* x, int64_t rows, int32_t cols, int32_t s
 int hyc_select_channels(const float* score, int32_t cols, int32_t k, int32_t* channels,
                         int32_t* rank_scratch, void* stream);
 
-/* LoRA-A weight gradient from a packed activation (channel mode), on the tcgen05 tensor cores:
+/* LoRA-A weight gradient from a packed activation, on the tcgen05 tensor cores:
  *     out[n, d] = sum_t grad[t, n] * X_hat[t, d],   fp32 [rank, cols].
  * Replaces the decompress + batched GEMM + batch sum of efficient_linear.py:61,66-67 without
  * writing X_hat to memory.  grad is bf16 [rows, rank] (contiguous, 16-byte aligned), rank a
- * multiple of 8 in [8, 64]; cols*bits/8 must be a multiple of 128.  `partials` is 16-byte aligned
- * scratch of hyc_lora_wgrad_scratch_floats(saved, rank) floats (a negative return is a hyc_status).
- * The columns of the outlier channels are out[:, channels] = grad^T * out_value, computed by extra
- * thread blocks of the same tensor-core kernel; with rotation the result already includes the inverse
- * rotation.  The sums are taken in a fixed order (no atomics): the result is reproducible. */
+ * multiple of 8 in [8, 64]; bits in {2,4,8}; cols*bits/8 must be a multiple of 128.  `partials` is
+ * 16-byte aligned scratch of hyc_lora_wgrad_scratch_floats(saved, rank) floats (a negative return
+ * is a hyc_status).  The sums over tokens are taken in a fixed order (no global atomics).
+ * HYC_MODE_N: the columns of the outlier channels are out[:, channels] = grad^T * out_value,
+ * computed by extra thread blocks of the same tensor-core kernel; with rotation the result already
+ * includes the inverse rotation.
+ * HYC_MODE_R: the static scale is folded into the gradient rows (per tensor / per position) or
+ * into the result's columns (per channel); the element outliers of the pool are added as a sparse
+ * side term by a second kernel.  A low-rank part is NOT included: the caller adds
+ * (sum over batch elements of grad)^T * lowrank, a [rank, seq] x [seq, cols] product. */
 int64_t hyc_lora_wgrad_scratch_floats(const hyc_packed* saved, int32_t rank);
 int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, float* out, float* partials, void* stream);
 

@@ -431,6 +431,32 @@ def test_lora_weight_gradient_from_codes(pk, rows, d, bits, group, rotate, rank,
     assert not p.wait_expired()
 
 
+@pytest.mark.parametrize("b,s,d,bits,method,rank,lr_rank,dtype", [
+    (4, 512, 4096, 4, "per-channel", 64, 0, torch.bfloat16), (3, 100, 768, 4, "per-token", 16, 0, torch.float32),
+    (2, 700, 4096, 8, "per-channel", 64, 2, torch.bfloat16), (5, 64, 1024, 2, "per-tensor", 32, 0, torch.bfloat16),
+    (2, 256, 11008, 4, "per-channel", 64, 0, torch.bfloat16), (2, 128, 2048, 8, "per-token", 8, 4, torch.bfloat16)])
+def test_lora_weight_gradient_from_reference_mode_codes(pk, b, s, d, bits, method, rank, lr_rank, dtype):
+    """The reference's own format through the tensor-core kernel: static per-channel / per-token / per-tensor
+    scales, element outliers from the pool, optional low-rank part; against the oracle's LoRA-A weight gradient
+    on the oracle's reconstruction (operators/efficient_linear.py:61-67)."""
+    x, _ = synthetic.roundtrip_activation(b, s, d, planted=max(4, d // 100), gain=20.0, dtype=dtype, salt=d + bits + rank)
+    g = torch.randn(b, s, rank, generator=torch.Generator().manual_seed(rank + d)).to(torch.bfloat16)
+    torch.manual_seed(d)
+    thr, L, R, scale = oc.r_calibrate(x, 0.01, 1.0, bits, method, lr_rank)
+    c = oc.r_compress(x, thr, scale, bits, 1.0, L if lr_rank else None, R if lr_rank else None)
+    xh = oc.r_decompress(c, L if lr_rank else None, R if lr_rank else None)
+    lr = (oc.fit_rows(L, s) @ R).to(torch.bfloat16).to(DEV) if lr_rank else None
+    p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), bits, lowrank=lr, outlier_ratio=0.01)
+    assert torch.equal(p.codes.cpu().reshape(c.codes.shape).view(torch.uint8), c.codes.view(torch.uint8))
+    assert pk.lora_wgrad_supported(p, rank) and int(p.status.item()) == 0
+    dw = pk.lora_wgrad(p, g.to(DEV))
+    want = torch.einsum("bsr,bsd->rd", g.float(), xh.float())
+    assert dw.shape == (rank, d) and dw.dtype == torch.float32
+    assert _cos(dw, want) > 0.9999 and _rel_err(dw, want) < 1e-2
+    assert _cos(dw, pk.lora_wgrad(p, g.to(DEV), force_library=True)) > 0.9999
+    assert not p.wait_expired()
+
+
 # ------------------------------------------------------------------ full-size properties (configuration 5 shapes)
 
 @pytest.mark.parametrize("bits,group,rotate,rows", [(4, 0, 0, 65536), (2, 128, 256, 16384), (8, 0, 256, 16384)])
