@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
   const PackedDev& p = a.p;
   const int D = p.cols;
   const int segw = D / NSEG;
-  const int U = segw >> 3;                  // a multiple of 32 here
+  const int U = segw >> 3;                  // a multiple of 32 here: a warp is wholly inside or outside a unit round
   const int k = p.n_channels;
   const int nrot = p.rotate;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
@@ -395,6 +395,7 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
         float s1 = 0.f;
 #pragma unroll
         for (int r = 0; r < NG; ++r) {
+          if (32 * (r / NSEG) >= U) continue;            // register groups beyond the row (uniform over the warp)
           float f[8];
           load8<__nv_bfloat16>(xs, (r % NSEG) * segw + ((lane + 32 * (r / NSEG)) << 3), f);
 #pragma unroll
@@ -407,6 +408,7 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
       float ss = 0.f;
 #pragma unroll
       for (int r = 0; r < NG; ++r) {
+        if (32 * (r / NSEG) >= U) continue;
         float f[8];
         load8<__nv_bfloat16>(xs, (r % NSEG) * segw + ((lane + 32 * (r / NSEG)) << 3), f);
 #pragma unroll
@@ -431,6 +433,16 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
 #pragma unroll
     for (int iu = 0; iu < UPL; ++iu) {
       const int u = lane + 32 * iu;
+      if (32 * iu >= U) {
+        // a unit round beyond the row: nothing to read, rotate or store; its registers quantise to nothing
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+          if (GROUP) ginv[GROUP ? iu * NSEG + s : 0] = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) rot[iu * NSEG + s][e] = 0.f;
+        }
+        continue;
+      }
 #pragma unroll
       for (int s = 0; s < NSEG; ++s) {
         const int col = s * segw + (u << 3);
@@ -482,6 +494,7 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
     }
 #pragma unroll
     for (int iu = 0; iu < UPL; ++iu) {
+      if (32 * iu >= U) continue;
       PackAcc<BITS> acc;
 #pragma unroll
       for (int s = 0; s < NSEG; ++s) acc.add(rot[iu * NSEG + s], GROUP ? ginv[GROUP ? iu * NSEG + s : 0] : inv_row, s);

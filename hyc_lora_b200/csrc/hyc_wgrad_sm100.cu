@@ -34,7 +34,10 @@
 // wgrad_pool_kernel accumulates it in shared memory, one CTA per (token slice, group of ranks),
 // and adds it into that slice's partial slab before the finish kernel runs.  A low-rank part is
 // left to the caller: it adds (sum over the batch of G)^T * lowrank, one small dense product.
+#include <stdlib.h>
+
 #include <mutex>
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -416,6 +419,321 @@ __global__ void __launch_bounds__(kWgThreads, 2) lora_wgrad_kernel(const __grid_
   if (warp == 0) tmem_dealloc(tmem_base, a.tmem_cols);
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Warp-specialised variant for launches in which every CTA is a code tile (reference-mode records and
+// channel-mode records without outlier channels; 2- and 4-bit codes; 4096 rows or more).  Measured on
+// [65536, 4096] INT4, rank 64: 0.105-0.114 ms against 0.128 ms for the kernel above.  Both kernels are bound by
+// shared-memory bandwidth, not by the tensor pipe: every element of the A operand is written to shared memory
+// once as bf16 and read from it once by the tensor core (4 bytes of shared-memory traffic per element, about
+// 30 us of the 128 bytes per clock and SM for this shape), on top of which come the code tile and the B tiles.
+//
+// Roles inside one CTA per SM (320 threads):
+//   warp 8, one thread    brings the packed code tiles -- 64 tokens x 128 bytes -- into a four-deep ring of
+//                         shared-memory tiles with 2-D tensor copies (cp.async.bulk.tensor, 128-byte swizzle,
+//                         completion on an mbarrier, no multicast);
+//   warps 0-7             turn a code tile into the bf16 A tiles (one per segment) and the scaled gradient
+//                         rows into the B tile(s) of a three-deep operand ring, and hand the stage to
+//   warp 9, one thread    which issues the tcgen05.mma instructions of the stage and lets tcgen05.commit
+//                         release it;
+//   warps 0-3             read the accumulators back from tensor memory at the end.
+// Every hand-over is an mbarrier (no CTA barrier per chunk), so the copies of chunk c+3, the conversion of
+// chunk c+1 and the tensor-core work of chunk c overlap.  The swizzled tile makes both sides of the
+// conversion free of bank conflicts: lanes read along tokens (8 tokens x 2 sixteen-byte pieces per
+// wavefront) and write the core matrices along tokens too.  Every wait is bounded; a role that gives up
+// raises the CTA's flag, the others see it, copies in flight are waited for (bounded) and tensor memory is
+// freed before the CTA ends.
+constexpr int kWsConvWarps = 8;
+constexpr int kWsThreads = (kWsConvWarps + 2) * 32;
+constexpr int kWsCodeStages = 4;
+constexpr uint32_t kWsCodeTile = kChunk * kTileM;   // 8 KiB
+constexpr long long kWsMinRows = 4096;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 2-D tiled copy global -> this CTA's shared memory (x: byte column, a multiple of 16; y: row)
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          dst_smem),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// operand stages: three, or two where four segments of A tiles would not fit three times
+__host__ __device__ constexpr int ws_ab_stages(int bits) { return bits == 2 ? 2 : 3; }
+
+template <int BITS>
+__global__ void __launch_bounds__(kWsThreads, 1) lora_wgrad_ws_kernel(const __grid_constant__ WgradArgs a,
+                                                                      const __grid_constant__ CUtensorMap tmap) {
+  constexpr int NSEG = 8 / BITS;
+  constexpr int kWsAbStages = ws_ab_stages(BITS);
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const PackedDev& p = a.p;
+  const int D = p.cols;
+  const int segw = D / NSEG;
+  const int G = p.group ? (D >> 7) : 1;
+  const int npad = a.npad;
+  const uint32_t b_lbo = static_cast<uint32_t>(npad / 8) * 128u;
+  const uint32_t b_stage = (kChunk / 8) * b_lbo;
+  const int nb = (BITS < 8 && p.group) ? NSEG : 1;
+  // shared-memory map
+  uint64_t* code_full = reinterpret_cast<uint64_t*>(smem);          // [4] a code tile has landed
+  uint64_t* code_empty = code_full + kWsCodeStages;                 // [4] the converters are done with it
+  uint64_t* ab_full = code_empty + kWsCodeStages;                   // [stages] operand stage written
+  uint64_t* ab_empty = ab_full + kWsAbStages;                       // [stages] its MMAs have finished
+  uint64_t* acc_done = ab_empty + kWsAbStages;                      // every MMA of the CTA has finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 128);
+  volatile uint32_t* fail = reinterpret_cast<volatile uint32_t*>(smem + 132);
+  unsigned char* code_ring = smem + 1024;                           // [4][8 KiB], 1024-byte aligned (swizzle atom)
+  unsigned char* a_buf = code_ring + kWsCodeStages * kWsCodeTile;   // [3][NSEG][kAStage]
+  unsigned char* b_buf = a_buf + static_cast<size_t>(kWsAbStages) * NSEG * kAStage;   // [3][nb][b_stage]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    for (int i = 0; i < kWsCodeStages; ++i) { mbar_init(&code_full[i], 1); mbar_init(&code_empty[i], kWsConvWarps); }
+    for (int i = 0; i < kWsAbStages; ++i) { mbar_init(&ab_full[i], kWsConvWarps); mbar_init(&ab_empty[i], 1); }
+    mbar_init(acc_done, 1);
+    fence_barrier_init();
+    *fail = 0;
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, a.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int byte0 = blockIdx.x * kTileM;   // first packed byte column of this CTA
+  const long long t_begin = static_cast<long long>(blockIdx.y) * a.tokens_per_split;
+  const long long t_end = min(p.rows, t_begin + a.tokens_per_split);
+  const int nchunks = t_end > t_begin ? static_cast<int>((t_end - t_begin + kChunk - 1) / kChunk) : 0;
+  const uint32_t a_smem = smem_u32(a_buf), b_smem = smem_u32(b_buf);
+
+  if (warp == kWsConvWarps) {
+    // ---------------------------------------------------------------- copy role
+    if (lane == 0) {
+      int issued = 0;
+      for (int c = 0; c < nchunks; ++c) {
+        const int st = c % kWsCodeStages;
+        if (c >= kWsCodeStages) {
+          if (!mbar_wait_bounded(&code_empty[st], ((c / kWsCodeStages) - 1) & 1)) *fail = 1;
+        }
+        if (*fail) break;
+        mbar_expect_tx(&code_full[st], kWsCodeTile);
+        tma_load_2d(smem_u32(code_ring + st * kWsCodeTile), &tmap, byte0, static_cast<int>(t_begin + static_cast<long long>(c) * kChunk),
+                    &code_full[st]);
+        issued = c + 1;
+      }
+      if (*fail) {
+        // copies still in flight must land before the CTA's shared memory goes away
+        for (int c = max(0, issued - kWsCodeStages); c < issued; ++c)
+          (void)mbar_wait_bounded(&code_full[c % kWsCodeStages], (c / kWsCodeStages) & 1);
+      }
+    }
+  } else if (warp == kWsConvWarps + 1) {
+    // ---------------------------------------------------------------- tensor-core role
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(npad);
+      const uint32_t b_k_step = (2u * b_lbo) >> 4, b_s_step = nb > 1 ? (b_stage >> 4) : 0u;
+      for (int c = 0; c < nchunks; ++c) {
+        const int st = c % kWsAbStages;
+        if (!mbar_wait_bounded(&ab_full[st], (c / kWsAbStages) & 1)) *fail = 1;
+        if (*fail) break;
+        tc_fence_after();
+        const uint32_t abase = a_smem + static_cast<uint32_t>(st) * NSEG * kAStage;
+        const uint32_t bbase = b_smem + static_cast<uint32_t>(st) * nb * b_stage;
+        const uint32_t a_lo = desc_lo(abase, kALbo), b_lo = desc_lo(bbase, b_lbo);
+        const uint32_t acc0 = c > 0 ? 1u : 0u;
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+#pragma unroll
+          for (int ks = 0; ks < kChunk / 16; ++ks) {
+            umma_bf16(tmem_base + static_cast<uint32_t>(s) * static_cast<uint32_t>(npad),
+                      a_lo + ((s * kAStage + ks * 2 * kALbo) >> 4), desc_hi(kASbo),
+                      b_lo + static_cast<uint32_t>(s) * b_s_step + static_cast<uint32_t>(ks) * b_k_step, desc_hi(kBSbo),
+                      idesc, ks > 0 ? 1u : acc0);
+          }
+        }
+        umma_commit(&ab_empty[st]);
+      }
+      // one more commit covers everything issued; on the give-up path it is also what this thread waits
+      // for (bounded) before tensor memory may be freed
+      umma_commit(acc_done);
+      if (*fail) (void)mbar_wait_bounded(acc_done, 0);
+    }
+  } else {
+    // ---------------------------------------------------------------- conversion role (warps 0-7)
+    const int k0 = lane & 7, u_lo = lane >> 3;
+    constexpr int kAItems = (kChunk / 8) * 4 / kWsConvWarps;   // 4 per warp and chunk
+    const int b_per_tg = (npad / 8 + 3) / 4;                     // 1 or 2 B items per token group
+    uint32_t a_src[kAItems], a_dst[kAItems];
+#pragma unroll
+    for (int i = 0; i < kAItems; ++i) {
+      const int item = warp + i * kWsConvWarps;
+      const int tg = item >> 2, unit = ((item & 3) << 2) + u_lo;
+      const int tl = tg * 8 + k0;                                 // token inside the chunk
+      // swizzled tile: sixteen-byte piece c of row t sits at piece c ^ (t & 7)
+      a_src[i] = static_cast<uint32_t>(tl) * kTileM + ((((unit >> 1) ^ (tl & 7))) << 4) + ((unit & 1) << 3);
+      a_dst[i] = tg * kALbo + unit * kASbo + k0 * 16;
+    }
+    // B items of this thread: j = warp, warp + 8
+    int b_tg[2], b_n1[2];
+    bool b_own[2], b_real[2];
+    uint32_t b_dst[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int j = warp + i * kWsConvWarps;
+      b_tg[i] = b_per_tg == 2 ? (j >> 1) : j;
+      b_n1[i] = (b_per_tg == 2 ? (j & 1) : 0) * 4 + u_lo;
+      b_own[i] = j < (kChunk / 8) * b_per_tg && b_n1[i] < npad / 8;
+      b_real[i] = b_own[i] && (b_n1[i] << 3) < a.rank;
+      b_dst[i] = b_tg[i] * b_lbo + b_n1[i] * kBSbo + k0 * 16;
+    }
+    const int b_sc_seg = p.group ? (segw >> 7) : 0;
+    // gradient rows and scales come straight from global memory, two chunks ahead of their use (a chunk is
+    // shorter than a global load's latency)
+    uint4 g_reg[2], g_nxt[2];
+    float gs_reg[2][NSEG], gs_nxt[2][NSEG];
+    float a_sc_reg[kAItems], a_sc_nxt[kAItems];   // 8-bit path: scale of the token of every A item
+    auto fetch = [&](int c, uint4 (&g_reg)[2], float (&gs_reg)[2][NSEG], float (&a_sc_reg)[kAItems]) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        g_reg[i] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) gs_reg[i][s] = 0.f;
+        const long long t = t_begin + static_cast<long long>(c) * kChunk + b_tg[i] * 8 + k0;
+        if (b_real[i] && t < t_end) {
+          g_reg[i] = *reinterpret_cast<const uint4*>(a.grad + t * a.rank + (b_n1[i] << 3));
+          if (BITS < 8) {
+            const float* sc = p.scales + t * G + (p.group ? (byte0 >> 7) : 0);
+#pragma unroll
+            for (int s = 0; s < NSEG; ++s)
+              if (s < nb) gs_reg[i][s] = __ldg(sc + s * b_sc_seg);
+          }
+        }
+      }
+      if (BITS == 8) {
+#pragma unroll
+        for (int i = 0; i < kAItems; ++i) {
+          const int item = warp + i * kWsConvWarps;
+          long long t = t_begin + static_cast<long long>(c) * kChunk + (item >> 2) * 8 + k0;
+          if (t > p.rows - 1) t = p.rows - 1;
+          a_sc_reg[i] = __ldg(p.scales + t * G + (p.group ? ((byte0 + ((((item & 3) << 2) + u_lo) << 3)) >> 7) : 0));
+        }
+      }
+    };
+    if (nchunks > 0) fetch(0, g_reg, gs_reg, a_sc_reg);
+    if (nchunks > 1) fetch(1, g_nxt, gs_nxt, a_sc_nxt);
+    for (int c = 0; c < nchunks; ++c) {
+      const int cst = c % kWsCodeStages, ast = c % kWsAbStages;
+      uint4 g_cur[2];
+      float gs_cur[2][NSEG], a_sc_cur[kAItems];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        g_cur[i] = g_reg[i];
+        g_reg[i] = g_nxt[i];
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) { gs_cur[i][s] = gs_reg[i][s]; gs_reg[i][s] = gs_nxt[i][s]; }
+      }
+#pragma unroll
+      for (int i = 0; i < kAItems; ++i) { a_sc_cur[i] = a_sc_reg[i]; a_sc_reg[i] = a_sc_nxt[i]; }
+      if (c + 2 < nchunks) fetch(c + 2, g_nxt, gs_nxt, a_sc_nxt);
+      if (!mbar_wait_bounded(&code_full[cst], (c / kWsCodeStages) & 1)) *fail = 1;
+      if (c >= kWsAbStages) {
+        if (!mbar_wait_bounded(&ab_empty[ast], ((c / kWsAbStages) - 1) & 1)) *fail = 1;
+        tc_fence_after();
+      }
+      if (*fail) break;
+      const unsigned char* tile = code_ring + cst * kWsCodeTile;
+      const uint32_t abase = a_smem + static_cast<uint32_t>(ast) * NSEG * kAStage;
+      const uint32_t bbase = b_smem + static_cast<uint32_t>(ast) * nb * b_stage;
+#pragma unroll
+      for (int i = 0; i < kAItems; ++i) {
+        const uint2 cw = *reinterpret_cast<const uint2*>(tile + a_src[i]);
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+          uint4 v;
+          if (BITS == 8) {
+            float f[8];
+            dequant8<BITS>(cw, s, a_sc_cur[i], f);
+            v = pack_bf16x8(f);
+          } else {
+            constexpr uint32_t m = 0x01010101u * CodeTraits<BITS>::kMask;
+            const uint32_t lo = (cw.x >> (s * BITS)) & m, hi = (cw.y >> (s * BITS)) & m;
+            const __nv_bfloat162 bias = __float2bfloat162_rn(128.f + static_cast<float>(CodeTraits<BITS>::kOff));
+            auto two = [&](uint32_t w, uint32_t sel) {
+              const uint32_t bits = __byte_perm(w, 0x43004300u, sel);      // (128 + field) as bf16x2
+              __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&bits), bias);
+              return *reinterpret_cast<uint32_t*>(&r);
+            };
+            v = make_uint4(two(lo, 0x7150), two(lo, 0x7352), two(hi, 0x7150), two(hi, 0x7352));
+          }
+          st_shared_u4(abase + s * kAStage + a_dst[i], v);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        if (b_own[i]) {
+          if (BITS == 8) {
+            st_shared_u4(bbase + b_dst[i], g_cur[i]);
+          } else {
+            float gv[8];
+            unpack_bf16x8(g_cur[i], gv);
+#pragma unroll
+            for (int s = 0; s < NSEG; ++s) {
+              if (s < nb) {
+                float sv[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sv[e] = gv[e] * gs_cur[i][s];
+                st_shared_u4(bbase + s * b_stage + b_dst[i], pack_bf16x8(sv));
+              }
+            }
+          }
+        }
+      }
+      fence_proxy_async();          // generic-proxy stores -> visible to the tensor-core (async) proxy
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&code_empty[cst]);
+        mbar_arrive(&ab_full[ast]);
+      }
+    }
+    // ---------------------------------------------------------------- read the accumulators back (warps 0-3)
+    if (warp < 4) {
+      if (nchunks > 0 && !*fail) {
+        if (!mbar_wait_bounded(acc_done, 0)) *fail = 1;
+      }
+      tc_fence_after();
+      const bool failed = *fail != 0;
+      float* slab = a.partials + static_cast<long long>(blockIdx.y) * a.rank * D;
+#pragma unroll
+      for (int s = 0; s < NSEG; ++s) {
+        const int d = s * segw + byte0 + warp * 32 + lane;      // channel of this thread's accumulator row
+        for (int n0 = 0; n0 < npad; n0 += 16) {
+          uint32_t v[16];
+          if (nchunks > 0 && !failed) {
+            tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(s * npad + n0), v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int q = 0; q < 16; ++q) v[q] = 0u;
+          }
+#pragma unroll
+          for (int q = 0; q < 16; ++q)
+            if (n0 + q < a.rank) slab[static_cast<long long>(n0 + q) * D + d] = __uint_as_float(v[q]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *fail && p.status) atomicOr(p.status, kStatusWaitExpired);
+  if (warp == 0) tmem_dealloc(tmem_base, a.tmem_cols);
+}
+
 // Last kernel of the call, one CTA per (output row n, part of the row): adds the partial slabs in a
 // fixed order, applies the inverse block rotation to the summed row in shared memory (the rotation
 // commutes with the contraction over tokens), overwrites the outlier channels' entries with the sums
@@ -520,7 +838,39 @@ struct WgradPlan {
   long long scratch_floats;
   long long row_scale_at;   // reference mode: offset (floats) of the per-row scales in the scratch
   int rpw;                  // reference mode: ranks per CTA of the pool kernel
+  bool ws;                  // code tiles on the warp-specialised kernel (one CTA per SM)
+  uint32_t ws_smem;
 };
+
+// cuTensorMapEncodeTiled through the runtime (no link-time dependency on the driver library)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// the packed codes as a 2-D byte tensor [rows][row bytes], tiles of 64 rows x 128 bytes, 128-byte swizzle
+static bool code_tensor_map(const hyc_packed* saved, CUtensorMap* map) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t cb = static_cast<cuuint64_t>(saved->cols) * saved->bits / 8;
+  const cuuint64_t dims[2] = {cb, static_cast<cuuint64_t>(saved->rows)};
+  const cuuint64_t strides[1] = {cb};
+  const cuuint32_t box[2] = {kTileM, kChunk};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, saved->codes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 // Resident CTAs per SM from the kernel's own resource use (registers, shared memory, threads).
 template <int BITS>
@@ -557,6 +907,14 @@ static int wgrad_plan(const hyc_packed* saved, int rank, WgradPlan* pl) {
   pl->smem_bytes = 1024 + 2u * nseg * kAStage + 2u * nb * b_stage;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // long inputs: warp-specialised kernel, one CTA per SM (short ones finish before its pipeline fills)
+  static const bool ws_off = getenv("HYC_WGRAD_WS") && getenv("HYC_WGRAD_WS")[0] == '0';
+  pl->ws_smem = 1024 + kWsCodeStages * kWsCodeTile + static_cast<uint32_t>(ws_ab_stages(bits)) * (nseg * kAStage + nb * b_stage);
+  // (used where every CTA is a code tile: with outlier-channel tiles in the launch the shared kernel below,
+  // two CTAs per SM, measured faster, and so it did for 8-bit codes)
+  const bool has_side = !ref && saved->n_channels > 0;
+  pl->ws = !ws_off && !has_side && bits < 8 && pl->ws_smem <= kSmemPerCtaMax && saved->rows >= kWsMinRows && tiles <= sms &&
+           encode_tiled_fn() != nullptr;
   // the device queries are cached per (device, bits, shared-memory size)
   struct Known { int dev, bits, per_sm; uint32_t smem; };
   static Known known[32];
@@ -581,7 +939,7 @@ static int wgrad_plan(const hyc_packed* saved, int rank, WgradPlan* pl) {
   pl->side_split = bits == 8 ? 2 : 1;
   const int side_tiles = (!ref && saved->n_channels > 0) ? (saved->n_channels + kTileM - 1) / kTileM * pl->side_split : 0;
   pl->side_tiles = side_tiles;
-  long long splits = static_cast<long long>(sms) * per_sm / (tiles + side_tiles);
+  long long splits = pl->ws ? sms / tiles : static_cast<long long>(sms) * per_sm / (tiles + side_tiles);
   // every slice costs a partial slab (written, then read by the finish kernel) and a prologue/epilogue:
   // keep at least four chunks per slice
   const long long max_splits = ((saved->rows + kChunk - 1) / kChunk + 3) / 4;
@@ -691,17 +1049,34 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
   a.out_value = static_cast<const __nv_bfloat16*>(saved->out_value);
   a.side = partials + static_cast<long long>(splits) * slab;
   const uint32_t smem_bytes = pl.smem_bytes;
-  const dim3 grid(a.tiles + pl.side_tiles, splits);
+  const long long code_tokens_per_split = (per + kChunk - 1) / kChunk * kChunk;
+  CUtensorMap tmap;
+  if (pl.ws && code_tensor_map(saved, &tmap)) {
+    // records without outlier-channel tiles: every CTA is a code tile, on the warp-specialised kernel
+    const dim3 wgrid(a.tiles, splits);
+#define HYC_WS(B)                                                                                         \
+  {                                                                                                       \
+    auto kern = lora_wgrad_ws_kernel<B>;                                                                  \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.ws_smem) !=       \
+        cudaSuccess)                                                                                      \
+      return HYC_ERR_CUDA;                                                                                \
+    kern<<<wgrid, kWsThreads, pl.ws_smem, stream>>>(a, tmap); HYC_LAUNCHED();                             \
+  }
+    if (saved->bits == 2) HYC_WS(2) else HYC_WS(4)
+#undef HYC_WS
+  } else {
+    const dim3 grid(a.tiles + pl.side_tiles, splits);
 #define HYC_WG(B)                                                                                         \
   {                                                                                                       \
     auto kern = lora_wgrad_kernel<B>;                                                                     \
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) !=       \
         cudaSuccess)                                                                                      \
       return HYC_ERR_CUDA;                                                                                \
-    kern<<<grid, kWgThreads, smem_bytes, stream>>>(a); HYC_LAUNCHED();                                                    \
+    kern<<<grid, kWgThreads, smem_bytes, stream>>>(a); HYC_LAUNCHED();                                    \
   }
-  if (saved->bits == 2) HYC_WG(2) else if (saved->bits == 4) HYC_WG(4) else HYC_WG(8)
+    if (saved->bits == 2) HYC_WG(2) else if (saved->bits == 4) HYC_WG(4) else HYC_WG(8)
 #undef HYC_WG
+  }
   if (cudaGetLastError() != cudaSuccess) return HYC_ERR_CUDA;
   const __nv_bfloat16* colscale =
       (ref && saved->scale_kind == HYC_SCALE_CHANNEL) ? static_cast<const __nv_bfloat16*>(saved->scale) : nullptr;
@@ -712,7 +1087,7 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
       return HYC_ERR_CUDA;
     wgrad_pool_kernel<<<dim3((rank + pl.rpw - 1) / pl.rpw, splits), 512, sm, stream>>>(
         saved->pool, reinterpret_cast<const uint2*>(saved->row_meta), a.grad, rank, pl.rpw, D, saved->rows,
-        a.tokens_per_split, colscale, partials);
+        code_tokens_per_split, colscale, partials);
     HYC_LAUNCHED();
     if (cudaGetLastError() != cudaSuccess) return HYC_ERR_CUDA;
   }

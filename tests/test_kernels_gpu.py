@@ -607,7 +607,9 @@ def _compress_into(pk, x, p, norm=None):
 
 
 @pytest.mark.parametrize("d,bits,rotate,mode", [(768, 4, 0, "N"), (768, 4, 64, "N"), (11008, 4, 0, "N"), (11008, 2, 256, "N"),
-                                               (768, 4, 0, "R"), (11008, 4, 0, "R"), (4096, 8, 256, "N")])
+                                               (768, 4, 0, "R"), (11008, 4, 0, "R"), (4096, 8, 256, "N"),
+                                               # unit counts per lane that are not a power of two (register groups beyond the row)
+                                               (2816, 8, 256, "N"), (3072, 4, 256, "N"), (3072, 4, 0, "N"), (2816, 2, 0, "N")])
 def test_kernels_write_nothing_outside_their_outputs(pk, d, bits, rotate, mode):
     """Compress (alone and fused with the norm), decompress and norm backward with every output a view
     into the middle of one guarded allocation: results equal the ordinary calls', both flanks of every
