@@ -199,8 +199,10 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
     float gq[kWarpOutPerLane];
 #pragma unroll
     for (int q = 0; q < kWarpOutPerLane; ++q) gq[q] = c.oc[q] >= 0 ? __bfloat162float(gs[c.oc[q]]) : 0.f;
-    // ---- pass 1: the two row sums
-    float c1 = 0.f, c2 = 0.f;
+    // ---- pass 1: the two row sums.  With x-hat = (x - mean) * rstd the first one is
+    //   c1 = mean_d(x-hat * w dy) = rstd * (S1 - mean * S2) / D,   S1 = sum x * w dy,  S2 = sum w dy,
+    // so the pass accumulates S1 and S2 from the rebuilt x itself (two fused multiply-adds per element).
+    float s1 = 0.f, s2 = 0.f;
 #pragma unroll 2
     for (int iu = 0; iu < upl; ++iu) {
       const int u = c.lane + 32 * iu;
@@ -221,21 +223,23 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
           load8_split(wsm, D, col, wv);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const float xn = (f[e] - mean) * rstd;
             const float wd = wv[e] * gv[e];
-            c1 = fmaf(xn, wd, c1);
-            c2 += wd;
+            s1 = fmaf(f[e], wd, s1);
+            s2 += wd;
           }
         }
       }
     }
-    // outlier channels: the true x-hat differs from the streamed one by o * rstd
+    // outlier channels: the streamed pass saw the zero their code encodes instead of the stored value
 #pragma unroll
     for (int q = 0; q < kWarpOutPerLane; ++q)
-      if (c.oc[q] >= 0) c1 = fmaf(ov[q] * rstd, wsm[split_index(c.oc[q], D)] * gq[q], c1);
-    c1 = warp_sum(c1) * inv_d;
-    c2 = (LN || a.ref_compat_c2) ? warp_sum(c2) * inv_d : 0.f;
-    // ---- pass 2: the result
+      if (c.oc[q] >= 0) s1 = fmaf(ov[q], wsm[split_index(c.oc[q], D)] * gq[q], s1);
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    const float c1 = rstd * (s1 - mean * s2) * inv_d;
+    const float c2 = (LN || a.ref_compat_c2) ? s2 * inv_d : 0.f;
+    // ---- pass 2: dx = (w dy - (x-hat * c1 + c2)) * rstd = ka * w dy + kb * x + kc with three row constants
+    const float ka = rstd, kb = -rstd * rstd * c1, kc = (mean * rstd * c1 - c2) * rstd;
     __nv_bfloat16* dxrow = a.out1 + row * D;
 #pragma unroll 2
     for (int iu = 0; iu < upl; ++iu) {
@@ -256,7 +260,7 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
           load8<__nv_bfloat16>(gs, col, gv);
           load8_split(wsm, D, col, wv);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) d[e] = (wv[e] * gv[e] - ((f[e] - mean) * rstd * c1 + c2)) * rstd;
+          for (int e = 0; e < 8; ++e) d[e] = fmaf(ka, wv[e] * gv[e], fmaf(kb, f[e], kc));
           store8<__nv_bfloat16>(dxrow, col, d);
         }
       }
@@ -269,10 +273,8 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
     }
 #pragma unroll
     for (int q = 0; q < kWarpOutPerLane; ++q) {
-      if (c.oc[q] >= 0) {
-        const float xh = (ov[q] - mean) * rstd;
-        dxrow[c.oc[q]] = __float2bfloat16_rn((wsm[split_index(c.oc[q], D)] * gq[q] - (xh * c1 + c2)) * rstd);
-      }
+      if (c.oc[q] >= 0)
+        dxrow[c.oc[q]] = __float2bfloat16_rn(fmaf(ka, wsm[split_index(c.oc[q], D)] * gq[q], fmaf(kb, ov[q], kc)));
     }
   }
 }
