@@ -375,7 +375,7 @@ def r_mode_record(packed, x, w, peak, steps):
     stored = int(p.pool_used.item())
     # read x, write y, codes, 4 B per stored outlier, 8 B row record, rstd
     nbytes = (4 * COLS + COLS * BITS // 8 + 8 + 4) * ROWS + 4 * stored
-    return {"kernel": "hyc::fwd_r_fast_kernel (fused RMSNorm + reference-mode compress)", "ms": round(ms, 4),
+    return {"kernel": "hyc::fwd_r_warp_kernel (fused RMSNorm + reference-mode compress, one warp per row)", "ms": round(ms, 4),
             "bytes": nbytes, "GBps": round(nbytes / ms / 1e6, 1), "frac": round(nbytes / ms / 1e6 / peak, 3),
             "stored_outliers": stored, "status": int(p.status.item()),
             "scale": "static per-channel INT4 (calibrated)", "outliers": "elements above the calibrated threshold"}

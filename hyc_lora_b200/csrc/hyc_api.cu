@@ -4,6 +4,7 @@
 
 #include "hyc_fwd_r_fast.cuh"
 #include "hyc_fwd_warp.cuh"
+#include "hyc_fwd_r_warp.cuh"
 
 namespace hyc {
 
@@ -30,6 +31,26 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
   if (out->rows == 0) return HYC_OK;
   const int es = x->dtype == HYC_BF16 ? 2 : 4;
   if (out->mode == HYC_MODE_R) {
+    // bf16 rows of up to 4096 channels: one warp per row
+    const RWarpPlan rw = plan_r_warp(out, x, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER);
+    if (rw.ok) {
+      RWarpArgs wa;
+      memset(&wa, 0, sizeof(wa));
+      wa.p = to_dev(out);
+      wa.x = static_cast<const __nv_bfloat16*>(x->base);
+      wa.row_stride = x->row_stride;
+      if (norm) {
+        wa.kind = norm->kind; wa.eps = norm->eps; wa.weight = norm->weight; wa.bias = norm->bias;
+        wa.param_bf16 = norm->param_dtype == HYC_BF16;
+        wa.y = static_cast<__nv_bfloat16*>(norm->y); wa.rstd = norm->rstd; wa.mean = norm->mean;
+      }
+      wa.off_csc = rw.off_csc; wa.off_crcp = rw.off_crcp; wa.off_wsm = rw.off_wsm; wa.off_bsm = rw.off_bsm;
+      wa.off_slots = rw.off_slots; wa.slot_bytes = rw.slot_bytes; wa.off_lr = rw.off_lr;
+      wa.wait_cycles = g_debug_wait_cycles > 0 ? g_debug_wait_cycles : kWaitCycles;
+      cudaError_t e = cudaMemsetAsync(out->pool_used, 0, sizeof(uint32_t), stream);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(pool_used)");
+      return launch_fwd_r_warp(wa, rw, norm != nullptr, stream);
+    }
     // register-resident kernel for 2/4/8-bit codes; 1-bit codes and rows too wide for it take the generic kernel
     const RFastPlan rf = plan_r_fast(out, es, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER);
     if (rf.ok) {

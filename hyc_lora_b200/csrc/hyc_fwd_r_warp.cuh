@@ -1,0 +1,291 @@
+// Warp-per-row forward kernel for the reference mode (bf16 rows of up to 4096 channels, 2/4/8-bit
+// codes): compress-only and fused norm + compress with the reference's arithmetic
+// (operators/compress_function.py:144-197) -- optional low-rank subtraction rounded to bf16, scalar
+// threshold on |v| selecting element outliers, static scale, correctly rounded quotient rounded to bf16,
+// round half to even, clamp, offset-binary segment packing.
+//
+// A warp owns its rows.  A row (and its low-rank row) lands in the warp's own shared-memory slot by bulk
+// asynchronous copies on the warp's own mbarrier, and the warp makes two passes over the slot with short
+// rolled loops: pass 1 takes the norm statistics and counts the row's outliers, the warp's lane 0 books the
+// row's share of the pool with one global atomic, and pass 2 writes the norm output, the packed codes and --
+// now that the place of every entry is known -- the outlier entries straight into the pool.  A row that does
+// not fit the pool is known to be one before pass 2 starts, so it is simply quantised whole (the overflow
+// bit is raised), with no second quantisation.  No CTA barrier in the row loop, no shared outlier list, no
+// helper warp; twenty warps per SM cover the atomic's round trip and the copies.
+//
+// Arithmetic per element is that of fwd_r_fast_kernel (hyc_fwd_r_fast.cuh), whose helpers are used here:
+// codes and the outlier set are identical.
+#pragma once
+#include "hyc_fwd_r_fast.cuh"
+#include "hyc_fwd_warp.cuh"
+
+namespace hyc {
+
+constexpr int kRWarpThreadsMax = 640;
+
+struct RWarpArgs {
+  PackedDev p;
+  const __nv_bfloat16* x;
+  long long row_stride;  // elements
+  int kind;
+  float eps;
+  const void* weight;
+  const void* bias;
+  int param_bf16;
+  __nv_bfloat16* y;
+  float* rstd;
+  float* mean;
+  uint32_t off_csc, off_crcp, off_wsm, off_bsm, off_slots, slot_bytes, off_lr;
+  long long wait_cycles;
+};
+
+// NK: 0 compress only, 1 RMSNorm (plain or Gemma), 2 LayerNorm
+template <int BITS, int NK>
+__global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const __grid_constant__ RWarpArgs a) {
+  using XT = __nv_bfloat16;
+  constexpr int NSEG = 8 / BITS;
+  constexpr bool NORM = NK != 0;
+  constexpr bool ln = NK == 2;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const PackedDev& p = a.p;
+  const int D = p.cols;
+  const int segw = D / NSEG;
+  const int U = segw >> 3;
+  const int upl = (U + 31) >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+  const float inv_d = 1.0f / static_cast<float>(D);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* bar = &bars[warp];
+  unsigned char* slot = smem + a.off_slots + static_cast<size_t>(warp) * a.slot_bytes;
+  const XT* xs = reinterpret_cast<const XT*>(slot);
+  const __nv_bfloat16* lrs = p.lowrank ? reinterpret_cast<const __nv_bfloat16*>(slot + a.off_lr) : nullptr;
+  const bool per_channel = p.scale_kind == kScaleChannel;
+  __nv_bfloat16* csc = per_channel ? reinterpret_cast<__nv_bfloat16*>(smem + a.off_csc) : nullptr;
+  float* crcp = per_channel ? reinterpret_cast<float*>(smem + a.off_crcp) : nullptr;
+  float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
+  float* bsm = reinterpret_cast<float*>(smem + a.off_bsm);
+  const uint32_t row_bytes = static_cast<uint32_t>(D) * 2u;
+  const long long rows = p.rows, stride = static_cast<long long>(gridDim.x) * W;
+  long long row = static_cast<long long>(blockIdx.x) * W + warp;
+  auto issue = [&](long long r) {
+    mbar_expect_tx(bar, row_bytes + (p.lowrank ? row_bytes : 0u));
+    bulk_g2s(slot, a.x + r * a.row_stride, row_bytes, bar);
+    if (p.lowrank) bulk_g2s(slot + a.off_lr, p.lowrank + (r % p.seq) * static_cast<long long>(D), row_bytes, bar);
+  };
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < W; ++i) mbar_init(&bars[i], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (lane == 0 && row < rows) issue(row);
+  if (per_channel) {
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+      csc[c] = p.scale[c];
+      crcp[split_index(c, D)] = r_safe_rcp(__bfloat162float(p.scale[c]));
+    }
+  }
+  if (NORM) {
+    const float plus = a.kind == HYC_NORM_RMS_GEMMA ? 1.f : 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+      wsm[split_index(c, D)] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[c])
+                                             : static_cast<const float*>(a.weight)[c]) + plus;
+      if (ln)
+        bsm[split_index(c, D)] = a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[c])
+                                              : static_cast<const float*>(a.bias)[c];
+    }
+  }
+  const float thr = bf16_round(*p.thr);   // the fp32 threshold is compared in the activation's dtype
+  float sc_row = 1.f, rc_row = 1.f;
+  if (p.scale_kind == kScaleTensor) {
+    sc_row = __bfloat162float(p.scale[0]);
+    rc_row = r_safe_rcp(sc_row);
+  }
+  const long long cb = static_cast<long long>(D) * BITS / 8;
+  __syncthreads();
+  uint32_t ph = 0;
+  for (; row < rows; row += stride, ph ^= 1u) {
+    if (p.scale_kind == kScaleToken) {
+      sc_row = __bfloat162float(p.scale[row % p.seq]);
+      rc_row = r_safe_rcp(sc_row);
+    }
+    if (!mbar_wait_bounded(bar, ph, a.wait_cycles)) {
+      if (lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
+      return;
+    }
+    // ---- pass 1: norm statistics (of x, before the low-rank part is removed) and the outlier count
+    float mean = 0.f;
+    if (ln) {
+      float s1 = 0.f;
+#pragma unroll 2
+      for (int iu = 0; iu < upl; ++iu) {
+        const int u = lane + 32 * iu;
+        if (u < U) {
+#pragma unroll
+          for (int s = 0; s < NSEG; ++s) {
+            float f[8];
+            load8<XT>(xs, s * segw + (u << 3), f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s1 += f[e];
+          }
+        }
+      }
+      mean = warp_sum(s1) * inv_d;
+    }
+    float ss = 0.f;
+    uint32_t mine = 0;
+#pragma unroll 2
+    for (int iu = 0; iu < upl; ++iu) {
+      const int u = lane + 32 * iu;
+      if (u < U) {
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+          const int col = s * segw + (u << 3);
+          float f[8];
+          load8<XT>(xs, col, f);
+          if (NORM) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { const float c = ln ? f[e] - mean : f[e]; ss = fmaf(c, c, ss); }
+          }
+          r_residual8<XT>(f, lrs, col);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) mine += fabsf(f[e]) > thr ? 1u : 0u;
+        }
+      }
+    }
+    // exclusive prefix of the lanes' counts and the row's total
+    uint32_t incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const uint32_t n = __shfl_sync(0xffffffffu, incl, 31);
+    // the row's share of the pool: the request leaves now, its answer is needed after the statistics
+    uint32_t base = 0;
+    if (lane == 0 && n > 0) base = atomicAdd(p.pool_used, n);
+    float rstd = 0.f;
+    if (NORM) {
+      ss = warp_sum(ss);
+      rstd = 1.0f / sqrtf(ss * inv_d + a.eps);
+      if (lane == 0) {
+        a.rstd[row] = rstd;
+        if (ln) a.mean[row] = mean;
+      }
+    }
+    base = __shfl_sync(0xffffffffu, base, 0);
+    const bool over = n > 0 && (base > p.pool_cap || n > p.pool_cap - base);
+    if (lane == 0) {
+      p.row_meta[row] = make_uint2(base, over ? 0u : n);
+      if (over && p.status) atomicOr(p.status, kStatusPoolOverflow);
+    }
+    const bool extract = !over;              // a row that does not fit the pool is quantised whole
+    uint32_t at = base + incl - mine;        // where this lane's entries go
+    // ---- pass 2: norm output, codes, outlier entries
+    unsigned char* codes_row = p.codes + row * cb;
+    XT* yrow = NORM ? a.y + row * a.row_stride : nullptr;
+#pragma unroll 2
+    for (int iu = 0; iu < upl; ++iu) {
+      const int u = lane + 32 * iu;
+      if (u < U) {
+        RPack<BITS> acc;
+        bool ok = true;
+        uint32_t flags = 0;
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+          const int col = s * segw + (u << 3);
+          float v[8];
+          load8<XT>(xs, col, v);
+          if (NORM) {
+            float y[8], wv[8];
+            load8_split(wsm, D, col, wv);
+            if (ln) {
+              float bv[8];
+              load8_split(bsm, D, col, bv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) y[e] = (v[e] - mean) * rstd * wv[e] + bv[e];
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) y[e] = v[e] * rstd * wv[e];
+            }
+            store8<XT>(yrow, col, y);
+          }
+          r_residual8<XT>(v, lrs, col);
+          RScale8 sc;
+          r_scale8(sc, csc, crcp, D, col, sc_row, rc_row);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const bool out = extract && fabsf(v[e]) > thr;
+            if (out) flags |= 1u << (s * 8 + e);
+            // what is quantised at an outlier's slot is x - x * mask as in the reference: 0, or NaN for an
+            // infinite input (the unit is then redone with the division sequence, which keeps the NaN)
+            float q = r_quotient(out ? v[e] - v[e] : v[e], sc.sc[e], sc.rc[e], ok);
+            q = bf16_round(q);
+            acc.add(q, s, e);
+          }
+        }
+        uint2 packed = acc.done();
+        if (!ok) packed = r_unit_exact<XT, BITS>(xs, lrs, csc, sc_row, segw, u, extract ? thr : __int_as_float(0x7f800000));
+        *reinterpret_cast<uint2*>(codes_row + (u << 3)) = packed;
+        // the unit's outliers, values read again from the staged row
+        while (flags) {
+          const int b = __ffs(flags) - 1;
+          flags &= flags - 1;
+          const int col = (b >> 3) * segw + (u << 3) + (b & 7);
+          float x = __bfloat162float(xs[col]);
+          if (lrs) x = bf16_round(x - __bfloat162float(lrs[col]));
+          p.pool[at++] = (float_to_bf16_bits(x) << 16) | static_cast<uint32_t>(col);
+        }
+      }
+    }
+    __syncwarp();   // every lane is done with the slot
+    const long long next = row + stride;
+    if (lane == 0 && next < rows) {
+      fence_proxy_async();
+      issue(next);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host: eligibility and launch
+
+struct RWarpPlan {
+  bool ok;
+  int threads, grid;
+  uint32_t off_csc, off_crcp, off_wsm, off_bsm, off_slots, slot_bytes, off_lr, total;
+};
+
+// bf16 rows in the plain layout, up to 4096 channels, 2/4/8-bit codes, at most 65535 columns per entry
+inline RWarpPlan plan_r_warp(const hyc_packed* q, const hyc_dense* x, bool norm, bool ln) {
+  RWarpPlan w;
+  memset(&w, 0, sizeof(w));
+  static const bool off_env = getenv("HYC_FWD_R_WARP") && getenv("HYC_FWD_R_WARP")[0] == '0';
+  if (off_env || q->mode != HYC_MODE_R || x->dtype != HYC_BF16 || x->chunks != 1) return w;
+  if (q->bits != 2 && q->bits != 4 && q->bits != 8) return w;
+  if (g_tune_threads || g_tune_stages || g_tune_ctas) return w;
+  const int D = q->cols;
+  if (D > 4096) return w;
+  uint32_t off = 64 * 8;
+  auto take = [&](uint32_t bytes) { uint32_t o = off; off = align_up(off + bytes, 16); return o; };
+  if (q->scale_kind == HYC_SCALE_CHANNEL) { w.off_csc = take(D * 2); w.off_crcp = take(D * 4); }
+  if (norm) w.off_wsm = take(D * 4);
+  if (ln) w.off_bsm = take(D * 4);
+  off = align_up(off, 128);
+  w.off_slots = off;
+  w.off_lr = align_up(static_cast<uint32_t>(D) * 2u, 128);
+  w.slot_bytes = w.off_lr * (q->lowrank ? 2u : 1u);
+  int warps = static_cast<int>((kSmemPerCtaMax - 2048 - off) / w.slot_bytes);
+  if (warps > kRWarpThreadsMax / 32) warps = kRWarpThreadsMax / 32;
+  if (warps < 4) return w;
+  w.threads = warps * 32;
+  w.total = off + w.slot_bytes * warps;
+  long long grid = sm_count();
+  const long long need = (q->rows + warps - 1) / warps;
+  if (grid > need) grid = need;
+  w.grid = static_cast<int>(grid);
+  w.ok = true;
+  return w;
+}
+
+int launch_fwd_r_warp(const RWarpArgs& a, const RWarpPlan& w, bool norm, cudaStream_t stream);
+
+}  // namespace hyc
