@@ -109,12 +109,17 @@ def lowrank_product(L: Optional[torch.Tensor], R: Optional[torch.Tensor], seq: i
     small library GEMM; it is cached while L and R are the same tensors."""
     if rank == 0 or L is None or R is None:
         return None
-    key = (L.data_ptr(), R.data_ptr(), L._version, R._version, seq)
+    # the entry is valid for these very tensor objects (held weakly: a new tensor that happens to reuse a freed
+    # tensor's address never matches), unmodified since
+    key = (L._version, R._version, seq)
     if cache is not None and cache.get("key") == key:
-        return cache["value"]
+        refs = cache.get("refs")
+        if refs is not None and refs[0]() is L and refs[1]() is R:
+            return cache["value"]
     value = (pad_cut_L(L, seq) @ R).to(BF16).contiguous()
     if cache is not None:
-        cache["key"], cache["value"] = key, value
+        import weakref
+        cache["key"], cache["value"], cache["refs"] = key, value, (weakref.ref(L), weakref.ref(R))
     return value
 
 
