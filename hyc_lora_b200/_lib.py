@@ -13,6 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libhyc_b200.so")
 
 HYC_OK = 0
+HYC_ERR_SHAPE = -2
 HYC_F32, HYC_BF16 = 0, 1
 HYC_MODE_R, HYC_MODE_N = 0, 1
 HYC_SCALE_TENSOR, HYC_SCALE_CHANNEL, HYC_SCALE_TOKEN = 0, 1, 2
@@ -90,6 +91,8 @@ SYMBOLS = {
     "hyc_compress": (C.c_int, [C.POINTER(HycDense), C.POINTER(HycPacked), C.c_void_p]),
     "hyc_decompress": (C.c_int, [C.POINTER(HycPacked), C.POINTER(HycDense), C.c_void_p]),
     "hyc_norm_compress": (C.c_int, [C.POINTER(HycDense), C.POINTER(HycNormFwd), C.POINTER(HycPacked), C.c_void_p]),
+    "hyc_norm_compress2": (C.c_int, [C.POINTER(HycDense), C.POINTER(HycNormFwd), C.POINTER(HycPacked), C.POINTER(HycPacked),
+                                     C.c_void_p]),
     "hyc_norm_bwd_partial_rows": (C.c_int, []),
     "hyc_norm_bwd": (C.c_int, [C.POINTER(HycPacked), C.POINTER(HycNormBwdArgs), C.c_void_p]),
     "hyc_act_bwd": (C.c_int, [C.c_int, C.POINTER(HycPacked), C.POINTER(HycPacked), C.c_void_p, C.c_int,

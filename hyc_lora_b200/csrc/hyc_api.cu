@@ -14,7 +14,8 @@ std::atomic<unsigned long long> g_launch_count{0};
 long long g_debug_wait_cycles = 0;
 unsigned int g_debug_tx_pad = 0;
 
-static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, cudaStream_t stream) {
+static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, cudaStream_t stream,
+                   const hyc_packed* out_y = nullptr) {
   const int empty = packed_is_empty(out);
   if (empty) return empty < 0 ? empty : HYC_OK;
   int rc = check_packed(out, true);
@@ -30,6 +31,7 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
   }
   if (out->rows == 0) return HYC_OK;
   const int es = x->dtype == HYC_BF16 ? 2 : 4;
+  if (out_y && out->mode != HYC_MODE_N) return HYC_ERR_SHAPE;
   if (out->mode == HYC_MODE_R) {
     // bf16 rows of up to 4096 channels: one warp per row
     const RWarpPlan rw = plan_r_warp(out, x, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER);
@@ -75,11 +77,14 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
   if (out->mode == HYC_MODE_N) {
     // rows of up to 4096 bf16 channels: one warp per row, no CTA barrier in the row loop
     static const bool warp_off = getenv("HYC_FWD_WARP") && getenv("HYC_FWD_WARP")[0] == '0';
-    const WarpPlan wp = warp_off ? WarpPlan{} : plan_warp_fwd(out, x, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER);
+    const WarpPlan wp = warp_off ? WarpPlan{} : plan_warp_fwd(out, x, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER, out_y);
+    if (out_y && !wp.ok) return HYC_ERR_SHAPE;     // the two-record variant exists on the warp-per-row kernel only
     if (wp.ok) {
       WarpFwdArgs wa;
       memset(&wa, 0, sizeof(wa));
       wa.p = to_dev(out);
+      if (out_y) wa.p2 = to_dev(out_y);
+      wa.off_chan2 = wp.off_chan2;
       wa.x = static_cast<const __nv_bfloat16*>(x->base);
       wa.row_stride = x->row_stride;
       if (norm) {
@@ -194,6 +199,14 @@ int hyc_compress(const hyc_dense* x, const hyc_packed* out, void* stream) {
 int hyc_norm_compress(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, void* stream) {
   if (!norm) return HYC_ERR_NULL;
   return run_fwd(x, norm, out, static_cast<cudaStream_t>(stream));
+}
+
+int hyc_norm_compress2(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out_x, const hyc_packed* out_y,
+                       void* stream) {
+  if (!norm || !out_y) return HYC_ERR_NULL;
+  int rc = check_packed(out_y, true);
+  if (rc) return rc;
+  return run_fwd(x, norm, out_x, static_cast<cudaStream_t>(stream), out_y);
 }
 
 }  // extern "C"

@@ -26,6 +26,7 @@ constexpr int kWarpOutPerLane = 4;          // outlier channels a lane looks aft
 
 struct WarpFwdArgs {
   PackedDev p;
+  PackedDev p2;          // two-record variant: the record of the norm output
   const __nv_bfloat16* x;
   long long row_stride;  // elements
   int kind;
@@ -36,7 +37,7 @@ struct WarpFwdArgs {
   __nv_bfloat16* y;
   float* rstd;
   float* mean;
-  uint32_t off_chan, off_wsm, off_bsm, off_slots, slot_bytes;
+  uint32_t off_chan, off_chan2, off_wsm, off_bsm, off_slots, slot_bytes;
   long long wait_cycles;
 };
 
@@ -91,69 +92,29 @@ __device__ __forceinline__ void group_scales(float (&v)[NG], float* scales_row, 
   for (int r = 0; r < NG; ++r) v[r] = __shfl_sync(0xffffffffu, inv, (lane & 16) | (r & 15));
 }
 
-// NK: 0 compress only, 1 RMSNorm (plain or Gemma), 2 LayerNorm;  NG: 16-byte register groups per lane
-// (units per lane x segments)
-template <int BITS, int NK, int NG, bool GROUP>
-__global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_n_warp_kernel(const __grid_constant__ WarpFwdArgs a) {
+// One row of the walk above, staged in `xs`: outlier channels, statistics, norm output, codes.
+// `next_src`: the row to bring into the slot once this one is in registers (nullptr: none).  TO_SLOT (the
+// first stage of the two-record variant): the slot is not handed back; instead the norm output, complete
+// with its outlier channels, takes the row's place in it, for a second call that compresses it.
+template <int BITS, int NK, int NG, bool GROUP, bool TO_SLOT>
+__device__ __forceinline__ void warp_row_plain(const WarpFwdArgs& a, const PackedDev& p, const int (&oc)[kWarpOutPerLane],
+                                               __nv_bfloat16* xs, uint64_t* bar, long long row,
+                                               const __nv_bfloat16* next_src, const float* wsm, const float* bsm) {
   using C = CodeTraits<BITS>;
   constexpr int NSEG = C::kSeg;
   constexpr int UPL = NG / NSEG;
   constexpr bool NORM = NK != 0;
   constexpr bool ln = NK == 2;
-  static_assert(UPL >= 1 && UPL * NSEG == NG, "register groups must cover whole units");
-  extern __shared__ __align__(128) unsigned char smem[];
-  const PackedDev& p = a.p;
   const int D = p.cols;
   const int segw = D / NSEG;
   const int U = segw >> 3;
   const int k = p.n_channels;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
   const int G = GROUP ? (D >> 7) : 1;
   const float qmax = static_cast<float>(C::kHi);
   const float inv_d = 1.0f / static_cast<float>(D);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-  int* chan = reinterpret_cast<int*>(smem + a.off_chan);
-  float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
-  float* bsm = reinterpret_cast<float*>(smem + a.off_bsm);
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem + a.off_slots + static_cast<size_t>(warp) * a.slot_bytes);
-  uint64_t* bar = &bars[warp];
   const uint32_t row_bytes = static_cast<uint32_t>(D) * 2u;
-  const long long rows = p.rows, stride = static_cast<long long>(gridDim.x) * W;
-  long long row = static_cast<long long>(blockIdx.x) * W + warp;
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < W; ++i) mbar_init(&bars[i], 1);
-    fence_barrier_init();
-  }
-  __syncthreads();
-  // the first row of every warp starts travelling before the per-CTA tables are set up
-  if (lane == 0 && row < rows) {
-    mbar_expect_tx(bar, row_bytes);
-    bulk_g2s(xs, a.x + row * a.row_stride, row_bytes, bar);
-  }
-  for (int j = threadIdx.x; j < k; j += blockDim.x) chan[j] = p.channels[j];
-  if (NORM) {
-    const float plus = a.kind == HYC_NORM_RMS_GEMMA ? 1.f : 0.f;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-      wsm[split_index(c, D)] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[c])
-                                             : static_cast<const float*>(a.weight)[c]) + plus;
-      if (ln)
-        bsm[split_index(c, D)] = a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[c])
-                                              : static_cast<const float*>(a.bias)[c];
-    }
-  }
-  __syncthreads();
-  // the outlier channels this lane looks after (-1: none)
-  int oc[kWarpOutPerLane];
-#pragma unroll
-  for (int q = 0; q < kWarpOutPerLane; ++q) oc[q] = (lane + 32 * q) < k ? chan[lane + 32 * q] : -1;
-
-  uint32_t ph = 0;
-  for (; row < rows; row += stride, ph ^= 1u) {
-    if (!mbar_wait_bounded(bar, ph, a.wait_cycles)) {
-      // the only copy this warp has in flight is the one it gave up on
-      if (lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
-      return;
-    }
+  {
     // ---- outlier channels: keep the original, write it out, zero it in the staged row
     float ov[kWarpOutPerLane];
 #pragma unroll
@@ -176,11 +137,10 @@ __global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_
     }
     __syncwarp();
     // every lane has what it needs: hand the slot back to the copy engine
-    const long long next = row + stride;
-    if (lane == 0 && next < rows) {
+    if (!TO_SLOT && lane == 0 && next_src) {
       fence_proxy_async();
       mbar_expect_tx(bar, row_bytes);
-      bulk_g2s(xs, a.x + next * a.row_stride, row_bytes, bar);
+      bulk_g2s(xs, next_src, row_bytes, bar);
     }
     // ---- statistics
     float mean = 0.f;
@@ -275,6 +235,7 @@ __global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_
               for (int e = 0; e < 8; ++e) y[e] = f[e] * rstd * wv[e];
             }
             store8<__nv_bfloat16>(yrow, col, y);
+            if (TO_SLOT) store8<__nv_bfloat16>(xs, col, y);    // the norm output takes the row's place in the slot
           }
           acc.add(f, GROUP ? ginv[iu * NSEG + s] : inv_row, s);
         }
@@ -294,33 +255,31 @@ __global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_
           const int cs = split_index(oc[q], D);
           const float y = ln ? ((ov[q] - mean) * rstd * wsm[cs] + bsm[cs]) : (ov[q] * rstd * wsm[cs]);
           yrow[oc[q]] = __float2bfloat16_rn(y);
+          if (TO_SLOT) xs[oc[q]] = __float2bfloat16_rn(y);
         }
       }
     }
   }
 }
 
-// The same walk with a block Walsh-Hadamard rotation (block <= 256) before quantisation.  A warp holds 256
-// consecutive channels of every segment (lane l: channels 8l..8l+7 of the window), so the butterflies of
-// strides 1, 2, 4 run inside a lane and those of strides 8..128 through shuffles (rotate_group).  The row
-// statistics of the norm are taken in a first pass over the staged row; the second pass writes the norm
-// output of a group, rotates the group in place and keeps it in registers as fp32 (per-token scale: the
-// row's absmax has to be known before any code can be written) or quantises it at once (group scales: a
-// group's absmax lives in one half-warp).  The slot is handed back after the second pass.
-template <int BITS, int NK, int NG, bool GROUP>
-__global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(const __grid_constant__ WarpFwdArgs a) {
+// NK: 0 compress only, 1 RMSNorm (plain or Gemma), 2 LayerNorm;  NG: 16-byte register groups per lane
+// (units per lane x segments)
+// DUAL: a second record (a.p2, with its own outlier channels) takes the compressed norm OUTPUT: the sites
+// behind a norm save that tensor, and this way it is compressed in the pass that produces it.
+template <int BITS, int NK, int NG, bool GROUP, bool DUAL>
+__global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_n_warp_kernel(const __grid_constant__ WarpFwdArgs a) {
   using C = CodeTraits<BITS>;
   constexpr int NSEG = C::kSeg;
   constexpr int UPL = NG / NSEG;
   constexpr bool NORM = NK != 0;
   constexpr bool ln = NK == 2;
+  static_assert(UPL >= 1 && UPL * NSEG == NG, "register groups must cover whole units");
   extern __shared__ __align__(128) unsigned char smem[];
   const PackedDev& p = a.p;
   const int D = p.cols;
   const int segw = D / NSEG;
-  const int U = segw >> 3;                  // a multiple of 32 here: a warp is wholly inside or outside a unit round
+  const int U = segw >> 3;
   const int k = p.n_channels;
-  const int nrot = p.rotate;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
   const int G = GROUP ? (D >> 7) : 1;
   const float qmax = static_cast<float>(C::kHi);
@@ -329,27 +288,25 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
   int* chan = reinterpret_cast<int*>(smem + a.off_chan);
   float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
   float* bsm = reinterpret_cast<float*>(smem + a.off_bsm);
-  // two slots per warp: the row after this one is already travelling while this one is rotated
-  unsigned char* slots = smem + a.off_slots + static_cast<size_t>(warp) * 2u * a.slot_bytes;
-  uint64_t* bar2 = &bars[2 * warp];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem + a.off_slots + static_cast<size_t>(warp) * a.slot_bytes);
+  uint64_t* bar = &bars[warp];
   const uint32_t row_bytes = static_cast<uint32_t>(D) * 2u;
   const long long rows = p.rows, stride = static_cast<long long>(gridDim.x) * W;
   long long row = static_cast<long long>(blockIdx.x) * W + warp;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2 * W; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < W; ++i) mbar_init(&bars[i], 1);
     fence_barrier_init();
   }
   __syncthreads();
-  if (lane == 0) {
-    for (int s = 0; s < 2; ++s) {
-      const long long r = row + s * stride;
-      if (r < rows) {
-        mbar_expect_tx(&bar2[s], row_bytes);
-        bulk_g2s(slots + s * a.slot_bytes, a.x + r * a.row_stride, row_bytes, &bar2[s]);
-      }
-    }
+  // the first row of every warp starts travelling before the per-CTA tables are set up
+  if (lane == 0 && row < rows) {
+    mbar_expect_tx(bar, row_bytes);
+    bulk_g2s(xs, a.x + row * a.row_stride, row_bytes, bar);
   }
   for (int j = threadIdx.x; j < k; j += blockDim.x) chan[j] = p.channels[j];
+  int* chan2 = reinterpret_cast<int*>(smem + a.off_chan2);
+  if (DUAL)
+    for (int j = threadIdx.x; j < a.p2.n_channels; j += blockDim.x) chan2[j] = a.p2.channels[j];
   if (NORM) {
     const float plus = a.kind == HYC_NORM_RMS_GEMMA ? 1.f : 0.f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
@@ -361,21 +318,56 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
     }
   }
   __syncthreads();
+  // the outlier channels this lane looks after (-1: none)
   int oc[kWarpOutPerLane];
 #pragma unroll
   for (int q = 0; q < kWarpOutPerLane; ++q) oc[q] = (lane + 32 * q) < k ? chan[lane + 32 * q] : -1;
+  int oc2[kWarpOutPerLane];
+#pragma unroll
+  for (int q = 0; q < kWarpOutPerLane; ++q) oc2[q] = (DUAL && (lane + 32 * q) < a.p2.n_channels) ? chan2[lane + 32 * q] : -1;
 
   uint32_t ph = 0;
-  int st = 0;
-  for (; row < rows; row += stride) {
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(slots + st * a.slot_bytes);
-    uint64_t* bar = &bar2[st];
+  for (; row < rows; row += stride, ph ^= 1u) {
     if (!mbar_wait_bounded(bar, ph, a.wait_cycles)) {
+      // the only copy this warp has in flight is the one it gave up on
       if (lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
-      // the copy into the other slot may still be in flight: give it a bounded chance to land
-      if (row + stride < rows) (void)mbar_wait_bounded(&bar2[st ^ 1], st ? ph ^ 1u : ph, a.wait_cycles);
       return;
     }
+    const long long next = row + stride;
+    const __nv_bfloat16* next_src = next < rows ? a.x + next * a.row_stride : nullptr;
+    if (DUAL) {
+      warp_row_plain<BITS, NK, NG, GROUP, true>(a, p, oc, xs, bar, row, nullptr, wsm, bsm);
+      __syncwarp();
+      warp_row_plain<BITS, 0, NG, GROUP, false>(a, a.p2, oc2, xs, bar, row, next_src, wsm, bsm);
+    } else {
+      warp_row_plain<BITS, NK, NG, GROUP, false>(a, p, oc, xs, bar, row, next_src, wsm, bsm);
+    }
+  }
+}
+
+// One row of the rotating walk, staged in `xs` (see the kernel below).  `next_src`: the row to bring into the
+// slot after the second pass (nullptr: none).  TO_SLOT as in warp_row_plain: the slot is kept and the norm
+// output takes the row's place in it.
+template <int BITS, int NK, int NG, bool GROUP, bool TO_SLOT>
+__device__ __forceinline__ void warp_row_rot(const WarpFwdArgs& a, const PackedDev& p, const int (&oc)[kWarpOutPerLane],
+                                             __nv_bfloat16* xs, uint64_t* bar, long long row,
+                                             const __nv_bfloat16* next_src, const float* wsm, const float* bsm) {
+  using C = CodeTraits<BITS>;
+  constexpr int NSEG = C::kSeg;
+  constexpr int UPL = NG / NSEG;
+  constexpr bool NORM = NK != 0;
+  constexpr bool ln = NK == 2;
+  const int D = p.cols;
+  const int segw = D / NSEG;
+  const int U = segw >> 3;                  // a multiple of 32 here: a warp is wholly inside or outside a unit round
+  const int k = p.n_channels;
+  const int nrot = p.rotate;
+  const int lane = threadIdx.x & 31;
+  const int G = GROUP ? (D >> 7) : 1;
+  const float qmax = static_cast<float>(C::kHi);
+  const float inv_d = 1.0f / static_cast<float>(D);
+  const uint32_t row_bytes = static_cast<uint32_t>(D) * 2u;
+  {
     float ov[kWarpOutPerLane];
 #pragma unroll
     for (int q = 0; q < kWarpOutPerLane; ++q) {
@@ -461,6 +453,7 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
             for (int e = 0; e < 8; ++e) y[e] = f[e] * rstd * wv[e];
           }
           store8<__nv_bfloat16>(yrow, col, y);
+          if (TO_SLOT) store8<__nv_bfloat16>(xs, col, y);      // the norm output takes the row's place in the slot
         }
         rotate_group(f, nrot, lane);
         float a8 = absmax8(f);
@@ -477,11 +470,10 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
       if (NORM && (iu & 1)) asm volatile("" ::: "memory");
     }
     __syncwarp();
-    const long long next = row + 2 * stride;
-    if (lane == 0 && next < rows) {
+    if (!TO_SLOT && lane == 0 && next_src) {
       fence_proxy_async();
       mbar_expect_tx(bar, row_bytes);
-      bulk_g2s(xs, a.x + next * a.row_stride, row_bytes, bar);
+      bulk_g2s(xs, next_src, row_bytes, bar);
     }
     float inv_row = 1.f;
     if constexpr (GROUP) {
@@ -507,8 +499,103 @@ __global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(cons
           const int cs = split_index(oc[q], D);
           const float y = ln ? ((ov[q] - mean) * rstd * wsm[cs] + bsm[cs]) : (ov[q] * rstd * wsm[cs]);
           yrow[oc[q]] = __float2bfloat16_rn(y);
+          if (TO_SLOT) xs[oc[q]] = __float2bfloat16_rn(y);
         }
       }
+    }
+  }
+}
+
+// The same walk with a block Walsh-Hadamard rotation (block <= 256) before quantisation.  A warp holds 256
+// consecutive channels of every segment (lane l: channels 8l..8l+7 of the window), so the butterflies of
+// strides 1, 2, 4 run inside a lane and those of strides 8..128 through shuffles (rotate_group).  The row
+// statistics of the norm are taken in a first pass over the staged row; the second pass writes the norm
+// output of a group, rotates the group in place and keeps it in registers as fp32 (per-token scale: the
+// row's absmax has to be known before any code can be written) or quantises it at once (group scales: a
+// group's absmax lives in one half-warp).  The slot is handed back after the second pass.
+template <int BITS, int NK, int NG, bool GROUP, bool DUAL>
+__global__ void __launch_bounds__(kWarpRotThreads, 1) fwd_n_warp_rot_kernel(const __grid_constant__ WarpFwdArgs a) {
+  using C = CodeTraits<BITS>;
+  constexpr int NSEG = C::kSeg;
+  constexpr int UPL = NG / NSEG;
+  constexpr bool NORM = NK != 0;
+  constexpr bool ln = NK == 2;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const PackedDev& p = a.p;
+  const int D = p.cols;
+  const int segw = D / NSEG;
+  const int U = segw >> 3;                  // a multiple of 32 here: a warp is wholly inside or outside a unit round
+  const int k = p.n_channels;
+  const int nrot = p.rotate;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+  const int G = GROUP ? (D >> 7) : 1;
+  const float qmax = static_cast<float>(C::kHi);
+  const float inv_d = 1.0f / static_cast<float>(D);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  int* chan = reinterpret_cast<int*>(smem + a.off_chan);
+  float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
+  float* bsm = reinterpret_cast<float*>(smem + a.off_bsm);
+  // two slots per warp: the row after this one is already travelling while this one is rotated
+  unsigned char* slots = smem + a.off_slots + static_cast<size_t>(warp) * 2u * a.slot_bytes;
+  uint64_t* bar2 = &bars[2 * warp];
+  const uint32_t row_bytes = static_cast<uint32_t>(D) * 2u;
+  const long long rows = p.rows, stride = static_cast<long long>(gridDim.x) * W;
+  long long row = static_cast<long long>(blockIdx.x) * W + warp;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2 * W; ++i) mbar_init(&bars[i], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (lane == 0) {
+    for (int s = 0; s < 2; ++s) {
+      const long long r = row + s * stride;
+      if (r < rows) {
+        mbar_expect_tx(&bar2[s], row_bytes);
+        bulk_g2s(slots + s * a.slot_bytes, a.x + r * a.row_stride, row_bytes, &bar2[s]);
+      }
+    }
+  }
+  for (int j = threadIdx.x; j < k; j += blockDim.x) chan[j] = p.channels[j];
+  int* chan2 = reinterpret_cast<int*>(smem + a.off_chan2);
+  if (DUAL)
+    for (int j = threadIdx.x; j < a.p2.n_channels; j += blockDim.x) chan2[j] = a.p2.channels[j];
+  if (NORM) {
+    const float plus = a.kind == HYC_NORM_RMS_GEMMA ? 1.f : 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+      wsm[split_index(c, D)] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[c])
+                                             : static_cast<const float*>(a.weight)[c]) + plus;
+      if (ln)
+        bsm[split_index(c, D)] = a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[c])
+                                              : static_cast<const float*>(a.bias)[c];
+    }
+  }
+  __syncthreads();
+  int oc[kWarpOutPerLane];
+#pragma unroll
+  for (int q = 0; q < kWarpOutPerLane; ++q) oc[q] = (lane + 32 * q) < k ? chan[lane + 32 * q] : -1;
+  int oc2[kWarpOutPerLane];
+#pragma unroll
+  for (int q = 0; q < kWarpOutPerLane; ++q) oc2[q] = (DUAL && (lane + 32 * q) < a.p2.n_channels) ? chan2[lane + 32 * q] : -1;
+
+  uint32_t ph = 0;
+  int st = 0;
+  for (; row < rows; row += stride) {
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(slots + st * a.slot_bytes);
+    uint64_t* bar = &bar2[st];
+    if (!mbar_wait_bounded(bar, ph, a.wait_cycles)) {
+      if (lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
+      // the copy into the other slot may still be in flight: give it a bounded chance to land
+      if (row + stride < rows) (void)mbar_wait_bounded(&bar2[st ^ 1], st ? ph ^ 1u : ph, a.wait_cycles);
+      return;
+    }
+    const long long next = row + 2 * stride;
+    const __nv_bfloat16* next_src = next < rows ? a.x + next * a.row_stride : nullptr;
+    if (DUAL) {
+      warp_row_rot<BITS, NK, NG, GROUP, true>(a, p, oc, xs, bar, row, nullptr, wsm, bsm);
+      __syncwarp();
+      warp_row_rot<BITS, 0, NG, GROUP, false>(a, a.p2, oc2, xs, bar, row, next_src, wsm, bsm);
+    } else {
+      warp_row_rot<BITS, NK, NG, GROUP, false>(a, p, oc, xs, bar, row, next_src, wsm, bsm);
     }
     if (st) ph ^= 1u;
     st ^= 1;
@@ -521,15 +608,24 @@ struct WarpPlan {
   bool ok;
   int ng;          // register groups per lane (instantiated: 2, 4, 8, 16)
   int warps, grid, threads;
-  bool rot;
+  bool rot, dual;
+  uint32_t off_chan2;
   uint32_t off_chan, off_wsm, off_bsm, off_slots, slot_bytes, total;
 };
 
 // bf16 rows in the plain layout, at most 16 register groups per lane and 128 outlier channels; a rotation
 // block of at most 256 channels that divides the segment width, with every lane of the warp in use
-inline WarpPlan plan_warp_fwd(const hyc_packed* q, const hyc_dense* x, bool norm, bool ln) {
+// `q2`: second record for the norm output (two-record variant), or nullptr; it must share the first record's
+// bit width, scale grouping and rotation
+inline WarpPlan plan_warp_fwd(const hyc_packed* q, const hyc_dense* x, bool norm, bool ln, const hyc_packed* q2 = nullptr) {
   WarpPlan w;
   memset(&w, 0, sizeof(w));
+  if (q2) {
+    if (!norm || q2->mode != HYC_MODE_N || q2->bits != q->bits || q2->group != q->group || q2->rotate != q->rotate ||
+        q2->cols != q->cols || q2->rows != q->rows || q2->n_channels > 32 * kWarpOutPerLane)
+      return w;
+    w.dual = true;
+  }
   if (q->mode != HYC_MODE_N || x->dtype != HYC_BF16 || x->chunks != 1) return w;
   if (q->rotate && (q->rotate > 256 || (q->cols / (8 / q->bits)) % 256 != 0)) return w;
   if (q->bits != 2 && q->bits != 4 && q->bits != 8) return w;
@@ -547,6 +643,7 @@ inline WarpPlan plan_warp_fwd(const hyc_packed* q, const hyc_dense* x, bool norm
   uint32_t off = 64 * 8;                                   // one mbarrier per warp
   auto take = [&](uint32_t bytes) { uint32_t o = off; off = align_up(off + bytes, 16); return o; };
   w.off_chan = take((q->n_channels > 0 ? q->n_channels : 1) * 4);
+  w.off_chan2 = take((q2 && q2->n_channels > 0 ? q2->n_channels : 1) * 4);
   if (norm) w.off_wsm = take(D * 4);
   if (ln) w.off_bsm = take(D * 4);
   off = align_up(off, 128);
@@ -572,12 +669,32 @@ int launch_fwd_warp_bits(const WarpFwdArgs& a, const WarpPlan& w, bool norm, cud
   {                                                                                             \
     if constexpr (NG >= 8 / BITS) {                                                             \
       if (w.rot) {                                                                              \
-        auto kern = fwd_n_warp_rot_kernel<BITS, NK, NG, GROUP>;                                 \
-        int rc = set_smem(kern, w.total);                                                       \
-        if (rc) return rc;                                                                      \
-        kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                        \
+        if (w.dual) {                                                                           \
+          if constexpr (NK != 0) {                                                              \
+            auto kern = fwd_n_warp_rot_kernel<BITS, NK, NG, GROUP, true>;                       \
+            int rc = set_smem(kern, w.total);                                                   \
+            if (rc) return rc;                                                                  \
+            kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                    \
+          } else {                                                                              \
+            return HYC_ERR_SHAPE;                                                               \
+          }                                                                                     \
+        } else {                                                                                \
+          auto kern = fwd_n_warp_rot_kernel<BITS, NK, NG, GROUP, false>;                        \
+          int rc = set_smem(kern, w.total);                                                     \
+          if (rc) return rc;                                                                    \
+          kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                      \
+        }                                                                                       \
+      } else if (w.dual) {                                                                      \
+        if constexpr (NK != 0) {                                                                \
+          auto kern = fwd_n_warp_kernel<BITS, NK, NG, GROUP, true>;                             \
+          int rc = set_smem(kern, w.total);                                                     \
+          if (rc) return rc;                                                                    \
+          kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                      \
+        } else {                                                                                \
+          return HYC_ERR_SHAPE;                                                                 \
+        }                                                                                       \
       } else {                                                                                  \
-        auto kern = fwd_n_warp_kernel<BITS, NK, NG, GROUP>;                                     \
+        auto kern = fwd_n_warp_kernel<BITS, NK, NG, GROUP, false>;                              \
         int rc = set_smem(kern, w.total);                                                       \
         if (rc) return rc;                                                                      \
         kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                        \

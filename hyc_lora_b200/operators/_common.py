@@ -3,6 +3,7 @@ mean of the reference, the options of the channel mode and the one helper that
 compresses an activation for backward in either mode."""
 from __future__ import annotations
 
+import weakref
 from typing import Optional
 
 import torch
@@ -39,6 +40,10 @@ class SiteOptions:
         self.fit_rotate = fit_rotate
         self.calib = cf.ChannelCalibration(outlier_ratio)
         self._dummy = None
+        # norm sites only: the format and calibration of the site that saves this norm's OUTPUT (learnt
+        # during calibration), and the record of that output the last forward call made beside its own
+        self.output_format = None
+        self.pending_output = None
 
     @property
     def channel(self) -> bool:
@@ -89,17 +94,72 @@ def _shared_lookup(x, key, opts, iteration):
             if iteration < 2:
                 opts.calib.score, opts.calib.channels = calib.score, calib.channels
                 return rec
-            if opts.calib.channels is not None and opts.calib.channels is calib.channels:
+            mine = opts.calib.channels
+            if mine is not None and mine is calib.channels:
                 return rec
+            # calibrations restored from a checkpoint hold equal channel lists in separate tensors: compare
+            # once (one read of the device per site) and adopt the producer's tensor when they agree
+            if (mine is not None and calib.channels is not None and getattr(opts.calib, "_compared", None) is not
+                    calib.channels):
+                opts.calib._compared = calib.channels
+                if mine.shape == calib.channels.shape and bool(torch.equal(mine, calib.channels)):
+                    opts.calib.channels = calib.channels
+                    return rec
     return None
 
 
-def _shared_store(x, key, rec, opts):
+def _shared_store(x, key, rec, calib):
     if not SHARE_SITES:
         return
-    import weakref
-    _shared.insert(0, (weakref.ref(x), x._version, key, rec, opts.calib))
+    _shared.insert(0, (weakref.ref(x), x._version, key, rec, calib))
     del _shared[2:]
+
+
+# ---------------------------------------------------------------------------------------------
+# The record of a norm's OUTPUT from the norm's own pass (channel mode).  The LoRA-A linears behind a
+# norm save the norm output; the fused norm kernel has that row in shared memory already and can emit
+# its record beside the record of the norm input.  Nothing tells a norm module who reads its output, so
+# it is learnt at run time: while a norm knows no reader, its module notes the tensor object it
+# returned, and the first site that is handed that very object (and has to compress it) leaves its
+# format and its calibration object with the norm's options.  From the first steady-state call on, the
+# norm's forward passes that site's frozen channels to the kernel and publishes the second record
+# through the table above, where the sites behind the norm find it.
+# ---------------------------------------------------------------------------------------------
+_last_norm_output = None     # (weakref to the tensor, version, options of the norm site)
+
+
+def _offer_to_norm(x, bits, rotate, opts):
+    """Called by a site that is about to compress ``x`` itself."""
+    global _last_norm_output
+    if _last_norm_output is None:
+        return
+    ref, version, norm_opts = _last_norm_output
+    if ref() is x and version == x._version:
+        norm_opts.output_format = (bits, opts.group_size, rotate, opts.calib)
+        _last_norm_output = None
+
+
+def norm_output_ready(result, opts, iteration):
+    """Called by a norm module with the tensor its Function returned."""
+    global _last_norm_output
+    if not SHARE_SITES:
+        return
+    rec, opts.pending_output = opts.pending_output, None
+    if rec is not None:
+        bits, group, rotate, calib = opts.output_format
+        _shared_store(result, (bits, group, rotate, calib.outlier_ratio, False), rec, calib)
+    elif opts.output_format is None:
+        _last_norm_output = (weakref.ref(result), result._version, opts)
+
+
+def _output_request(opts, iteration):
+    """What a norm site asks ``compress_n`` to emit for its output, or None."""
+    if not SHARE_SITES or iteration < 2 or opts.output_format is None:
+        return None
+    bits, group, rotate, calib = opts.output_format
+    if calib.channels is None:
+        return None
+    return dict(channels=calib.channels, bits=bits, group=group, rotate=rotate)
 
 
 @torch.no_grad()
@@ -118,12 +178,16 @@ def compress_site(x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, method, 
             shared = _shared_lookup(x, key, opts, iteration)
             if shared is not None:
                 return shared, stats, None
+            _offer_to_norm(x, sub_outlier_bit, rotate, opts)
         channels = opts.calib.channels_for(x, iteration)
-        res = cf.channel_compress(x, channels, sub_outlier_bit, opts.group_size, rotate, norm=norm)
         if norm is None:
-            _shared_store(x, key, res, opts)
+            res = cf.channel_compress(x, channels, sub_outlier_bit, opts.group_size, rotate)
+            _shared_store(x, key, res, opts.calib)
             return res, stats, None
-        return res[0], stats, res[1:]
+        also = _output_request(opts, iteration)
+        res = cf.channel_compress(x, channels, sub_outlier_bit, opts.group_size, rotate, norm=norm, also_output=also)
+        opts.pending_output = res[4] if also is not None else None
+        return res[0], stats, res[1:4]
     if iteration < 2:
         outlier, L, R, scale = cf.get_statistics(x, iteration, outlier_ratio, sub_outlier_ratio, sub_outlier_bit,
                                                  method, rank)

@@ -9,7 +9,7 @@ lock-free partials for the weight gradient."""
 import torch
 
 from .. import packed as _pk
-from ._common import SiteOptions, compress_site, site_options, update_static
+from ._common import SiteOptions, compress_site, norm_output_ready, site_options, update_static
 from .compress_function import StaticList
 
 
@@ -74,6 +74,9 @@ def make_norm(kind: str, func_name: str, module_name: str, doc: str):
                 self.static_value, self.site)
             if not self.site.channel:
                 update_static(self.static_value, self.iteration, outlier, L, scale, R)
+            else:
+                # the sites behind this norm save ``result``: hand them the record made in the same pass
+                norm_output_ready(result, self.site, self.iteration)
             self.iteration += 1
             return result
 

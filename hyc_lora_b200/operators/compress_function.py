@@ -238,6 +238,6 @@ class ChannelCalibration:
 
 @torch.no_grad()
 def channel_compress(x: torch.Tensor, channels, bits: int, group_size: int = 0, rotate: int = 0,
-                     norm: Optional[dict] = None):
+                     norm: Optional[dict] = None, also_output: Optional[dict] = None):
     """Channel-mode compression; see :func:`hyc_lora_b200.packed.compress_n`."""
-    return _pk.compress_n(x, channels, bits, group_size, rotate, norm=norm)
+    return _pk.compress_n(x, channels, bits, group_size, rotate, norm=norm, also_output=also_output)

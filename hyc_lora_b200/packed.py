@@ -374,17 +374,34 @@ def compress_r(x: torch.Tensor, thr: torch.Tensor, scale: torch.Tensor, bits: in
 
 
 def compress_n(x: torch.Tensor, channels: Optional[torch.Tensor], bits: int, group: int = 0, rotate: int = 0,
-               norm: Optional[dict] = None):
+               norm: Optional[dict] = None, also_output: Optional[dict] = None):
     """North-star-mode compression (channel outliers, dynamic absmax scales,
-    optional block Hadamard rotation)."""
+    optional block Hadamard rotation).
+
+    ``also_output`` (with ``norm`` only; keys ``channels``, ``bits``, ``group``, ``rotate``): the norm OUTPUT is
+    compressed in the same pass into a second record, for the sites behind the norm that save it.  Returns
+    ``(packed, y, rstd, mean, packed_y)`` then; ``packed_y`` is None when the library does not take the pair
+    (the caller compresses ``y`` with a call of its own)."""
     _require_cuda(x, channels)
     cols = x.shape[-1] if x.dim() != 4 else x.shape[1] * x.shape[3]
     d, rows, seq, shape, keep = _dense_record(x, cols)
     p = _new_n(keep, rows, cols, seq, shape, channels, bits, group, rotate)
-    return _run_fwd(d, keep, p, norm)
+    if also_output is None or norm is None:
+        return _run_fwd(d, keep, p, norm)
+    p2 = None
+    o = also_output
+    # the library builds the pair for bf16 rows of one format that a warp can hold (rotation blocks of at most 256
+    # channels that tile a packed segment); anything else is not asked for
+    fits = cols <= 4096 and (rotate == 0 or (rotate <= 256 and (cols // (8 // bits)) % 256 == 0))
+    if (o["bits"] == bits and o.get("group", 0) == group and o.get("rotate", 0) == rotate and keep.dim() != 4
+            and keep.dtype == torch.bfloat16 and fits):
+        p2 = _new_n(keep, rows, cols, seq, shape, o["channels"], bits, group, rotate)
+    if p2 is None:
+        return (*_run_fwd(d, keep, p, norm), None)
+    return _run_fwd(d, keep, p, norm, p2)
 
 
-def _run_fwd(d, x, p: Packed, norm):
+def _run_fwd(d, x, p: Packed, norm, p2: Optional[Packed] = None):
     rec = p.record()
     if norm is None:
         check(lib.hyc_compress(C.byref(d), C.byref(rec), _stream()), "hyc_compress")
@@ -403,6 +420,16 @@ def _run_fwd(d, x, p: Packed, norm):
     rstd = torch.empty(p.rows, dtype=torch.float32, device=x.device)
     mean = torch.empty(p.rows, dtype=torch.float32, device=x.device) if kind == "ln" else None
     n.y, n.rstd, n.mean = y.data_ptr(), rstd.data_ptr(), (mean.data_ptr() if mean is not None else None)
+    if p2 is not None:
+        rec2 = p2.record()
+        rc = lib.hyc_norm_compress2(C.byref(d), C.byref(n), C.byref(rec), C.byref(rec2), _stream())
+        if rc == 0:
+            return p, y, rstd, mean, p2
+        if rc != _lib.HYC_ERR_SHAPE:
+            check(rc, "hyc_norm_compress2")
+        # the pair is not taken (row too wide, rotation, ...): one record now, the caller makes the other
+        check(lib.hyc_norm_compress(C.byref(d), C.byref(n), C.byref(rec), _stream()), "hyc_norm_compress")
+        return p, y, rstd, mean, None
     check(lib.hyc_norm_compress(C.byref(d), C.byref(n), C.byref(rec), _stream()), "hyc_norm_compress")
     return p, y, rstd, mean
 

@@ -164,6 +164,16 @@ typedef struct {
 } hyc_norm_fwd;
 int hyc_norm_compress(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, void* stream);
 
+/* The same with a second record, `out_y`, that takes the compressed norm OUTPUT y in the same pass.  In the
+ * reference every LoRA-A linear behind a norm compresses the norm output again on its own
+ * (efficient_linear.py:46 after efficient_rmsnorm.py:201: three times for q/k/v, twice for gate/up); here the
+ * kernel that produces y compresses it once, with `out_y`'s own outlier channels.  Channel mode only, bf16
+ * rows of up to 4096 channels in the plain layout; both records must share bits, group and rotation.
+ * HYC_ERR_SHAPE means "this pair is not taken": make the two calls (hyc_norm_compress, then hyc_compress
+ * on y) instead. */
+int hyc_norm_compress2(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out_x, const hyc_packed* out_y,
+                       void* stream);
+
 /* Decompress + norm backward.  Replaces the decompress chain followed by
  * _rms_norm_bwd_dx_fused/_dwdb or _layer_norm_bwd_dx_fused/_dwdb
  * (efficient_rmsnorm.py:214-269, efficient_layernorm.py:275-335).

@@ -655,6 +655,98 @@ def test_kernels_write_nothing_outside_their_outputs(pk, d, bits, rotate, mode):
     arena.check()
 
 
+@pytest.mark.parametrize("kind,d,bits,group,rotate,rows", [
+    ("rms", 4096, 4, 0, 0, 3001), ("rms", 4096, 2, 128, 0, 517), ("rms_gemma", 2048, 8, 0, 0, 700),
+    ("ln", 768, 4, 0, 0, 5003), ("rms", 2816, 4, 128, 0, 333), ("ln", 3072, 2, 0, 0, 129), ("rms", 1024, 4, 0, 0, 1),
+    # rotated codes (the kernel that keeps the rotated row in registers)
+    ("rms", 4096, 4, 0, 256, 3001), ("rms", 4096, 2, 128, 256, 517), ("ln", 1024, 4, 0, 64, 5003),
+    ("rms_gemma", 2048, 8, 0, 256, 700), ("rms", 3072, 4, 128, 16, 333), ("ln", 2048, 2, 0, 256, 129)])
+def test_norm_output_record_from_the_same_pass(pk, kind, d, bits, group, rotate, rows):
+    """``hyc_norm_compress2``: the record of the norm OUTPUT that the pass emits beside the record of its
+    input is, bit for bit, the record a separate ``hyc_compress`` of that output makes; the input record,
+    the output and the row statistics are those of ``hyc_norm_compress``; nothing else is written."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=torch.bfloat16, salt=d + bits)
+    xd = x.to(DEV)
+    w = synthetic.norm_weight(d, 0.1, dtype=torch.bfloat16).to(DEV)
+    b = (0.05 * torch.randn(d, generator=torch.Generator().manual_seed(d))).to(torch.bfloat16).to(DEV)
+    k = oc.n_outlier_count(d, 0.01)
+    ch_x = pk.select_channels(pk.channel_absmax(xd), k)
+    norm = dict(kind=kind, weight=w, bias=b, eps=1e-5)
+    p1, y1, rstd1, mean1 = pk.compress_n(xd, ch_x, bits, group, rotate, norm=norm)
+    # the consumer's outlier channels come from the norm output, not from its input
+    ch_y = pk.select_channels(pk.channel_absmax(y1), k)
+    want_y = pk.compress_n(y1, ch_y, bits, group, rotate)
+    px, y, rstd, mean, py = pk.compress_n(xd, ch_x, bits, group, rotate, norm=norm,
+                                          also_output=dict(channels=ch_y, bits=bits, group=group, rotate=rotate))
+    assert py is not None, "the pair was refused"
+    assert torch.equal(y, y1) and torch.equal(rstd, rstd1)
+    if kind == "ln":
+        assert torch.equal(mean, mean1)
+    for got, want in ((px, p1), (py, want_y)):
+        assert torch.equal(got.codes, want.codes)
+        assert torch.equal(got.scales, want.scales)
+        assert torch.equal(got.out_value, want.out_value)
+        assert int(got.status.item()) == 0
+    # against the CPU restatement, on the output the kernel wrote
+    o = oc.n_compress(y.cpu(), ch_y.cpu(), bits, group, rotate)
+    assert torch.equal(py.codes.cpu().view(torch.uint8), o.codes.view(torch.uint8))
+    assert torch.equal(py.scales.cpu(), o.scales) and torch.equal(py.out_value.cpu(), o.out_value)
+    # the same call with every output inside a guarded arena
+    arena = _Arena(rows * d * 8 + (1 << 20))
+    ax = _packed_n_in(arena, pk, rows, d, bits, group, rotate, ch_x)
+    ay = _packed_n_in(arena, pk, rows, d, bits, group, rotate, ch_y)
+    yy, rr = arena.take((rows, d), torch.bfloat16), arena.take((rows,), torch.float32)
+    mm = arena.take((rows,), torch.float32)
+    n = _lib.HycNormFwd()
+    n.kind, n.eps = pk._NORM_KIND[kind], 1e-5
+    n.weight, n.bias, n.param_dtype = w.data_ptr(), (b.data_ptr() if kind == "ln" else None), _lib.HYC_BF16
+    n.y, n.rstd, n.mean = yy.data_ptr(), rr.data_ptr(), (mm.data_ptr() if kind == "ln" else None)
+    rx, ry, dn = ax.record(), ay.record(), _dense(xd, d)
+    _lib.check(_lib.lib.hyc_norm_compress2(C.byref(dn), C.byref(n), C.byref(rx), C.byref(ry), pk._stream()),
+               "hyc_norm_compress2")
+    torch.cuda.synchronize()
+    assert torch.equal(ay.codes, want_y.codes) and torch.equal(ax.codes, p1.codes) and torch.equal(yy, y1)
+    if kind != "ln":
+        assert bool((mm.view(torch.uint8) == _Arena.FILL).all())
+    arena.check()
+
+
+def test_norm_output_record_is_refused_where_the_pair_is_not_built(pk):
+    """Records of two formats (rotation block, bits, scale grouping): the call answers HYC_ERR_SHAPE
+    and writes nothing; the wrapper then returns no second record and the first one as ever."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    d, rows = 1024, 64
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=torch.bfloat16, salt=3)
+    xd = x.to(DEV)
+    w = synthetic.norm_weight(d, 0.1, dtype=torch.bfloat16).to(DEV)
+    ch = pk.select_channels(pk.channel_absmax(xd), 10)
+    norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
+    p1, y1, _, _ = pk.compress_n(xd, ch, 4, 0, 256, norm=norm)
+    px, y, _, _, py = pk.compress_n(xd, ch, 4, 0, 256, norm=norm, also_output=dict(channels=ch, bits=4, group=0, rotate=64))
+    assert py is None and torch.equal(px.codes, p1.codes) and torch.equal(y, y1)
+    px, y, _, _, py = pk.compress_n(xd, ch, 4, 0, 0, norm=norm, also_output=dict(channels=ch, bits=2, group=0, rotate=0))
+    assert py is None
+    for fmt_x, fmt_y in (((4, 0, 256), (4, 0, 64)), ((4, 0, 0), (2, 0, 0)), ((4, 0, 0), (4, 128, 0))):
+        arena = _Arena(rows * d * 8 + (1 << 20))
+        ax = _packed_n_in(arena, pk, rows, d, *fmt_x, ch)
+        ay = _packed_n_in(arena, pk, rows, d, *fmt_y, ch)
+        yy, rr = arena.take((rows, d), torch.bfloat16), arena.take((rows,), torch.float32)
+        arena.taken.clear()                      # nothing may be written at all
+        ax.status.view(torch.uint8).fill_(_Arena.FILL), ay.status.view(torch.uint8).fill_(_Arena.FILL)
+        n = _lib.HycNormFwd()
+        n.kind, n.eps = pk._NORM_KIND["rms"], 1e-5
+        n.weight, n.bias, n.param_dtype = w.data_ptr(), None, _lib.HYC_BF16
+        n.y, n.rstd, n.mean = yy.data_ptr(), rr.data_ptr(), None
+        rx, ry, dn = ax.record(), ay.record(), _dense(xd, d)
+        rc = _lib.lib.hyc_norm_compress2(C.byref(dn), C.byref(n), C.byref(rx), C.byref(ry), pk._stream())
+        assert rc == _lib.HYC_ERR_SHAPE
+        torch.cuda.synchronize()
+        arena.check()
+
+
 def test_config1_in_channel_mode_on_its_own_tensor(pk):
     """Configuration 1 as written: LayerNorm of the [8,128,768] fp32 activation, the top 1 % absmax
     channels (8 of 768 -- they must be the planted ones) kept in full precision, the rest INT4 with one

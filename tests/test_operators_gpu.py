@@ -329,6 +329,67 @@ def test_sites_saving_the_same_tensor_share_one_record():
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("kind,rotate", [("rms", 0), ("ln", 0), ("rms", 256)])
+def test_norm_emits_the_record_of_its_output_for_the_sites_behind_it(kind, rotate):
+    """A norm followed by three LoRA-A style linears (the q/k/v arrangement), all in channel mode
+    with and without rotation: from the first steady-state call on, one launch makes both the record of the
+    norm input and the record the three linears save, and every gradient is what it is when each
+    site compresses for itself."""
+    from hyc_lora_b200 import _lib
+    from hyc_lora_b200.operators import _common, compress_function as cf
+    from hyc_lora_b200.operators.efficient_layernorm import EfficientMemoryLayerNorm
+    from hyc_lora_b200.operators.efficient_linear import EfficientMemoryLinear
+    from hyc_lora_b200.operators.efficient_rmsnorm import EfficientMemoryRMSNorm
+    d, r = 1024, 16
+    x = _act(2, 40, d, salt=80, gain=20.0)
+    g = [_rand((2, 40, r), 81 + i) for i in range(3)]
+    ws = [(0.02 * _rand((r, d), 85 + i, torch.float32)).to(torch.bfloat16) for i in range(3)]
+    kw = dict(outlier_ratio=0.01, sub_outlier_ratio=1.0, sub_outlier_bit=4, rank=0, outlier_mode="channel", rotate=rotate)
+    grads, calls = {}, {}
+    for share in (True, False):
+        _common.SHARE_SITES = share
+        _common._shared.clear()
+        _common._last_norm_output = None
+        norm = (EfficientMemoryRMSNorm(d, bias=False, **kw) if kind == "rms" else EfficientMemoryLayerNorm(d, **kw))
+        norm = norm.to(DEV).to(torch.bfloat16)
+        norm.weight.data.copy_(1.0 + 0.1 * _rand((d,), 90, torch.float32))
+        lins = []
+        for w in ws:
+            lin = EfficientMemoryLinear(d, r, bias=False, **kw).to(DEV).to(torch.bfloat16)
+            lin.weight.data.copy_(w)
+            lins.append(lin)
+        count, real = [0], cf.channel_compress
+        def counted(*a, **k):
+            count[0] += 1
+            return real(*a, **k)
+        cf.channel_compress = counted
+        per_call = []
+        try:
+            for it in range(4):                      # two calibration calls, two steady-state calls
+                for m in lins + [norm]:
+                    m.weight.grad = None
+                xd = x.to(DEV).requires_grad_(True)
+                before, l0 = count[0], _lib.lib.hyc_launch_count()
+                h = norm(xd)
+                out = sum((lin(h) * gi.to(DEV)).sum() for lin, gi in zip(lins, g))
+                per_call.append((count[0] - before, _lib.lib.hyc_launch_count() - l0))
+                out.backward()
+        finally:
+            cf.channel_compress = real
+        calls[share] = per_call
+        grads[share] = [lin.weight.grad.clone() for lin in lins] + [xd.grad.clone(), norm.weight.grad.clone()]
+        if share:
+            assert norm.site.output_format is not None and norm.site.output_format[3] is lins[0].site.calib
+    _common.SHARE_SITES = True
+    # compress calls per forward: norm + one shared while calibrating, the norm's alone afterwards; 4 without sharing
+    assert [c for c, _ in calls[True]] == [2, 2, 1, 1]
+    assert [c for c, _ in calls[False]] == [4, 4, 4, 4]
+    # and in launches of the library: the steady-state forward is ONE launch
+    assert calls[True][3][1] == 1 and calls[False][3][1] == 4
+    for a, b in zip(grads[True], grads[False]):
+        assert torch.equal(a, b)
+
+
 def test_low_rank_site_and_calibration_state_roundtrip():
     """rank > 0: the randomized SVD differs between devices, so the check is against the exact
     derivative; then a second module restored from the first one's calibration state reproduces
