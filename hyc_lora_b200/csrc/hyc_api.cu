@@ -4,6 +4,7 @@
 
 #include "hyc_fwd_r_fast.cuh"
 #include "hyc_fwd_warp.cuh"
+#include "hyc_fwd_chunk.cuh"
 #include "hyc_fwd_r_warp.cuh"
 
 namespace hyc {
@@ -75,6 +76,28 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
     }
   }
   if (out->mode == HYC_MODE_N) {
+    // rotated rows whose segment is 32 chunks wide: one warp per row, a chunk of every segment per lane
+    static const bool chunk_off = getenv("HYC_FWD_CHUNK") && getenv("HYC_FWD_CHUNK")[0] == '0';
+    const ChunkPlan cp = chunk_off ? ChunkPlan{} : plan_chunk_fwd(out, x, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER, out_y);
+    CUtensorMap in_map, y_map;
+    if (cp.ok && row_tensor_map(&in_map, x->base, out->rows, out->cols, x->row_stride) &&
+        (norm ? row_tensor_map(&y_map, norm->y, out->rows, out->cols, x->row_stride) : (y_map = in_map, true))) {
+      ChunkFwdArgs ca;
+      memset(&ca, 0, sizeof(ca));
+      ca.p = to_dev(out);
+      if (out_y) ca.p2 = to_dev(out_y);
+      if (norm) {
+        ca.kind = norm->kind; ca.eps = norm->eps; ca.weight = norm->weight; ca.bias = norm->bias;
+        ca.param_bf16 = norm->param_dtype == HYC_BF16;
+        ca.rstd = norm->rstd; ca.mean = norm->mean;
+      }
+      ca.off_chan = cp.off_chan; ca.off_chan2 = cp.off_chan2; ca.off_wsm = cp.off_wsm; ca.off_bsm = cp.off_bsm;
+      ca.off_slots = cp.off_slots; ca.slot_bytes = cp.slot_bytes;
+      ca.wait_cycles = g_debug_wait_cycles > 0 ? g_debug_wait_cycles : kWaitCycles;
+      return out->bits == 2 ? launch_fwd_chunk_b2(ca, cp, norm != nullptr, in_map, y_map, stream)
+           : out->bits == 4 ? launch_fwd_chunk_b4(ca, cp, norm != nullptr, in_map, y_map, stream)
+                            : launch_fwd_chunk_b8(ca, cp, norm != nullptr, in_map, y_map, stream);
+    }
     // rows of up to 4096 bf16 channels: one warp per row, no CTA barrier in the row loop
     static const bool warp_off = getenv("HYC_FWD_WARP") && getenv("HYC_FWD_WARP")[0] == '0';
     const WarpPlan wp = warp_off ? WarpPlan{} : plan_warp_fwd(out, x, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER, out_y);

@@ -655,6 +655,55 @@ def test_kernels_write_nothing_outside_their_outputs(pk, d, bits, rotate, mode):
     arena.check()
 
 
+@pytest.mark.parametrize("d,bits,group,rotate,kind,rows", [
+    # the rotating kernel that gives a lane one chunk of every packed segment (segments of 32 chunks of 32, 64 or
+    # 128 channels); few rows take its 8-warp build, many rows the 12-warp one
+    (4096, 4, 0, 256, None, 300), (4096, 4, 0, 256, "rms", 4001), (4096, 4, 128, 256, "ln", 300),
+    (4096, 4, 0, 16, "rms", 300), (4096, 4, 0, 1024, None, 4001), (4096, 4, 128, 1024, "rms", 4001),
+    (2048, 4, 0, 256, "rms", 4001), (2048, 4, 128, 64, None, 300), (2048, 4, 0, 1024, "ln", 300),
+    (4096, 2, 0, 256, "rms", 300), (4096, 2, 128, 1024, None, 4001), (4096, 2, 0, 64, "ln", 4001),
+    (4096, 8, 0, 256, "rms", 4001), (4096, 8, 128, 4096, None, 300), (4096, 8, 128, 256, "ln", 300),
+    (2048, 8, 0, 1024, "rms", 300), (1024, 8, 128, 256, None, 4001), (1024, 8, 0, 1024, "rms", 300)])
+def test_rotating_forward_one_chunk_per_lane(pk, d, bits, group, rotate, kind, rows):
+    """Codes, scales and outlier values equal the oracle's bit for bit; the norm output and the row
+    statistics are the oracle's within the bf16 tolerance; nothing is written outside the outputs."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=torch.bfloat16, salt=d + bits + rotate)
+    x[rows // 2] = 0                                  # a dead row: scale 1, codes of zero
+    xd = x.to(DEV)
+    k = oc.n_outlier_count(d, 0.01)
+    ch = pk.select_channels(pk.channel_absmax(xd), k)
+    c = oc.n_compress(x, ch.cpu(), bits, group, rotate)
+    w = synthetic.norm_weight(d, 0.1, dtype=torch.bfloat16)
+    b = (0.05 * torch.randn(d, generator=torch.Generator().manual_seed(d))).to(torch.bfloat16)
+    arena = _Arena(rows * d * 4 + (1 << 20))
+    p = _packed_n_in(arena, pk, rows, d, bits, group, rotate, ch)
+    rec, dn = p.record(), _dense(xd, d)
+    if kind is None:
+        _lib.check(_lib.lib.hyc_compress(C.byref(dn), C.byref(rec), pk._stream()), "hyc_compress")
+    else:
+        y, rstd = arena.take((rows, d), torch.bfloat16), arena.take((rows,), torch.float32)
+        mean = arena.take((rows,), torch.float32)
+        wd, bd = w.to(DEV), b.to(DEV)
+        n = _lib.HycNormFwd()
+        n.kind, n.eps = pk._NORM_KIND[kind], 1e-5
+        n.weight, n.bias, n.param_dtype = wd.data_ptr(), (bd.data_ptr() if kind == "ln" else None), _lib.HYC_BF16
+        n.y, n.rstd, n.mean = y.data_ptr(), rstd.data_ptr(), (mean.data_ptr() if kind == "ln" else None)
+        _lib.check(_lib.lib.hyc_norm_compress(C.byref(dn), C.byref(n), C.byref(rec), pk._stream()), "hyc_norm_compress")
+        y_o, mean_o, rstd_o = oc.norm_forward(x, w, b, 1e-5, kind)
+        assert ((y.float().cpu() - y_o.float()).abs() <= 1e-2 * y_o.float().abs() + 1e-3).all()
+        assert _rel_err(rstd, rstd_o) < 1e-5
+        if kind == "ln":
+            assert (mean.cpu() - mean_o).abs().max() < 1e-4
+    torch.cuda.synchronize()
+    assert torch.equal(p.scales.cpu(), c.scales)
+    assert torch.equal(p.codes.cpu().view(torch.uint8), c.codes.view(torch.uint8))
+    assert torch.equal(p.out_value.cpu(), c.out_value)
+    assert int(p.status.item()) == 0
+    arena.check()
+
+
 @pytest.mark.parametrize("kind,d,bits,group,rotate,rows", [
     ("rms", 4096, 4, 0, 0, 3001), ("rms", 4096, 2, 128, 0, 517), ("rms_gemma", 2048, 8, 0, 0, 700),
     ("ln", 768, 4, 0, 0, 5003), ("rms", 2816, 4, 128, 0, 333), ("ln", 3072, 2, 0, 0, 129), ("rms", 1024, 4, 0, 0, 1),
