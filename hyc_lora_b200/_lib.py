@@ -93,6 +93,10 @@ SYMBOLS = {
     "hyc_norm_compress": (C.c_int, [C.POINTER(HycDense), C.POINTER(HycNormFwd), C.POINTER(HycPacked), C.c_void_p]),
     "hyc_norm_compress2": (C.c_int, [C.POINTER(HycDense), C.POINTER(HycNormFwd), C.POINTER(HycPacked), C.POINTER(HycPacked),
                                      C.c_void_p]),
+    "hyc_act_compress": (C.c_int, [C.POINTER(HycDense), C.c_int, C.c_void_p, C.POINTER(HycPacked), C.POINTER(HycPacked),
+                                   C.c_void_p]),
+    "hyc_product_compress": (C.c_int, [C.POINTER(HycDense), C.POINTER(HycDense), C.c_void_p, C.POINTER(HycPacked),
+                                       C.POINTER(HycPacked), C.c_void_p]),
     "hyc_norm_bwd_partial_rows": (C.c_int, []),
     "hyc_norm_bwd": (C.c_int, [C.POINTER(HycPacked), C.POINTER(HycNormBwdArgs), C.c_void_p]),
     "hyc_act_bwd": (C.c_int, [C.c_int, C.POINTER(HycPacked), C.POINTER(HycPacked), C.c_void_p, C.c_int,

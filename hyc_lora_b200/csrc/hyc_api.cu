@@ -5,6 +5,7 @@
 #include "hyc_fwd_r_fast.cuh"
 #include "hyc_fwd_warp.cuh"
 #include "hyc_fwd_chunk.cuh"
+#include "hyc_fwd_wide.cuh"
 #include "hyc_fwd_r_warp.cuh"
 
 namespace hyc {
@@ -14,6 +15,32 @@ int g_tune_threads = 0, g_tune_stages = 0, g_tune_ctas = 0;
 std::atomic<unsigned long long> g_launch_count{0};
 long long g_debug_wait_cycles = 0;
 unsigned int g_debug_tx_pad = 0;
+
+
+// The wide-row kernels (hyc_fwd_wide.cuh): compress-only of rows wider than 4096 channels, activation + compress,
+// product + compress.  HYC_ERR_SHAPE: this combination is not built; the caller takes the separate calls.
+static int run_wide(int op, const hyc_dense* x, const hyc_dense* x2, void* y, const hyc_packed* out, const hyc_packed* out_y,
+                    cudaStream_t stream) {
+  static const bool wide_off = getenv("HYC_FWD_WIDE") && getenv("HYC_FWD_WIDE")[0] == '0';
+  if (wide_off) return HYC_ERR_SHAPE;
+  const WidePlan wp = plan_wide(out, x, out_y);
+  if (!wp.ok) return HYC_ERR_SHAPE;
+  CUtensorMap m0, m1, m2;
+  if (!row_tensor_map(&m0, x->base, out->rows, out->cols, x->row_stride)) return HYC_ERR_SHAPE;
+  m1 = m0;
+  m2 = m0;
+  if (x2 && !row_tensor_map(&m1, x2->base, out->rows, out->cols, x2->row_stride)) return HYC_ERR_SHAPE;
+  if (y && !row_tensor_map(&m2, y, out->rows, out->cols, out->cols)) return HYC_ERR_SHAPE;
+  WideArgs wa;
+  memset(&wa, 0, sizeof(wa));
+  wa.p = to_dev(out);
+  if (out_y) { wa.p2 = to_dev(out_y); wa.has_p2 = 1; }
+  wa.lanes = wp.lanes;
+  wa.off_chan = wp.off_chan; wa.off_chan2 = wp.off_chan2; wa.off_red = wp.off_red;
+  wa.off_slots = wp.off_slots; wa.slot_stride = wp.slot_stride;
+  wa.wait_cycles = g_debug_wait_cycles > 0 ? g_debug_wait_cycles : kWaitCycles;
+  return launch_wide(wa, wp, op, m0, m1, m2, stream);
+}
 
 static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, cudaStream_t stream,
                    const hyc_packed* out_y = nullptr) {
@@ -76,6 +103,13 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
     }
   }
   if (out->mode == HYC_MODE_N) {
+    // rows wider than one warp holds: up to four warps per row, a chunk of every segment per lane
+    // (measured: with a rotation the chunk layout wins, 23 against 26 us at 2048 x 11008; without one the
+    // CTA-per-row kernel below does, 15 against 18 us)
+    if (!norm && !out_y && out->cols > 4096 && out->rotate && x->dtype == HYC_BF16) {
+      const int rw = run_wide(kWideCompress, x, nullptr, nullptr, out, nullptr, stream);
+      if (rw != HYC_ERR_SHAPE) return rw;
+    }
     // rotated rows whose segment is 32 chunks wide: one warp per row, a chunk of every segment per lane
     static const bool chunk_off = getenv("HYC_FWD_CHUNK") && getenv("HYC_FWD_CHUNK")[0] == '0';
     const ChunkPlan cp = chunk_off ? ChunkPlan{} : plan_chunk_fwd(out, x, norm != nullptr, norm && norm->kind == HYC_NORM_LAYER, out_y);
@@ -222,6 +256,37 @@ int hyc_compress(const hyc_dense* x, const hyc_packed* out, void* stream) {
 int hyc_norm_compress(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out, void* stream) {
   if (!norm) return HYC_ERR_NULL;
   return run_fwd(x, norm, out, static_cast<cudaStream_t>(stream));
+}
+
+static int check_wide_call(const hyc_dense* x, void* y, const hyc_packed* out, const hyc_packed* out_y) {
+  if (!x || !y || !out) return HYC_ERR_NULL;
+  const int empty = packed_is_empty(out);
+  if (empty) return empty < 0 ? empty : 1;        // 1: nothing to do
+  int rc = check_packed(out, true);
+  if (rc) return rc;
+  if (out_y && (rc = check_packed(out_y, true))) return rc;
+  rc = check_dense(x, out->cols, true);
+  if (rc) return rc;
+  if (!aligned16(y)) return HYC_ERR_ALIGN;
+  if (out->mode != HYC_MODE_N || x->dtype != HYC_BF16) return HYC_ERR_SHAPE;
+  return out->rows == 0 ? 1 : HYC_OK;
+}
+
+int hyc_act_compress(const hyc_dense* x, int op, void* y, const hyc_packed* out_x, const hyc_packed* out_y, void* stream) {
+  if (op != HYC_ACT_SILU && op != HYC_ACT_GELU_TANH) return HYC_ERR_MODE;
+  const int rc = check_wide_call(x, y, out_x, out_y);
+  if (rc) return rc == 1 ? HYC_OK : rc;
+  return run_wide(op == HYC_ACT_SILU ? kWideSilu : kWideGelu, x, nullptr, y, out_x, out_y, static_cast<cudaStream_t>(stream));
+}
+
+int hyc_product_compress(const hyc_dense* x1, const hyc_dense* x2, void* y, const hyc_packed* out_x2, const hyc_packed* out_y,
+                         void* stream) {
+  int rc = check_wide_call(x2, y, out_x2, out_y);
+  if (rc) return rc == 1 ? HYC_OK : rc;
+  rc = check_dense(x1, out_x2->cols, true);
+  if (rc) return rc;
+  if (x1->dtype != HYC_BF16) return HYC_ERR_SHAPE;
+  return run_wide(kWideProduct, x1, x2, y, out_x2, out_y, static_cast<cudaStream_t>(stream));
 }
 
 int hyc_norm_compress2(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out_x, const hyc_packed* out_y,

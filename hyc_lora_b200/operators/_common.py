@@ -163,6 +163,34 @@ def _output_request(opts, iteration):
 
 
 @torch.no_grad()
+def fused_site(kind: str, x, bits: int, iteration: int, opts: Optional[SiteOptions], x1=None):
+    """Channel mode, bf16 rows: the site's output AND the record of its saved input from one kernel --
+    ``kind`` "silu" / "gelu": ``y = act(x)``; "product": ``y = x1 * x``, the record being that of ``x`` (the
+    second operand; the first one's record comes from the site that produced it).  When a later site has
+    registered as the reader of ``y`` (see ``norm_output_ready``), the kernel makes that record too and it is
+    left in ``opts.pending_output``.  Returns ``(packed, y)``, or None where this path does not apply (the
+    caller then computes ``y`` and calls ``compress_site``)."""
+    if (opts is None or not opts.channel or not x.is_cuda or x.dtype != torch.bfloat16 or x.dim() == 4
+            or (x1 is not None and (x1.dtype != torch.bfloat16 or x1.shape != x.shape))):
+        return None
+    cols = x.shape[-1]
+    rotate = opts.rotate_for(cols, bits)
+    channels = opts.calib.channels_for(x, iteration)
+    also = _output_request(opts, iteration)
+    if kind == "product":
+        res = cf._pk.product_compress_n(x1, x, channels, bits, opts.group_size, rotate, also_output=also)
+    else:
+        res = cf._pk.act_compress_n(kind, x, channels, bits, opts.group_size, rotate, also_output=also)
+    if res is None:
+        # the library does not build this shape: the separate passes, with the channels chosen above
+        y = x1 * x if kind == "product" else (torch.nn.functional.silu(x) if kind == "silu" else torch.nn.functional.gelu(x))
+        opts.pending_output = None
+        return cf.channel_compress(x, channels, bits, opts.group_size, rotate), y
+    packed, y, opts.pending_output = res
+    return packed, y.view(x.shape)
+
+
+@torch.no_grad()
 def compress_site(x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, method, rank, iteration, static_value,
                   opts: Optional[SiteOptions], norm: Optional[dict] = None):
     """Compress ``x`` for backward.  Returns ``(packed, (outlier, L, R, scale), norm_out)``

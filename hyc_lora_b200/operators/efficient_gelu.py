@@ -6,7 +6,7 @@ import torch
 import torch.nn.functional as F
 
 from .. import packed as _pk
-from ._common import SiteOptions, compress_site, site_options, update_static
+from ._common import SiteOptions, compress_site, fused_site, norm_output_ready, site_options, update_static
 from .compress_function import StaticList
 
 
@@ -15,10 +15,17 @@ class EfficientMemoryGELUFunc(torch.autograd.Function):
     def forward(ctx, x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, sub_outlier_quantize_method, rank,
                 iteration, static_value, *extra):
         ctx.n_extra = len(extra)
-        result = F.gelu(x)
-        packed, (outlier, L, R, scale), _ = compress_site(
-            x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, sub_outlier_quantize_method, rank, iteration,
-            static_value, site_options(extra))
+        opts = site_options(extra)
+        fused = fused_site("gelu", x, sub_outlier_bit, iteration, opts)
+        if fused is not None:
+            # one kernel: the activation, the record of its input and (once a reader is known) of its output
+            packed, result = fused
+            outlier, L, R, scale = opts.dummy_stats(x.device)
+        else:
+            result = F.gelu(x)
+            packed, (outlier, L, R, scale), _ = compress_site(
+                x, outlier_ratio, sub_outlier_ratio, sub_outlier_bit, sub_outlier_quantize_method, rank, iteration,
+                static_value, opts)
         ctx.x_outlier_compressed = packed
         # the statistics carry no gradient: without this autograd would fill a zero tensor for each of them
         # on every backward call
@@ -56,5 +63,8 @@ class EfficientMemoryGELU(torch.nn.Module):
             self.sub_outlier_quantize_method, self.rank, self.iteration, self.static_value, self.site)
         if not self.site.channel:
             update_static(self.static_value, self.iteration, outlier, L, scale, R)
+        else:
+            # the site behind this one saves ``result``: hand it the record made in the same pass
+            norm_output_ready(result, self.site, self.iteration)
         self.iteration += 1
         return result

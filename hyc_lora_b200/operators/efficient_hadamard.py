@@ -5,7 +5,7 @@ one kernel over both packed operands (efficient_hadamard.py:56-66)."""
 import torch
 
 from .. import packed as _pk
-from ._common import SiteOptions, compress_site, update_static
+from ._common import SiteOptions, compress_site, fused_site, norm_output_ready, update_static
 from .compress_function import StaticList
 
 
@@ -20,14 +20,21 @@ class EfficientMemoryHadamardFunc(torch.autograd.Function):
                 outlier_ratio_2, sub_outlier_ratio_2, sub_outlier_bit_2, sub_outlier_quantize_method_2, rank,
                 iteration, static_value_1, static_value_2, *extra):
         ctx.n_extra = len(extra)
-        result = x1 * x2
         o1, o2 = (extra[0], extra[1]) if len(extra) >= 2 else (None, None)
+        # x1 is, in the gated MLP, the activation's output: its record usually exists already (shared table)
         p1, (outlier_1, L_1, R_1, scale_1), _ = compress_site(
             x1, outlier_ratio_1, sub_outlier_ratio_1, sub_outlier_bit_1, sub_outlier_quantize_method_1, rank,
             iteration, static_value_1, o1)
-        p2, (outlier_2, L_2, R_2, scale_2), _ = compress_site(
-            x2, outlier_ratio_2, sub_outlier_ratio_2, sub_outlier_bit_2, sub_outlier_quantize_method_2, rank,
-            iteration, static_value_2, o2)
+        fused = fused_site("product", x2, sub_outlier_bit_2, iteration, o2, x1=x1)
+        if fused is not None:
+            # one kernel: the product, the record of x2 and (once a reader is known) of the product
+            p2, result = fused
+            outlier_2, L_2, R_2, scale_2 = o2.dummy_stats(x2.device)
+        else:
+            result = x1 * x2
+            p2, (outlier_2, L_2, R_2, scale_2), _ = compress_site(
+                x2, outlier_ratio_2, sub_outlier_ratio_2, sub_outlier_bit_2, sub_outlier_quantize_method_2, rank,
+                iteration, static_value_2, o2)
         ctx.x_outlier_compressed = (p1, p2)
         # the statistics carry no gradient: without this autograd would fill a zero tensor for each of them
         # on every backward call
@@ -77,6 +84,9 @@ class EfficientMemoryHadamard(torch.nn.Module):
         if not self.site_1.channel:
             update_static(self.static_value_1, self.iteration, outlier_1, L_1, scale_1, R_1)
             update_static(self.static_value_2, self.iteration, outlier_2, L_2, scale_2, R_2)
+        else:
+            # the linear behind the product saves ``result``: hand it the record made in the same pass
+            norm_output_ready(result, self.site_2, self.iteration)
         self.iteration += 1
         # the reference empties the CUDA cache here on every call (efficient_hadamard.py:181); that
         # stalls the allocator and is left out

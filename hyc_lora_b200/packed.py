@@ -401,6 +401,61 @@ def compress_n(x: torch.Tensor, channels: Optional[torch.Tensor], bits: int, gro
     return _run_fwd(d, keep, p, norm, p2)
 
 
+def _same_format(a: dict, bits, group, rotate) -> bool:
+    return a["bits"] == bits and a.get("group", 0) == group and a.get("rotate", 0) == rotate
+
+
+def act_compress_n(op: str, x: torch.Tensor, channels, bits: int, group: int = 0, rotate: int = 0,
+                   also_output: Optional[dict] = None):
+    """``y = silu(x)`` / ``gelu(x)`` and the channel-mode record of ``x`` in one pass; with ``also_output``
+    (keys ``channels``, ``bits``, ``group``, ``rotate``) also the record of ``y``.  Returns ``(packed_x, y, packed_y)``,
+    or None when the library does not build this combination (the caller then computes ``y`` and compresses with
+    calls of its own)."""
+    _require_cuda(x, channels)
+    if x.dim() == 4 or x.dtype != torch.bfloat16:
+        return None
+    cols = x.shape[-1]
+    d, rows, seq, shape, keep = _dense_record(x, cols)
+    p = _new_n(keep, rows, cols, seq, shape, channels, bits, group, rotate)
+    p2 = None
+    if also_output is not None and _same_format(also_output, bits, group, rotate):
+        p2 = _new_n(keep, rows, cols, seq, shape, also_output["channels"], bits, group, rotate)
+    y = torch.empty_like(keep)
+    rec = p.record()
+    rec2 = p2.record() if p2 is not None else None
+    rc = lib.hyc_act_compress(C.byref(d), _ACT_OP[op], y.data_ptr(), C.byref(rec), C.byref(rec2) if rec2 is not None else None,
+                              _stream())
+    if rc == _lib.HYC_ERR_SHAPE:
+        return None
+    check(rc, "hyc_act_compress")
+    return p, y, p2
+
+
+def product_compress_n(x1: torch.Tensor, x2: torch.Tensor, channels2, bits: int, group: int = 0, rotate: int = 0,
+                       also_output: Optional[dict] = None):
+    """``y = x1 * x2`` and the channel-mode record of ``x2`` in one pass; with ``also_output`` also the record
+    of ``y``.  Returns ``(packed_x2, y, packed_y)`` or None (see :func:`act_compress_n`)."""
+    _require_cuda(x1, x2, channels2)
+    if x1.dim() == 4 or x1.dtype != torch.bfloat16 or x2.dtype != torch.bfloat16 or x1.shape != x2.shape:
+        return None
+    cols = x2.shape[-1]
+    d1, _, _, _, keep1 = _dense_record(x1, cols)
+    d2, rows, seq, shape, keep2 = _dense_record(x2, cols)
+    p = _new_n(keep2, rows, cols, seq, shape, channels2, bits, group, rotate)
+    p2 = None
+    if also_output is not None and _same_format(also_output, bits, group, rotate):
+        p2 = _new_n(keep2, rows, cols, seq, shape, also_output["channels"], bits, group, rotate)
+    y = torch.empty_like(keep2)
+    rec = p.record()
+    rec2 = p2.record() if p2 is not None else None
+    rc = lib.hyc_product_compress(C.byref(d1), C.byref(d2), y.data_ptr(), C.byref(rec),
+                                  C.byref(rec2) if rec2 is not None else None, _stream())
+    if rc == _lib.HYC_ERR_SHAPE:
+        return None
+    check(rc, "hyc_product_compress")
+    return p, y, p2
+
+
 def _run_fwd(d, x, p: Packed, norm, p2: Optional[Packed] = None):
     rec = p.record()
     if norm is None:

@@ -174,6 +174,23 @@ int hyc_norm_compress(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_pa
 int hyc_norm_compress2(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packed* out_x, const hyc_packed* out_y,
                        void* stream);
 
+/* Activation forward + compress, one pass: y = silu(x) (HYC_ACT_SILU) or the exact erf GELU (HYC_ACT_GELU_TANH:
+ * the GELU site, named for its backward formula), the record of the input x and, when out_y is not NULL, the
+ * record of the output y (the product site behind a SiLU saves it).  Replaces F.silu / F.gelu followed by
+ * true_divide_outlier_suboutlier_svd_compress (efficient_silu.py:33-35, efficient_gelu.py:33-35) and the
+ * compression of the same tensor by the next site (efficient_hadamard.py:45).  y: bf16 [rows, cols], contiguous.
+ * Channel mode, bf16 rows of a multiple of 128 channels, at most 16384; both records in one format.
+ * HYC_ERR_SHAPE means "not built for this call": compute y and make the separate hyc_compress calls. */
+int hyc_act_compress(const hyc_dense* x, int op, void* y, const hyc_packed* out_x, const hyc_packed* out_y, void* stream);
+
+/* Product forward + compress, one pass: y = x1 * x2, the record of x2 and, when out_y is not NULL, the record
+ * of y (the LoRA-A linear behind the product saves it).  The record of x1 is not made here: in the gated MLP
+ * x1 is the activation output, whose record hyc_act_compress has already made.  Replaces x1 * x2 and the
+ * compress calls of efficient_hadamard.py:43-46 and efficient_linear.py:46.  Same limits and the same meaning
+ * of HYC_ERR_SHAPE as hyc_act_compress. */
+int hyc_product_compress(const hyc_dense* x1, const hyc_dense* x2, void* y, const hyc_packed* out_x2, const hyc_packed* out_y,
+                         void* stream);
+
 /* Decompress + norm backward.  Replaces the decompress chain followed by
  * _rms_norm_bwd_dx_fused/_dwdb or _layer_norm_bwd_dx_fused/_dwdb
  * (efficient_rmsnorm.py:214-269, efficient_layernorm.py:275-335).

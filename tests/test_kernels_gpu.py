@@ -704,6 +704,113 @@ def test_rotating_forward_one_chunk_per_lane(pk, d, bits, group, rotate, kind, r
     arena.check()
 
 
+WIDE_CASES = [
+    # d, bits, group, rotate, rows, outlier fraction
+    (11008, 4, 0, 64, 70, 0.01), (11008, 4, 0, 0, 2500, 0.01), (11008, 4, 128, 64, 300, 0.02), (11008, 2, 0, 16, 70, 0.01),
+    (11008, 8, 128, 64, 70, 0.01), (14336, 2, 128, 0, 300, 0.02), (14336, 4, 0, 256, 70, 0.01), (3072, 4, 0, 0, 300, 0.01),
+    (3072, 8, 128, 256, 70, 0.01), (8192, 4, 0, 256, 300, 0.01), (5120, 4, 128, 64, 70, 0.01), (4096, 4, 0, 256, 2500, 0.01),
+    (16384, 4, 0, 1024, 70, 0.005)]
+
+
+def _same_record(got, want):
+    assert torch.equal(got.codes, want.codes)
+    assert torch.equal(got.scales, want.scales)
+    if want.out_value is not None:
+        assert torch.equal(got.out_value, want.out_value)
+    assert int(got.status.item()) == 0
+
+
+@pytest.mark.parametrize("d,bits,group,rotate,rows,frac", WIDE_CASES)
+def test_wide_rows_compress_against_oracle(pk, d, bits, group, rotate, rows, frac):
+    """Rows wider than one warp holds (up to four warps per row): the record equals the oracle's."""
+    x, _ = synthetic.sweep_activation(rows, d, frac, dtype=torch.bfloat16, salt=d + bits)
+    x[rows // 3] = 0
+    xd = x.to(DEV)
+    k = oc.n_outlier_count(d, frac)
+    ch = pk.select_channels(pk.channel_absmax(xd), k)
+    c = oc.n_compress(x, ch.cpu(), bits, group, rotate)
+    p = pk.compress_n(xd, ch, bits, group, rotate)
+    assert torch.equal(p.scales.cpu(), c.scales)
+    assert torch.equal(p.codes.cpu().view(torch.uint8), c.codes.view(torch.uint8))
+    assert torch.equal(p.out_value.cpu(), c.out_value)
+    assert torch.equal(pk.decompress(p).cpu().reshape(rows, d), oc.n_decompress(c))
+
+
+@pytest.mark.parametrize("d,bits,group,rotate,rows,frac", WIDE_CASES)
+@pytest.mark.parametrize("op", ["silu", "gelu"])
+def test_activation_and_both_records_in_one_pass(pk, op, d, bits, group, rotate, rows, frac):
+    """``hyc_act_compress``: the output is torch's, the record of the input is that of ``hyc_compress``, and
+    the record of the output is that of ``hyc_compress`` on the output."""
+    x, _ = synthetic.sweep_activation(rows, d, frac, dtype=torch.bfloat16, salt=d + bits + 1)
+    xd = (0.25 * x).to(DEV)
+    k = oc.n_outlier_count(d, frac)
+    ch_x = pk.select_channels(pk.channel_absmax(xd), k)
+    want_y = torch.nn.functional.silu(xd) if op == "silu" else torch.nn.functional.gelu(xd)
+    ch_y = pk.select_channels(pk.channel_absmax(want_y), k)
+    got = pk.act_compress_n(op, xd, ch_x, bits, group, rotate, also_output=dict(channels=ch_y, bits=bits, group=group, rotate=rotate))
+    assert got is not None, "the call was refused"
+    px, y, py = got
+    # one rounding to bf16 of an fp32 value on both sides; the two exponential / erf routines may differ in the
+    # last place of the fp32 value
+    assert ((y.float() - want_y.float()).abs() <= 2 ** -7 * want_y.float().abs() + 1e-30).all()
+    _same_record(px, pk.compress_n(xd, ch_x, bits, group, rotate))
+    _same_record(py, pk.compress_n(y, ch_y, bits, group, rotate))
+    # without the second record
+    px1, y1, none = pk.act_compress_n(op, xd, ch_x, bits, group, rotate)
+    assert none is None and torch.equal(y1, y)
+    _same_record(px1, px)
+
+
+@pytest.mark.parametrize("d,bits,group,rotate,rows,frac", WIDE_CASES)
+def test_product_and_both_records_in_one_pass(pk, d, bits, group, rotate, rows, frac):
+    """``hyc_product_compress``: ``y = x1 * x2`` exactly, the record of ``x2`` and the record of ``y``."""
+    x1, _ = synthetic.sweep_activation(rows, d, frac, dtype=torch.bfloat16, salt=d + bits + 2)
+    x2, _ = synthetic.sweep_activation(rows, d, frac, dtype=torch.bfloat16, salt=d + bits + 3)
+    x1d, x2d = (0.25 * x1).to(DEV), x2.to(DEV)
+    k = oc.n_outlier_count(d, frac)
+    ch2 = pk.select_channels(pk.channel_absmax(x2d), k)
+    want_y = x1d * x2d
+    ch_y = pk.select_channels(pk.channel_absmax(want_y), k)
+    got = pk.product_compress_n(x1d, x2d, ch2, bits, group, rotate, also_output=dict(channels=ch_y, bits=bits, group=group, rotate=rotate))
+    assert got is not None, "the call was refused"
+    p2, y, py = got
+    assert torch.equal(y, want_y)
+    _same_record(p2, pk.compress_n(x2d, ch2, bits, group, rotate))
+    _same_record(py, pk.compress_n(want_y, ch_y, bits, group, rotate))
+    p2b, yb, none = pk.product_compress_n(x1d, x2d, ch2, bits, group, rotate)
+    assert none is None and torch.equal(yb, want_y)
+    _same_record(p2b, p2)
+
+
+def test_wide_row_kernels_write_nothing_outside_their_outputs(pk):
+    """The three one-pass calls with every output inside a guarded arena."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    d, rows, bits = 11008, 131, 4
+    x1, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=torch.bfloat16, salt=5)
+    x2, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=torch.bfloat16, salt=6)
+    x1d, x2d = x1.to(DEV), x2.to(DEV)
+    ch = pk.select_channels(pk.channel_absmax(x2d), 111)
+    arena = _Arena(rows * d * 12 + (1 << 20))
+    for op in ("compress", "silu", "product"):
+        pa = _packed_n_in(arena, pk, rows, d, bits, 0, 64, ch)
+        pb = _packed_n_in(arena, pk, rows, d, bits, 0, 64, ch)
+        y = arena.take((rows, d), torch.bfloat16)
+        ra, rb = pa.record(), pb.record()
+        d1, d2 = _dense(x1d, d), _dense(x2d, d)
+        if op == "compress":
+            _lib.check(_lib.lib.hyc_compress(C.byref(d2), C.byref(ra), pk._stream()), "hyc_compress")
+        elif op == "silu":
+            _lib.check(_lib.lib.hyc_act_compress(C.byref(d2), _lib.HYC_ACT_SILU, y.data_ptr(), C.byref(ra), C.byref(rb),
+                                                 pk._stream()), "hyc_act_compress")
+        else:
+            _lib.check(_lib.lib.hyc_product_compress(C.byref(d1), C.byref(d2), y.data_ptr(), C.byref(ra), C.byref(rb),
+                                                     pk._stream()), "hyc_product_compress")
+        torch.cuda.synchronize()
+        _same_record(pa, pk.compress_n(x2d, ch, bits, 0, 64))
+    arena.check()
+
+
 @pytest.mark.parametrize("kind,d,bits,group,rotate,rows", [
     ("rms", 4096, 4, 0, 0, 3001), ("rms", 4096, 2, 128, 0, 517), ("rms_gemma", 2048, 8, 0, 0, 700),
     ("ln", 768, 4, 0, 0, 5003), ("rms", 2816, 4, 128, 0, 333), ("ln", 3072, 2, 0, 0, 129), ("rms", 1024, 4, 0, 0, 1),

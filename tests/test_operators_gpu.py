@@ -390,6 +390,57 @@ def test_norm_emits_the_record_of_its_output_for_the_sites_behind_it(kind, rotat
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("rotate,act", [(0, "silu"), (64, "silu"), (0, "gelu")])
+def test_gated_mlp_sites_make_every_record_in_two_passes(rotate, act):
+    """activation -> product -> LoRA-A linear (the gated MLP), channel mode: from the first steady-state call
+    on, one launch makes the activation, the record of its input and the record of its output, a second one the
+    product, the record of the other operand and the record the linear saves; gradients are what they are
+    when every site compresses for itself."""
+    from hyc_lora_b200 import _lib
+    from hyc_lora_b200.operators import _common
+    from hyc_lora_b200.operators.efficient_gelu import EfficientMemoryGELU
+    from hyc_lora_b200.operators.efficient_hadamard import EfficientMemoryHadamard
+    from hyc_lora_b200.operators.efficient_linear import EfficientMemoryLinear
+    from hyc_lora_b200.operators.efficient_silu import EfficientMemorySiLU
+    d, r = 1024, 16
+    gate = 0.2 * _act(2, 40, d, salt=90, gain=20.0)
+    up = _act(2, 40, d, salt=91, gain=20.0)
+    g = _rand((2, 40, r), 92)
+    w = (0.02 * _rand((r, d), 93, torch.float32)).to(torch.bfloat16)
+    kw = dict(outlier_ratio=0.01, sub_outlier_ratio=1.0, sub_outlier_bit=4, rank=0, outlier_mode="channel", rotate=rotate)
+    kw2 = dict(outlier_ratio_1=0.01, sub_outlier_ratio_1=1.0, sub_outlier_bit_1=4, outlier_ratio_2=0.01,
+               sub_outlier_ratio_2=1.0, sub_outlier_bit_2=4, rank=0, outlier_mode="channel", rotate=rotate)
+    grads, launches = {}, {}
+    for share in (True, False):
+        _common.SHARE_SITES = share
+        _common._shared.clear()
+        _common._last_norm_output = None
+        fn = (EfficientMemorySiLU if act == "silu" else EfficientMemoryGELU)(**kw)
+        prod = EfficientMemoryHadamard(**kw2)
+        lin = EfficientMemoryLinear(d, r, bias=False, **kw).to(DEV).to(torch.bfloat16)
+        lin.weight.data.copy_(w)
+        per_call = []
+        for it in range(4):                      # two calibration calls, two steady-state calls
+            lin.weight.grad = None
+            gd, ud = gate.to(DEV).requires_grad_(True), up.to(DEV).requires_grad_(True)
+            l0 = _lib.lib.hyc_launch_count()
+            out = lin(prod(fn(gd), ud))
+            per_call.append(_lib.lib.hyc_launch_count() - l0)
+            (out * g.to(DEV)).sum().backward()
+        launches[share] = per_call
+        grads[share] = [lin.weight.grad.clone(), gd.grad.clone(), ud.grad.clone(), out.detach().clone()]
+    _common.SHARE_SITES = True
+    # steady state: activation + product with sharing; without it the activation's output and the product are
+    # compressed again by the sites that save them
+    assert launches[True][3] == 2 and launches[False][3] == 4
+    for a, b in zip(grads[True], grads[False]):
+        assert torch.equal(a, b)
+    # the forward value against torch's own activation and product (bf16, one unit in the last place)
+    ref = torch.nn.functional.linear((torch.nn.functional.silu if act == "silu" else torch.nn.functional.gelu)(gate.to(DEV))
+                                     * up.to(DEV), w.to(DEV))
+    assert _cos(grads[True][3], ref) > 0.9999
+
+
 def test_low_rank_site_and_calibration_state_roundtrip():
     """rank > 0: the randomized SVD differs between devices, so the check is against the exact
     derivative; then a second module restored from the first one's calibration state reproduces
