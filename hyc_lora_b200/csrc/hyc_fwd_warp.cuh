@@ -264,10 +264,220 @@ __device__ __forceinline__ void warp_row_plain(const WarpFwdArgs& a, const Packe
 
 // NK: 0 compress only, 1 RMSNorm (plain or Gemma), 2 LayerNorm;  NG: 16-byte register groups per lane
 // (units per lane x segments)
-// DUAL: a second record (a.p2, with its own outlier channels) takes the compressed norm OUTPUT: the sites
-// behind a norm save that tensor, and this way it is compressed in the pass that produces it.
-template <int BITS, int NK, int NG, bool GROUP, bool DUAL>
+template <int BITS, int NK, int NG, bool GROUP>
 __global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_n_warp_kernel(const __grid_constant__ WarpFwdArgs a) {
+  using C = CodeTraits<BITS>;
+  constexpr int NSEG = C::kSeg;
+  constexpr int UPL = NG / NSEG;
+  constexpr bool NORM = NK != 0;
+  constexpr bool ln = NK == 2;
+  static_assert(UPL >= 1 && UPL * NSEG == NG, "register groups must cover whole units");
+  extern __shared__ __align__(128) unsigned char smem[];
+  const PackedDev& p = a.p;
+  const int D = p.cols;
+  const int segw = D / NSEG;
+  const int U = segw >> 3;
+  const int k = p.n_channels;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+  const int G = GROUP ? (D >> 7) : 1;
+  const float qmax = static_cast<float>(C::kHi);
+  const float inv_d = 1.0f / static_cast<float>(D);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  int* chan = reinterpret_cast<int*>(smem + a.off_chan);
+  float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
+  float* bsm = reinterpret_cast<float*>(smem + a.off_bsm);
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem + a.off_slots + static_cast<size_t>(warp) * a.slot_bytes);
+  uint64_t* bar = &bars[warp];
+  const uint32_t row_bytes = static_cast<uint32_t>(D) * 2u;
+  const long long rows = p.rows, stride = static_cast<long long>(gridDim.x) * W;
+  long long row = static_cast<long long>(blockIdx.x) * W + warp;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < W; ++i) mbar_init(&bars[i], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  // the first row of every warp starts travelling before the per-CTA tables are set up
+  if (lane == 0 && row < rows) {
+    mbar_expect_tx(bar, row_bytes);
+    bulk_g2s(xs, a.x + row * a.row_stride, row_bytes, bar);
+  }
+  for (int j = threadIdx.x; j < k; j += blockDim.x) chan[j] = p.channels[j];
+  if (NORM) {
+    const float plus = a.kind == HYC_NORM_RMS_GEMMA ? 1.f : 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+      wsm[split_index(c, D)] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[c])
+                                             : static_cast<const float*>(a.weight)[c]) + plus;
+      if (ln)
+        bsm[split_index(c, D)] = a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[c])
+                                              : static_cast<const float*>(a.bias)[c];
+    }
+  }
+  __syncthreads();
+  // the outlier channels this lane looks after (-1: none)
+  int oc[kWarpOutPerLane];
+#pragma unroll
+  for (int q = 0; q < kWarpOutPerLane; ++q) oc[q] = (lane + 32 * q) < k ? chan[lane + 32 * q] : -1;
+
+  uint32_t ph = 0;
+  for (; row < rows; row += stride, ph ^= 1u) {
+    if (!mbar_wait_bounded(bar, ph, a.wait_cycles)) {
+      // the only copy this warp has in flight is the one it gave up on
+      if (lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
+      return;
+    }
+    // ---- outlier channels: keep the original, write it out, zero it in the staged row
+    float ov[kWarpOutPerLane];
+#pragma unroll
+    for (int q = 0; q < kWarpOutPerLane; ++q) {
+      ov[q] = 0.f;
+      if (oc[q] >= 0) {
+        const __nv_bfloat16 o = xs[oc[q]];
+        p.out_value[row * k + lane + 32 * q] = o;
+        ov[q] = __bfloat162float(o);
+        xs[oc[q]] = __float2bfloat16_rn(0.f);
+      }
+    }
+    __syncwarp();
+    // ---- the lane's share of the row, raw
+    uint4 raw[NG];
+#pragma unroll
+    for (int r = 0; r < NG; ++r) {
+      const int u = lane + 32 * (r / NSEG);
+      raw[r] = u < U ? *reinterpret_cast<const uint4*>(xs + (r % NSEG) * segw + (u << 3)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncwarp();
+    // every lane has what it needs: hand the slot back to the copy engine
+    const long long next = row + stride;
+    if (lane == 0 && next < rows) {
+      fence_proxy_async();
+      mbar_expect_tx(bar, row_bytes);
+      bulk_g2s(xs, a.x + next * a.row_stride, row_bytes, bar);
+    }
+    // ---- statistics
+    float mean = 0.f;
+    if (ln) {
+      float s1 = 0.f;
+#pragma unroll
+      for (int r = 0; r < NG; ++r) {
+        float f[8];
+        unpack_bf16x8(raw[r], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s1 += f[e];
+      }
+#pragma unroll
+      for (int q = 0; q < kWarpOutPerLane; ++q) s1 += ov[q];
+      mean = warp_sum(s1) * inv_d;
+#pragma unroll
+      for (int r = 0; r < NG; ++r) forget_unpacked(raw[r]);
+    }
+    float ss = 0.f;
+    __nv_bfloat162 am2 = __float2bfloat162_rn(0.f);
+    float ginv[GROUP ? NG : 1];
+#pragma unroll
+    for (int r = 0; r < NG; ++r) {
+      if (NORM) {
+        float f[8];
+        unpack_bf16x8(raw[r], f);
+        if (ln) {
+          const bool live = (lane + 32 * (r / NSEG)) < U;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { const float c = f[e] - mean; ss = live ? fmaf(c, c, ss) : ss; }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+        }
+      }
+      if (GROUP) {
+        // 16 consecutive lanes hold one 128-channel group of this register group
+        float a8 = pair_max(absmax_acc(__float2bfloat162_rn(0.f), raw[r]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) a8 = fmaxf(a8, __shfl_xor_sync(0xffffffffu, a8, o));
+        ginv[r] = a8;
+      } else {
+        am2 = absmax_acc(am2, raw[r]);
+      }
+    }
+    if constexpr (GROUP) group_scales<BITS, NG>(ginv, p.scales + row * G, segw, U, lane);
+    float rstd = 0.f;
+    if (NORM) {
+      // the zeroed outlier channels still belong to the row statistics
+#pragma unroll
+      for (int q = 0; q < kWarpOutPerLane; ++q)
+        if (oc[q] >= 0) ss += ln ? ((ov[q] - mean) * (ov[q] - mean) - mean * mean) : ov[q] * ov[q];
+      ss = warp_sum(ss);
+      rstd = 1.0f / sqrtf(ss * inv_d + a.eps);
+      if (lane == 0) {
+        a.rstd[row] = rstd;
+        if (ln) a.mean[row] = mean;
+      }
+    }
+    float inv_row = 1.f;
+    if (!GROUP) {
+      const float amax = warp_max(pair_max(am2));
+      const bool live = amax > 0.f;
+      inv_row = live ? __fdiv_rn(qmax, amax) : 1.f;
+      if (lane == 0) p.scales[row] = live ? __fdiv_rn(amax, qmax) : 1.f;
+    }
+    // ---- pass 2: norm output and packed codes from the registers
+#pragma unroll
+    for (int r = 0; r < NG; ++r) forget_unpacked(raw[r]);
+    unsigned char* codes_row = p.codes + row * (static_cast<long long>(D) * BITS / 8);
+    __nv_bfloat16* yrow = NORM ? a.y + row * a.row_stride : nullptr;
+#pragma unroll
+    for (int iu = 0; iu < UPL; ++iu) {
+      const int u = lane + 32 * iu;
+      if (u < U) {
+        PackAcc<BITS> acc;
+#pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+          const int col = s * segw + (u << 3);
+          float f[8];
+          unpack_bf16x8(raw[iu * NSEG + s], f);
+          if (NORM) {
+            float y[8], wv[8];
+            load8_split(wsm, D, col, wv);
+            if (ln) {
+              float bv[8];
+              load8_split(bsm, D, col, bv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) y[e] = (f[e] - mean) * rstd * wv[e] + bv[e];
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) y[e] = f[e] * rstd * wv[e];
+            }
+            store8<__nv_bfloat16>(yrow, col, y);
+          }
+          acc.add(f, GROUP ? ginv[iu * NSEG + s] : inv_row, s);
+        }
+        *reinterpret_cast<uint2*>(codes_row + (u << 3)) = acc.done();
+      }
+      // keep the table loads of the next unit behind this unit's stores: hoisting all of them to the top of
+      // the unrolled pass would cost more registers than the raw row itself
+      if (NORM && (iu & 1)) asm volatile("" ::: "memory");
+    }
+    if (NORM) {
+      // the vector stores above wrote the norm of the zeroed value at the outlier channels: order
+      // them before the scalar stores of the real values (same warp, other lanes)
+      __syncwarp();
+#pragma unroll
+      for (int q = 0; q < kWarpOutPerLane; ++q) {
+        if (oc[q] >= 0) {
+          const int cs = split_index(oc[q], D);
+          const float y = ln ? ((ov[q] - mean) * rstd * wsm[cs] + bsm[cs]) : (ov[q] * rstd * wsm[cs]);
+          yrow[oc[q]] = __float2bfloat16_rn(y);
+        }
+      }
+    }
+  }
+}
+
+// The two-record variant of the kernel above: a second record (a.p2, with its own outlier channels) takes the
+// compressed norm OUTPUT -- the sites behind a norm save that tensor, and this way it is compressed in the pass
+// that produces it.  The row body is warp_row_plain, run twice on the warp's slot.  (The one-record kernel
+// keeps its own hand-scheduled body: folding both into one template cost it 15 % at 65 536 rows.)
+template <int BITS, int NK, int NG, bool GROUP>
+__global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_n_warp_dual_kernel(const __grid_constant__ WarpFwdArgs a) {
+  constexpr bool DUAL = true;
   using C = CodeTraits<BITS>;
   constexpr int NSEG = C::kSeg;
   constexpr int UPL = NG / NSEG;
@@ -686,7 +896,7 @@ int launch_fwd_warp_bits(const WarpFwdArgs& a, const WarpPlan& w, bool norm, cud
         }                                                                                       \
       } else if (w.dual) {                                                                      \
         if constexpr (NK != 0) {                                                                \
-          auto kern = fwd_n_warp_kernel<BITS, NK, NG, GROUP, true>;                             \
+          auto kern = fwd_n_warp_dual_kernel<BITS, NK, NG, GROUP>;                             \
           int rc = set_smem(kern, w.total);                                                     \
           if (rc) return rc;                                                                    \
           kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                      \
@@ -694,7 +904,7 @@ int launch_fwd_warp_bits(const WarpFwdArgs& a, const WarpPlan& w, bool norm, cud
           return HYC_ERR_SHAPE;                                                                 \
         }                                                                                       \
       } else {                                                                                  \
-        auto kern = fwd_n_warp_kernel<BITS, NK, NG, GROUP, false>;                              \
+        auto kern = fwd_n_warp_kernel<BITS, NK, NG, GROUP>;                              \
         int rc = set_smem(kern, w.total);                                                       \
         if (rc) return rc;                                                                      \
         kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                        \

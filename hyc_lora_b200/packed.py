@@ -575,7 +575,7 @@ def lora_wgrad_supported(p: Packed, rank: int) -> bool:
             and p.rows > 0)
 
 
-def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False) -> torch.Tensor:
+def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False, path: str = "auto") -> torch.Tensor:
     """``dW[r, D] = sum_t G[t, r] * X_hat[t, d]`` in fp32 from the packed input.
 
     The packed codes go to the dequant-fused tcgen05 kernel (the reconstruction never touches HBM).  Channel
@@ -585,11 +585,19 @@ def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False
     by a second kernel, and a low-rank part adds ``(sum over the batch of G)^T @ lowrank`` here, one small
     library GEMM.  1-bit codes (and ranks the kernel does not take) are rebuilt by the decompress kernel and
     contracted by a library GEMM in bf16 with fp32 accumulation -- the arithmetic of the reference
-    (efficient_linear.py:61-67) followed by the autograd engine's sum over the batch."""
+    (efficient_linear.py:61-67) followed by the autograd engine's sum over the batch.
+
+    ``path``: "tensor" (the tcgen05 kernel where it takes the record), "library" (decompress + GEMM), or "auto":
+    the faster of the two as measured on a B200 -- the tensor-core kernel for channel-mode records (0.13 ms
+    against 0.24 ms at 65 536 x 4 096, rank 64); decompress + GEMM for reference-mode records, whose
+    element-outlier side term (one multiply-add per stored outlier and rank, through shared-memory atomics)
+    costs 0.44 ms + 0.43 ms per million stored outliers against 0.26 ms for the dense route."""
     _require_cuda(grad_output)
     rank = grad_output.shape[-1]
     g = grad_output.reshape(p.rows, rank).to(torch.bfloat16).contiguous()
-    if force_library or not lora_wgrad_supported(p, rank):
+    if path == "auto":
+        path = "library" if p.mode == "R" else "tensor"
+    if force_library or path == "library" or not lora_wgrad_supported(p, rank):
         xh = decompress(p).reshape(p.rows, p.cols)
         return (g.t() @ xh).float()
     rec = p.record()
