@@ -314,6 +314,18 @@ def kernel_list(packed, x, w, channels, k, peak):
             if rows != ROWS or rotate:
                 out.append(graph_timed(lambda i: packed.compress_n(sets[i % n], channels, BITS, 0, rotate, norm=norm),
                                        algorithmic_bytes_per_row(d, BITS, k, 1) * rows, "norm+compress " + tag, peak))
+            # the norm site with the record of its output from the same pass (what a norm in front of LoRA-A linears
+            # runs).  With a rotation the library builds the pair for at most 8192 rows (beyond that two launches are
+            # quicker): that line is taken on the first 4096 rows of each 16384-row set
+            fmt = dict(channels=channels, bits=BITS, group=0, rotate=rotate)
+            if rotate == 0 and rows == ROWS:
+                out.append(graph_timed(lambda i: packed.compress_n(sets[i % n], channels, BITS, 0, rotate, norm=norm, also_output=fmt),
+                                       (algorithmic_bytes_per_row(d, BITS, k, 1) + base) * rows, "norm+compress, two records " + tag, peak))
+            if rotate and rows == 16384:
+                small = [s_[:4096] for s_ in sets]
+                out.append(graph_timed(lambda i: packed.compress_n(small[i % n], channels, BITS, 0, rotate, norm=norm, also_output=fmt),
+                                       (algorithmic_bytes_per_row(d, BITS, k, 1) + base) * 4096,
+                                       f"norm+compress, two records T=4096 b={BITS} rot={rotate}", peak))
             ps = [packed.compress_n(s_, channels, BITS, 0, rotate) for s_ in sets]
             out.append(graph_timed(lambda i: packed.decompress(ps[i % n]), (base + 2 * d) * rows, "decompress " + tag, peak))
             out.append(graph_timed(lambda i: packed.act_bwd("silu", ps[i % n], dys[i % len(dys)]), (base + 4 * d) * rows,
@@ -322,6 +334,41 @@ def kernel_list(packed, x, w, channels, k, peak):
                                    (base + 4 + 4 * d) * rows, "norm_bwd " + tag, peak))
             del ps
         del dys
+    # the sites of the gated MLP at its width (11008 channels, rotation block 64 as the operators pick it there):
+    # activation with both records, product with the record of its second operand and of its result
+    import torch.nn.functional as F
+    from hyc_lora_b200 import synthetic
+    from hyc_lora_b200.operators.compress_function import outlier_channel_count
+    dw, rw = 11008, 8192
+    gates = [(0.25 * synthetic.sweep_activation(rw, dw, FRACTION, salt=50 + i)[0]).to(x.device) for i in range(2)]
+    ups = [synthetic.sweep_activation(rw, dw, FRACTION, salt=60 + i)[0].to(x.device) for i in range(2)]
+    kw = outlier_channel_count(dw, FRACTION)
+    chw = packed.select_channels(packed.channel_absmax(ups[0]), kw)
+    basew = dw * BITS // 8 + 2 * kw + 4
+    fmt = dict(channels=chw, bits=BITS, group=0, rotate=64)
+    tagw = f"T={rw} D={dw} b={BITS} rot=64"
+    out.append(graph_timed(lambda i: packed.compress_n(gates[i % 2], chw, BITS, 0, 64), (2 * dw + basew) * rw, "compress " + tagw, peak))
+    out.append(graph_timed(lambda i: packed.act_compress_n("silu", gates[i % 2], chw, BITS, 0, 64, also_output=fmt),
+                           (4 * dw + 2 * basew) * rw, "silu + two records, one pass " + tagw, peak))
+
+    def silu_separate(i):
+        y = F.silu(gates[i % 2])
+        packed.compress_n(gates[i % 2], chw, BITS, 0, 64)
+        packed.compress_n(y, chw, BITS, 0, 64)
+    rec = graph_timed(silu_separate, (4 * dw + 2 * basew) * rw, "silu + two records, three passes " + tagw, peak)
+    rec["note"] = "same algorithmic bytes; the passes move 8 D + 2 records"
+    out.append(rec)
+    out.append(graph_timed(lambda i: packed.product_compress_n(gates[i % 2], ups[i % 2], chw, BITS, 0, 64, also_output=fmt),
+                           (6 * dw + 2 * basew) * rw, "product + two records, one pass " + tagw, peak))
+
+    def product_separate(i):
+        y = gates[i % 2] * ups[i % 2]
+        packed.compress_n(ups[i % 2], chw, BITS, 0, 64)
+        packed.compress_n(y, chw, BITS, 0, 64)
+    rec = graph_timed(product_separate, (6 * dw + 2 * basew) * rw, "product + two records, three passes " + tagw, peak)
+    rec["note"] = "same algorithmic bytes; the passes move 10 D + 2 records"
+    out.append(rec)
+    del gates, ups
     # the one dense contraction of the path: LoRA-A weight gradient from the packed codes (tensor roofline)
     p = packed.compress_n(x, channels, BITS, 0, 0)
     g = torch.randn(x.shape[0], 64, device=x.device, dtype=torch.bfloat16)
@@ -735,6 +782,20 @@ def run_case(args):
     from hyc_lora_b200.operators import compress_function as cf
     torch.cuda.set_device(0)
     rows = args.rows
+    if args.case == "mlp_sites":
+        # the three one-pass kernels of the gated MLP's sites on bf16 [rows, cols] tensors, `launches` rounds
+        cols = args.cols
+        gate = (0.25 * synthetic.sweep_activation(rows, cols, FRACTION, salt=1)[0]).to("cuda")
+        up = synthetic.sweep_activation(rows, cols, FRACTION, salt=2)[0].to("cuda")
+        ch = packed.select_channels(packed.channel_absmax(gate), cf.outlier_channel_count(cols, FRACTION))
+        fmt = dict(channels=ch, bits=BITS, group=args.group, rotate=args.rotate)
+        for _ in range(args.launches):
+            assert packed.product_compress_n(gate, up, ch, BITS, args.group, args.rotate, also_output=fmt) is not None
+            assert packed.act_compress_n("silu", gate, ch, BITS, args.group, args.rotate, also_output=fmt) is not None
+            packed.compress_n(gate, ch, BITS, args.group, args.rotate)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "rows": rows, "cols": cols, "launches": args.launches}))
+        return
     x = synthetic.sweep_activation(rows, COLS, FRACTION)[0].to("cuda")
     w = synthetic.norm_weight(COLS).to("cuda")
     k = cf.outlier_channel_count(COLS, FRACTION)
@@ -793,6 +854,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="run the training step eagerly instead of from a CUDA graph")
     ap.add_argument("--case", default=None, help="profiling aid: run only this kernel (see run_case)")
     ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--cols", type=int, default=11008, help="--case mlp_sites: row width")
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--group", type=int, default=GROUP)
     ap.add_argument("--rotate", type=int, default=ROTATE)

@@ -557,6 +557,9 @@ inline ChunkPlan plan_chunk_fwd(const hyc_packed* q, const hyc_dense* x, bool no
     if (!norm || q2->mode != HYC_MODE_N || q2->bits != q->bits || q2->group != q->group || q2->rotate != q->rotate ||
         q2->cols != q->cols || q2->rows != q->rows || q2->n_channels > 32 * kWarpOutPerLane)
       return w;
+    // measured (4096 channels, rotation 256; one launch against norm + compress and compress of the output):
+    // 25 against 29 us at 2048 rows, 44 against 50 at 4096, 139 against 138 at 16384, 519 against 463 at 65536
+    if (q2->rotate && q->rows > 8192) return w;
     w.dual = true;
   }
   if (q->mode != HYC_MODE_N || x->dtype != HYC_BF16 || x->chunks != 1 || !q->rotate) return w;
@@ -572,7 +575,8 @@ inline ChunkPlan plan_chunk_fwd(const hyc_packed* q, const hyc_dense* x, bool no
   if (q->rotate > segw || segw % q->rotate) return w;
   if (!tensor_map_encoder()) return w;
   w.ch = ch;
-  const int choices[2] = {q->rows <= 2LL * kChunkWarpsFew * sm_count() ? kChunkWarpsFew : kChunkWarpsMany, kChunkWarpsFew};
+  // (the two-record variant holds more state: its 12-warp build spills and is slower than two launches)
+  const int choices[2] = {(q2 || q->rows <= 2LL * kChunkWarpsFew * sm_count()) ? kChunkWarpsFew : kChunkWarpsMany, kChunkWarpsFew};
   for (int c = 0; c < 2; ++c) {
     const int warps = choices[c];
     uint32_t off = 64 * 8;                                   // two mbarriers per warp

@@ -834,6 +834,7 @@ inline WarpPlan plan_warp_fwd(const hyc_packed* q, const hyc_dense* x, bool norm
     if (!norm || q2->mode != HYC_MODE_N || q2->bits != q->bits || q2->group != q->group || q2->rotate != q->rotate ||
         q2->cols != q->cols || q2->rows != q->rows || q2->n_channels > 32 * kWarpOutPerLane)
       return w;
+    if (q2->rotate && q->rows > 8192) return w;      // with a rotation the pair pays off for few rows only
     w.dual = true;
   }
   if (q->mode != HYC_MODE_N || x->dtype != HYC_BF16 || x->chunks != 1) return w;
