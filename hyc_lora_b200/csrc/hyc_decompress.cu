@@ -1,5 +1,6 @@
 // Packed activation -> bf16 rows.
 #include "hyc_bwd_warp.cuh"
+#include "hyc_bwd_chunk.cuh"
 
 namespace hyc {
 
@@ -76,6 +77,12 @@ int hyc_decompress(const hyc_packed* in, const hyc_dense* o, void* stream_) {
   if (o->dtype != HYC_BF16) return HYC_ERR_DTYPE;
   if (in->rows == 0) return HYC_OK;
   if (o->chunks == 1) {
+    // rotated records whose segment is 32 chunks wide: one warp per row, a chunk of every segment per lane
+    const ChunkBwdPlan cp = plan_chunk_bwd(in, false);
+    if (cp.ok && (o->row_stride * 2) % 16 == 0) {
+      const int rcb = run_chunk_bwd(in, cp, nullptr, o->base, o->row_stride, 0, nullptr, 0, nullptr, nullptr, 0, stream);
+      if (rcb != HYC_ERR_SHAPE) return rcb;
+    }
     // plain output rows of up to 4096 channels: one warp per row
     const WarpBwdPlan wp = plan_warp_bwd(in, nullptr, false, false);
     if (wp.ok) {

@@ -1,5 +1,6 @@
 // Decompress + RMSNorm / LayerNorm backward, with the optional weight / bias gradient.
 #include "hyc_bwd_warp.cuh"
+#include "hyc_bwd_chunk.cuh"
 
 namespace hyc {
 
@@ -168,6 +169,16 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
     return HYC_OK;
   }
   const int D = saved->cols;
+  if (g->dy_dtype == HYC_BF16 && !g->dweight && saved->rotate) {
+    // frozen norm weight, bf16 gradient, rotated record whose segment is 32 chunks wide: one warp per row, a
+    // chunk of every segment per lane (six of the eight butterfly stages inside the lane)
+    const ChunkBwdPlan cp = plan_chunk_bwd(saved, true);
+    if (cp.ok) {
+      const int rcb = run_chunk_bwd(saved, cp, g->dy, g->dx, D, g->kind, g->weight, g->param_dtype == HYC_BF16, g->rstd,
+                                    g->mean, g->ref_compat_c2, stream);
+      if (rcb != HYC_ERR_SHAPE) return rcb;
+    }
+  }
   if (g->dy_dtype == HYC_BF16 && !g->dweight && !saved->rotate) {
     // frozen norm weight (the adapter case), bf16 gradient, no rotation: one warp per row (a rotated record
     // would be rotated back in both of that kernel's passes; the shuffle pipe is its bound, so it stays on

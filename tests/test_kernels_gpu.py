@@ -706,6 +706,48 @@ def test_rotating_forward_one_chunk_per_lane(pk, d, bits, group, rotate, kind, r
     arena.check()
 
 
+@pytest.mark.parametrize("d,bits,group,rotate,kind,rows", [
+    (4096, 4, 0, 256, "rms", 300), (4096, 4, 128, 256, "ln", 4001), (4096, 4, 0, 16, "rms_gemma", 300),
+    (4096, 4, 128, 1024, "rms", 300), (2048, 4, 0, 256, "ln", 300), (2048, 4, 128, 64, "rms", 4001),
+    (4096, 2, 0, 256, "rms", 4001), (4096, 2, 128, 1024, "ln", 300), (4096, 8, 0, 256, "rms", 300),
+    (4096, 8, 128, 4096, "ln", 300), (2048, 8, 0, 1024, "rms", 300), (1024, 8, 128, 256, "rms", 4001)])
+def test_rotated_consumers_one_chunk_per_lane(pk, d, bits, group, rotate, kind, rows):
+    """Decompress of a rotated record equals the oracle's bit for bit; decompress + norm backward (frozen
+    weight, bf16 gradient) is the oracle's within the bf16 tolerance; both write inside their outputs only."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=torch.bfloat16, salt=d + bits + rotate + 5)
+    x[rows // 2] = 0
+    xd = x.to(DEV)
+    k = oc.n_outlier_count(d, 0.01)
+    ch = pk.select_channels(pk.channel_absmax(xd), k)
+    c = oc.n_compress(x, ch.cpu(), bits, group, rotate)
+    xh_o = oc.n_decompress(c)
+    p = pk.compress_n(xd, ch, bits, group, rotate)
+    w = synthetic.norm_weight(d, 0.1, dtype=torch.bfloat16)
+    dy = torch.randn(rows, d, generator=torch.Generator().manual_seed(d + 1)).to(torch.bfloat16)
+    _, mean_o, rstd_o = oc.norm_forward(x, w, torch.zeros(d), 1e-5, kind)
+    arena = _Arena(rows * d * 4 + (1 << 20))
+    xh, dx = arena.take((rows, d), torch.bfloat16), arena.take((rows, d), torch.bfloat16)
+    rec, out = p.record(), _dense(xh, d)
+    _lib.check(_lib.lib.hyc_decompress(C.byref(rec), C.byref(out), pk._stream()), "hyc_decompress")
+    wd, dyd, rstd = w.to(DEV), dy.to(DEV), rstd_o.to(DEV)
+    mean = mean_o.to(DEV) if kind == "ln" else None
+    a = _lib.HycNormBwdArgs()
+    a.kind, a.ref_compat_c2 = pk._NORM_KIND[kind], 1
+    a.weight, a.param_dtype, a.dy, a.dy_dtype = wd.data_ptr(), _lib.HYC_BF16, dyd.data_ptr(), _lib.HYC_BF16
+    a.rstd, a.mean, a.dx = rstd.data_ptr(), (mean.data_ptr() if mean is not None else None), dx.data_ptr()
+    _lib.check(_lib.lib.hyc_norm_bwd(C.byref(rec), C.byref(a), pk._stream()), "hyc_norm_bwd")
+    torch.cuda.synchronize()
+    assert torch.equal(xh.cpu(), xh_o)
+    dx_o, _, _ = oc.norm_backward(xh_o, dy, w, mean_o if kind == "ln" else None, rstd_o, kind)
+    err = (dx.float().cpu() - dx_o.float()).abs().max() / dx_o.float().abs().max()
+    assert err < 1e-2, f"norm backward differs from the oracle ({err:.3e})"
+    assert ((dx.float().cpu() - dx_o.float()).abs() <= 2e-2 * dx_o.float().abs() + 2e-2 * dx_o.float().abs().mean()).all()
+    assert int(p.status.item()) == 0
+    arena.check()
+
+
 WIDE_CASES = [
     # d, bits, group, rotate, rows, outlier fraction
     (11008, 4, 0, 64, 70, 0.01), (11008, 4, 0, 0, 2500, 0.01), (11008, 4, 128, 64, 300, 0.02), (11008, 2, 0, 16, 70, 0.01),
