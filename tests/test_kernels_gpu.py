@@ -748,6 +748,45 @@ def test_rotated_consumers_one_chunk_per_lane(pk, d, bits, group, rotate, kind, 
     arena.check()
 
 
+@pytest.mark.parametrize("d,bits,group,rotate,rows,frac", [
+    (11008, 4, 0, 64, 70, 0.01), (11008, 4, 128, 64, 2500, 0.02), (11008, 2, 0, 16, 70, 0.01), (11008, 8, 128, 64, 70, 0.01),
+    (14336, 4, 0, 256, 70, 0.02), (14336, 2, 128, 16, 300, 0.02), (3072, 8, 128, 256, 70, 0.01), (8192, 4, 0, 256, 300, 0.01),
+    (5120, 4, 128, 64, 70, 0.01), (4096, 4, 0, 256, 2500, 0.01), (4096, 4, 128, 1024, 300, 0.01), (16384, 4, 0, 1024, 70, 0.005)])
+def test_rotated_activation_backward_wide_rows(pk, d, bits, group, rotate, rows, frac):
+    """SiLU / GELU / product backward from rotated records of many widths with a bf16 gradient: the product's two
+    results equal the oracle's bit for bit, the activations' are within the tolerance of the formulas; nothing
+    is written outside the outputs."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    x1, _ = synthetic.sweep_activation(rows, d, frac, dtype=torch.bfloat16, salt=d + bits + 11)
+    x2, _ = synthetic.sweep_activation(rows, d, frac, dtype=torch.bfloat16, salt=d + bits + 12)
+    x1 = 0.25 * x1
+    g = torch.randn(rows, d, generator=torch.Generator().manual_seed(d)).to(torch.bfloat16)
+    k = oc.n_outlier_count(d, frac)
+    recs, xhs = [], []
+    for x in (x1, x2):
+        xd = x.to(DEV)
+        ch = pk.select_channels(pk.channel_absmax(xd), k)
+        recs.append(pk.compress_n(xd, ch, bits, group, rotate))
+        xhs.append(oc.n_decompress(oc.n_compress(x, ch.cpu(), bits, group, rotate)))
+    gd = g.to(DEV)
+    arena = _Arena(rows * d * 10 + (1 << 20))
+    outs = [arena.take((rows, d), torch.bfloat16) for _ in range(4)]
+    r1, r2 = recs[0].record(), recs[1].record()
+    for op, o1, o2 in ((_lib.HYC_ACT_SILU, outs[0], None), (_lib.HYC_ACT_GELU_TANH, outs[1], None),
+                       (_lib.HYC_ACT_PRODUCT, outs[2], outs[3])):
+        _lib.check(_lib.lib.hyc_act_bwd(op, C.byref(r1), C.byref(r2) if o2 is not None else None, gd.data_ptr(), _lib.HYC_BF16,
+                                        o1.data_ptr(), o2.data_ptr() if o2 is not None else None, pk._stream()), "hyc_act_bwd")
+    torch.cuda.synchronize()
+    s_o, g_o = oc.silu_backward(xhs[0], g), oc.gelu_backward(xhs[0], g)
+    assert ((outs[0].float().cpu() - s_o.float()).abs() <= 1e-2 * s_o.float().abs() + 1e-4).all()
+    assert ((outs[1].float().cpu() - g_o.float()).abs() <= 1e-2 * g_o.float().abs() + 1e-4).all()
+    p1_o, p2_o = oc.product_backward(xhs[0], xhs[1], g)
+    assert torch.equal(outs[2].cpu(), p1_o) and torch.equal(outs[3].cpu(), p2_o)
+    assert int(recs[0].status.item()) == 0 and int(recs[1].status.item()) == 0
+    arena.check()
+
+
 WIDE_CASES = [
     # d, bits, group, rotate, rows, outlier fraction
     (11008, 4, 0, 64, 70, 0.01), (11008, 4, 0, 0, 2500, 0.01), (11008, 4, 128, 64, 300, 0.02), (11008, 2, 0, 16, 70, 0.01),
