@@ -166,6 +166,45 @@ __device__ __forceinline__ void store8<float>(float* row, int col, const float (
   *reinterpret_cast<float4*>(row + col + 4) = make_float4(f[4], f[5], f[6], f[7]);
 }
 
+// ---------------------------------------------------------------- packed fp32 pairs
+
+// Two fp32 values in one 64-bit register pair, for the packed fp32 instructions of sm_100
+// (add / sub / mul / fma .f32x2: two IEEE operations, round to nearest even, per issue slot).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_make(float lo, float hi) {
+  f32x2 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void f2_split(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_sub(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+// the eight bf16 values of a 16-byte piece as four fp32 pairs
+__device__ __forceinline__ void unpack_bf16x8_pairs(const uint4& w, f32x2 (&f)[4]) {
+  f[0] = f2_make(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u));
+  f[1] = f2_make(__uint_as_float(w.y << 16), __uint_as_float(w.y & 0xffff0000u));
+  f[2] = f2_make(__uint_as_float(w.z << 16), __uint_as_float(w.z & 0xffff0000u));
+  f[3] = f2_make(__uint_as_float(w.w << 16), __uint_as_float(w.w & 0xffff0000u));
+}
+
 // ---------------------------------------------------------------- reductions
 
 struct OpSum {

@@ -2,10 +2,14 @@
 and ONE exchange step -- the sum of the trainable (LoRA) gradients -- on NCCL.
 
 The gradients of all trainable parameters live in a single flat fp32 buffer (each ``.grad`` is
-a view into it), so the exchange is one large all-reduce that NCCL can run through NVSwitch
-(in-switch reduction when available) instead of hundreds of small ones.  Nothing else on the
-compression path communicates: every kernel is rank-local and calibration state stays per
-rank, as in the reference (its DDP comes implicitly from the HF Trainer)."""
+a view into it), so the exchange is a few large all-reduces that NCCL can run through NVSwitch
+(in-switch reduction when available) instead of hundreds of small ones.  With ``overlap=True`` the
+buffer is cut into buckets (64 MB by default) and a bucket's all-reduce is enqueued, asynchronously,
+the moment backward has accumulated the last gradient that lives in it, so the exchange of the later
+layers' gradients runs under the backward pass of the earlier ones; ``comm_dtype=torch.bfloat16``
+halves the bytes on the wire (the sum is then a bf16 sum).  Nothing else on the compression path
+communicates: every kernel is rank-local and calibration state stays per rank, as in the reference
+(its DDP comes implicitly from the HF Trainer)."""
 from __future__ import annotations
 
 from typing import Iterable, List
@@ -15,7 +19,8 @@ import torch.distributed as dist
 
 
 class FlatGradSync:
-    def __init__(self, params: Iterable[torch.nn.Parameter], average: bool = True, dtype=None):
+    def __init__(self, params: Iterable[torch.nn.Parameter], average: bool = True, dtype=None, overlap: bool = False,
+                 bucket_bytes: int = 64 << 20, comm_dtype=None):
         self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
         if not self.params:
             raise ValueError("no trainable parameters to synchronise")
@@ -30,6 +35,50 @@ class FlatGradSync:
             p.grad = self.flat[off:off + n].view_as(p) if dtype == p.dtype else None
             off += n
         self._views = dtype == self.params[0].dtype and all(p.dtype == dtype for p in self.params)
+        self.comm_dtype = comm_dtype
+        # buckets: runs of whole parameters, in parameter order, of at least bucket_bytes each
+        self.buckets, self._bucket_of = [], []
+        start = off = 0
+        members = []
+        for i, p in enumerate(self.params):
+            members.append(i)
+            off += p.numel()
+            if (off - start) * self.flat.element_size() >= bucket_bytes or i == len(self.params) - 1:
+                self.buckets.append((start, off, members))
+                self._bucket_of += [len(self.buckets) - 1] * len(members)
+                start, members = off, []
+        self.overlap = bool(overlap) and self._views
+        self._pending, self._works, self._launched = [], [], []
+        if self.overlap:
+            for i, p in enumerate(self.params):
+                p.register_post_accumulate_grad_hook(lambda _p, i=i: self._ready(i))
+
+    def _active(self) -> bool:
+        return dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+
+    def begin(self):
+        """Call before backward (overlap mode): every bucket waits for all of its gradients again."""
+        self._pending = [len(m) for _, _, m in self.buckets]
+        self._launched = [False] * len(self.buckets)
+        self._works = []
+
+    def _ready(self, i: int):
+        if not self._pending or not self._active():
+            return
+        b = self._bucket_of[i]
+        self._pending[b] -= 1
+        if self._pending[b] == 0 and not self._launched[b]:
+            self._launch(b)
+
+    def _launch(self, b: int):
+        s, e, _ = self.buckets[b]
+        self._launched[b] = True
+        piece = self.flat[s:e]
+        if self.comm_dtype is not None and self.comm_dtype != piece.dtype:
+            wire = piece.to(self.comm_dtype)
+            self._works.append((dist.all_reduce(wire, op=dist.ReduceOp.SUM, async_op=True), piece, wire))
+        else:
+            self._works.append((dist.all_reduce(piece, op=dist.ReduceOp.SUM, async_op=True), None, None))
 
     def numel(self) -> int:
         return self.flat.numel()
@@ -55,7 +104,20 @@ class FlatGradSync:
 
     def sync(self, async_op: bool = False):
         """All-reduce the flat gradient buffer (sum, then divide by the world size)."""
-        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        if not self._active():
+            return None
+        if self.overlap and self._pending:
+            # buckets whose parameters got no gradient this step have not been sent yet
+            for b in range(len(self.buckets)):
+                if not self._launched[b]:
+                    self._launch(b)
+            for work, piece, wire in self._works:
+                work.wait()
+                if wire is not None:
+                    piece.copy_(wire)
+            self._works, self._pending = [], []
+            if self.average:
+                self.flat.div_(dist.get_world_size())
             return None
         self._gather_into_flat()
         if self.average:

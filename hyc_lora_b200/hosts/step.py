@@ -27,7 +27,7 @@ class Trainer:
     def __init__(self, model, lr: float = 1e-4):
         self.model = model
         self.params = lora_parameters(model)
-        self.sync = FlatGradSync(self.params)
+        self.sync = FlatGradSync(self.params, overlap=True)
         self.opt = torch.optim.AdamW(self.params, lr=lr, fused=True, capturable=True)
         self.graph = None
         self.static_ids = None
@@ -40,6 +40,7 @@ class Trainer:
     def _step(self, ids: torch.Tensor) -> torch.Tensor:
         self.sync.zero()
         loss = self.model(ids)
+        self.sync.begin()                    # buckets of the flat gradient go out as backward completes them
         loss.backward()
         self.sync.sync()
         self.opt.step()

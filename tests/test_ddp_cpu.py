@@ -27,17 +27,22 @@ class _Tiny(torch.nn.Module):
         return ((x @ self.base.t() + x @ self.lora_A.t() @ self.lora_B.t()) ** 2).mean()
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, overlap=False, comm_dtype=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from hyc_lora_b200.ddp import FlatGradSync
     model = _Tiny()
-    sync = FlatGradSync(model.parameters())
-    assert sync.numel() == 4 * 24 * 2
+    # overlap: one bucket per parameter (the buckets go out from the gradient hooks, during backward)
+    sync = FlatGradSync(model.parameters(), overlap=overlap, bucket_bytes=64 if overlap else 64 << 20, comm_dtype=comm_dtype)
+    assert sync.numel() == 4 * 24 * 2 and len(sync.buckets) == (2 if overlap else 1)
     x = torch.randn(8, 24, generator=torch.Generator().manual_seed(9))
     for step in range(2):                       # second step: the flat buffer is reused after zero()
         sync.zero()
-        model(x[rank * 4:(rank + 1) * 4]).backward()
+        loss = model(x[rank * 4:(rank + 1) * 4])
+        sync.begin()
+        loss.backward()
+        if overlap:
+            assert all(sync._launched)          # every bucket was sent by a hook before sync()
         sync.sync()
     if rank == 0:
         out.put((model.lora_A.grad.clone(), model.lora_B.grad.clone()))
@@ -45,11 +50,15 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_flat_gradient_allreduce_matches_single_process():
+import pytest
+
+
+@pytest.mark.parametrize("overlap,comm_dtype,atol", [(False, None, 1e-6), (True, None, 1e-6), (True, torch.bfloat16, 2e-3)])
+def test_flat_gradient_allreduce_matches_single_process(overlap, comm_dtype, atol):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out, overlap, comm_dtype)) for r in range(2)]
     for p in procs:
         p.start()
     ga, gb = out.get(timeout=120)
@@ -60,7 +69,7 @@ def test_flat_gradient_allreduce_matches_single_process():
     x = torch.randn(8, 24, generator=torch.Generator().manual_seed(9))
     # each rank's loss is the mean over ITS shard; averaging the ranks gives the mean over the batch
     (0.5 * ref(x[:4]) + 0.5 * ref(x[4:])).backward()
-    assert torch.allclose(ga, ref.lora_A.grad, atol=1e-6) and torch.allclose(gb, ref.lora_B.grad, atol=1e-6)
+    assert torch.allclose(ga, ref.lora_A.grad, atol=atol) and torch.allclose(gb, ref.lora_B.grad, atol=atol)
 
 
 def test_flat_buffer_views_and_single_process_noop():

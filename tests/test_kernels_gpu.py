@@ -787,6 +787,34 @@ def test_rotated_activation_backward_wide_rows(pk, d, bits, group, rotate, rows,
     arena.check()
 
 
+def test_chunk_and_wide_kernels_without_outlier_channels(pk):
+    """No outlier channels at all (ratio 0): the rotating forward, its two-record variant, the rotated consumers
+    and the one-pass activation / product sites."""
+    rows, d, bits, rotate = 300, 4096, 4, 256
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=torch.bfloat16, salt=77)
+    xd = x.to(DEV)
+    w = synthetic.norm_weight(d, 0.1, dtype=torch.bfloat16).to(DEV)
+    none = torch.empty(0, dtype=torch.int32)
+    c = oc.n_compress(x, none, bits, 0, rotate)
+    p = pk.compress_n(xd, None, bits, 0, rotate)
+    assert torch.equal(p.codes.cpu(), c.codes) and torch.equal(p.scales.cpu(), c.scales)
+    assert torch.equal(pk.decompress(p).cpu().reshape(rows, d), oc.n_decompress(c))
+    norm = dict(kind="rms", weight=w, bias=None, eps=1e-5)
+    px, y, rstd, _, py = pk.compress_n(xd, None, bits, 0, rotate, norm=norm, also_output=dict(channels=None, bits=bits, group=0, rotate=rotate))
+    assert py is not None and torch.equal(px.codes, p.codes)
+    assert torch.equal(py.codes.cpu(), oc.n_compress(y.cpu(), none, bits, 0, rotate).codes)
+    dy = torch.randn(rows, d, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    dx, _, _ = pk.norm_bwd(p, dy.to(DEV), w, rstd, None, "rms")
+    dx_o, _, _ = oc.norm_backward(oc.n_decompress(c), dy, w.cpu(), None, rstd.cpu(), "rms")
+    assert (dx.float().cpu() - dx_o.float()).abs().max() / dx_o.float().abs().max() < 1e-2
+    fmt = dict(channels=None, bits=bits, group=0, rotate=64)
+    pg, act, pa = pk.act_compress_n("silu", xd, None, bits, 0, 64, also_output=fmt)
+    assert torch.equal(pg.codes.cpu(), oc.n_compress(x, none, bits, 0, 64).codes)
+    assert torch.equal(pa.codes.cpu(), oc.n_compress(act.cpu(), none, bits, 0, 64).codes)
+    pu, prod, pp = pk.product_compress_n(act, xd, None, bits, 0, 64, also_output=fmt)
+    assert torch.equal(prod, act * xd) and torch.equal(pp.codes.cpu(), oc.n_compress(prod.cpu(), none, bits, 0, 64).codes)
+
+
 WIDE_CASES = [
     # d, bits, group, rotate, rows, outlier fraction
     (11008, 4, 0, 64, 70, 0.01), (11008, 4, 0, 0, 2500, 0.01), (11008, 4, 128, 64, 300, 0.02), (11008, 2, 0, 16, 70, 0.01),
