@@ -39,6 +39,7 @@ static int run_wide(int op, const hyc_dense* x, const hyc_dense* x2, void* y, co
   wa.off_chan = wp.off_chan; wa.off_chan2 = wp.off_chan2; wa.off_red = wp.off_red;
   wa.off_slots = wp.off_slots; wa.slot_stride = wp.slot_stride;
   wa.wait_cycles = g_debug_wait_cycles > 0 ? g_debug_wait_cycles : kWaitCycles;
+  wa.tx_pad = g_debug_tx_pad;
   return launch_wide(wa, wp, op, m0, m1, m2, stream);
 }
 
@@ -128,6 +129,7 @@ static int run_fwd(const hyc_dense* x, const hyc_norm_fwd* norm, const hyc_packe
       ca.off_chan = cp.off_chan; ca.off_chan2 = cp.off_chan2; ca.off_wsm = cp.off_wsm; ca.off_bsm = cp.off_bsm;
       ca.off_slots = cp.off_slots; ca.slot_bytes = cp.slot_bytes;
       ca.wait_cycles = g_debug_wait_cycles > 0 ? g_debug_wait_cycles : kWaitCycles;
+      ca.tx_pad = g_debug_tx_pad;
       return out->bits == 2 ? launch_fwd_chunk_b2(ca, cp, norm != nullptr, in_map, y_map, stream)
            : out->bits == 4 ? launch_fwd_chunk_b4(ca, cp, norm != nullptr, in_map, y_map, stream)
                             : launch_fwd_chunk_b8(ca, cp, norm != nullptr, in_map, y_map, stream);

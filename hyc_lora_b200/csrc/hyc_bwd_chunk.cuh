@@ -36,6 +36,7 @@ struct ChunkBwdArgs {
   int ref_compat_c2;
   uint32_t off_chan, off_wsm, off_slots, slot_bytes;
   long long wait_cycles;
+  uint32_t tx_pad;       // test hook: bytes announced beyond what a copy brings (0 in normal use)
 };
 
 // codes of one 8-channel unit pair -> (code - offset) * scale as fp32 pairs, for segment s
@@ -119,7 +120,7 @@ bwd_n_chunk_kernel(const __grid_constant__ ChunkBwdArgs a, const __grid_constant
     for (int s = 0; s < 2; ++s) {
       const int r = row + s * stride;
       if (r < rows) {
-        mbar_expect_tx(&bar2[s], row_bytes);
+        mbar_expect_tx(&bar2[s], row_bytes + a.tx_pad);
         tensor_load_row(gslots + s * a.slot_bytes, &dy_map, r, &bar2[s]);
       }
     }
@@ -281,7 +282,7 @@ bwd_n_chunk_kernel(const __grid_constant__ ChunkBwdArgs a, const __grid_constant
       const int next = row + 2 * stride;
       if (lane == 0 && next < rows) {
         fence_proxy_async();
-        mbar_expect_tx(bar, row_bytes);
+        mbar_expect_tx(bar, row_bytes + a.tx_pad);
         tensor_load_row(gslot, &dy_map, next, bar);
       }
       // the vector stores above come before the outlier channels' results (other lanes)
@@ -391,6 +392,7 @@ inline int run_chunk_bwd(const hyc_packed* q, const ChunkBwdPlan& w, const void*
   a.kind = kind; a.weight = weight; a.param_bf16 = param_bf16; a.rstd = rstd; a.mean = mean; a.ref_compat_c2 = ref_compat_c2;
   a.off_chan = w.off_chan; a.off_wsm = w.off_wsm; a.off_slots = w.off_slots; a.slot_bytes = w.slot_bytes;
   a.wait_cycles = g_debug_wait_cycles > 0 ? g_debug_wait_cycles : kWaitCycles;
+  a.tx_pad = g_debug_tx_pad;
   const int op = !dy ? kChunkDecompress : kind == HYC_NORM_LAYER ? kChunkNormBwdLn : kChunkNormBwdRms;
   return q->bits == 2 ? launch_bwd_chunk_b2(a, w, op, dy_map, out_map, stream)
        : q->bits == 4 ? launch_bwd_chunk_b4(a, w, op, dy_map, out_map, stream)

@@ -44,6 +44,7 @@ struct ChunkFwdArgs {
   float* mean;
   uint32_t off_chan, off_chan2, off_wsm, off_bsm, off_slots, slot_bytes;
   long long wait_cycles;
+  uint32_t tx_pad;       // test hook: bytes announced beyond what a copy brings (0 in normal use)
 };
 
 // Byte offset, inside a staged row, of the 16-byte piece that holds channels e..e+7 (e a multiple of 8).
@@ -278,7 +279,7 @@ fwd_n_chunk_kernel(const __grid_constant__ ChunkFwdArgs a, const __grid_constant
     for (int s = 0; s < 2; ++s) {
       const int r = row + s * stride;
       if (r < rows) {
-        mbar_expect_tx(&bar2[s], row_bytes);
+        mbar_expect_tx(&bar2[s], row_bytes + a.tx_pad);
         tensor_load_row(slots + s * a.slot_bytes, &in_map, r, &bar2[s]);
       }
     }
@@ -321,7 +322,7 @@ fwd_n_chunk_kernel(const __grid_constant__ ChunkFwdArgs a, const __grid_constant
       __syncwarp();
       if (lane == 0 && next < rows) {
         fence_proxy_async();
-        mbar_expect_tx(bar, row_bytes);
+        mbar_expect_tx(bar, row_bytes + a.tx_pad);
         tensor_load_row(slot, &in_map, next, bar);
       }
       chunk_unpack_rotate<NSEG, CH>(raw, v, p.rotate, lane);
@@ -471,7 +472,7 @@ fwd_n_chunk_kernel(const __grid_constant__ ChunkFwdArgs a, const __grid_constant
         bulk_wait_read();
         if (next < rows) {
           fence_proxy_async();
-          mbar_expect_tx(bar, row_bytes);
+          mbar_expect_tx(bar, row_bytes + a.tx_pad);
           tensor_load_row(slot, &in_map, next, bar);
         }
       }

@@ -32,6 +32,7 @@ struct WideArgs {
   int lanes;             // chunks per segment = lanes at work on a row (D / 128)
   uint32_t off_chan, off_chan2, off_red, off_slots, slot_stride;
   long long wait_cycles;
+  uint32_t tx_pad;       // test hook: bytes announced beyond what a copy brings (0 in normal use)
 };
 
 template <int WPR>
@@ -215,16 +216,16 @@ fwd_n_wide_kernel(const __grid_constant__ WideArgs a, const __grid_constant__ CU
   if (leader) {
     if (PROD) {
       if (row < rows) {
-        mbar_expect_tx(&bar2[0], row_bytes);
+        mbar_expect_tx(&bar2[0], row_bytes + a.tx_pad);
         tensor_load_row(slots, &in_map, row, &bar2[0]);
-        mbar_expect_tx(&bar2[1], row_bytes);
+        mbar_expect_tx(&bar2[1], row_bytes + a.tx_pad);
         tensor_load_row(slots + a.slot_stride, &in2_map, row, &bar2[1]);
       }
     } else {
       for (int s = 0; s < 2; ++s) {
         const int r = row + s * stride;
         if (r < rows) {
-          mbar_expect_tx(&bar2[s], row_bytes);
+          mbar_expect_tx(&bar2[s], row_bytes + a.tx_pad);
           tensor_load_row(slots + s * a.slot_stride, &in_map, r, &bar2[s]);
         }
       }
@@ -275,7 +276,7 @@ fwd_n_wide_kernel(const __grid_constant__ WideArgs a, const __grid_constant__ CU
       group_sync<WPR>(group);
       if (leader && next < rows) {
         fence_proxy_async();
-        mbar_expect_tx(bar, row_bytes);
+        mbar_expect_tx(bar, row_bytes + a.tx_pad);
         tensor_load_row(slot, PROD ? &in2_map : &in_map, next, bar);
       }
     }
@@ -354,7 +355,7 @@ fwd_n_wide_kernel(const __grid_constant__ WideArgs a, const __grid_constant__ CU
         if (next < rows) {
           fence_proxy_async();
           uint64_t* ybar = PROD ? &bar2[0] : bar;
-          mbar_expect_tx(ybar, row_bytes);
+          mbar_expect_tx(ybar, row_bytes + a.tx_pad);
           tensor_load_row(yslot, &in_map, next, ybar);
         }
       }

@@ -1065,6 +1065,77 @@ def test_status_poll_reports_a_pool_overflow_without_blocking(pk):
     assert pk.default_pool_entries(128, 768, 0.01) == before and pk.poll_status(wait=True) == 0
 
 
+def test_expired_wait_in_the_tensor_copy_kernels(pk):
+    """The same give-up path in the kernels that stage rows by tensor copies (rotating forward, its consumers,
+    the wide-row sites with one and with three warps per row, where the warps of a row decide together):
+    every call returns 0, every record carries HYC_STATUS_WAIT_EXPIRED, nothing is written outside the
+    outputs, and the next ordinary calls are exact."""
+    import ctypes as C
+    from hyc_lora_b200 import _lib
+    rows = 96
+    pk.reset_status()
+    cases = []
+    for d, rotate in ((4096, 256), (11008, 64)):
+        x, _ = synthetic.sweep_activation(rows, d, 0.01, dtype=torch.bfloat16, salt=d)
+        xd = (0.25 * x).to(DEV)
+        ch = pk.select_channels(pk.channel_absmax(xd), oc.n_outlier_count(d, 0.01))
+        cases.append((d, rotate, xd, ch))
+    d0, r0, x0, ch0 = cases[0]
+    w = synthetic.norm_weight(d0, 0.1, dtype=torch.bfloat16).to(DEV)
+    good = pk.compress_n(x0, ch0, 4, 0, r0)
+    want_dec = pk.decompress(good).reshape(rows, d0).clone()
+    dy = torch.randn(rows, d0, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
+    rstd = torch.ones(rows, device=DEV)
+    want_dx, _, _ = pk.norm_bwd(good, dy, w, rstd, None, "rms")
+    arena = _Arena(rows * 11008 * 16 + (1 << 20))
+    flagged = []
+    assert _lib.lib.hyc_debug_wait(2_000_000, 16) == 0
+    try:
+        # rotating forward with the norm fused, and the norm backward of a rotated record
+        pa = _packed_n_in(arena, pk, rows, d0, 4, 0, r0, ch0)
+        y, rs_ = arena.take((rows, d0), torch.bfloat16), arena.take((rows,), torch.float32)
+        n = _lib.HycNormFwd()
+        n.kind, n.eps = pk._NORM_KIND["rms"], 1e-5
+        n.weight, n.bias, n.param_dtype = w.data_ptr(), None, _lib.HYC_BF16
+        n.y, n.rstd, n.mean = y.data_ptr(), rs_.data_ptr(), None
+        ra, dn = pa.record(), _dense(x0, d0)
+        rcs = [_lib.lib.hyc_norm_compress(C.byref(dn), C.byref(n), C.byref(ra), pk._stream())]
+        flagged.append(pa)
+        dx = arena.take((rows, d0), torch.bfloat16)
+        a = _lib.HycNormBwdArgs()
+        a.kind, a.ref_compat_c2 = _lib.HYC_NORM_RMS, 1
+        a.weight, a.param_dtype, a.dy, a.dy_dtype = w.data_ptr(), _lib.HYC_BF16, dy.data_ptr(), _lib.HYC_BF16
+        a.rstd, a.mean, a.dx = rstd.data_ptr(), None, dx.data_ptr()
+        rg = good.record()
+        rcs.append(_lib.lib.hyc_norm_bwd(C.byref(rg), C.byref(a), pk._stream()))
+        flagged.append(good)
+        # the one-pass sites, one warp per row and three warps per row
+        for d, rotate, xd, ch in cases:
+            px = _packed_n_in(arena, pk, rows, d, 4, 0, rotate, ch)
+            py = _packed_n_in(arena, pk, rows, d, 4, 0, rotate, ch)
+            out = arena.take((rows, d), torch.bfloat16)
+            rx, ry, dd = px.record(), py.record(), _dense(xd, d)
+            rcs.append(_lib.lib.hyc_act_compress(C.byref(dd), _lib.HYC_ACT_SILU, out.data_ptr(), C.byref(rx), C.byref(ry), pk._stream()))
+            rcs.append(_lib.lib.hyc_product_compress(C.byref(dd), C.byref(dd), out.data_ptr(), C.byref(rx), C.byref(ry), pk._stream()))
+            flagged.append(px)
+        torch.cuda.synchronize()
+    finally:
+        assert _lib.lib.hyc_debug_wait(0, 0) == 0
+    assert rcs == [0] * len(rcs)
+    for p in flagged:
+        assert p.wait_expired()
+    arena.check()
+    with pytest.raises(RuntimeError, match="WAIT_EXPIRED"):
+        pk.poll_status(wait=True)
+    good.status.zero_()
+    pk.reset_status()
+    again = pk.compress_n(x0, ch0, 4, 0, r0)
+    assert torch.equal(again.codes, good.codes) and torch.equal(pk.decompress(good).reshape(rows, d0), want_dec)
+    assert torch.equal(pk.norm_bwd(good, dy, w, rstd, None, "rms")[0], want_dx)
+    assert pk.act_compress_n("silu", cases[1][2], cases[1][3], 4, 0, 64) is not None
+    assert not good.wait_expired() and pk.poll_status(wait=True) == 0
+
+
 def test_expired_wait_is_reported_and_leaves_the_device_usable(pk):
     """The give-up path of the bounded waits, made to run without any fault: through the test hook every
     staged row of the consumer kernels announces 16 bytes more than it copies and waits end after about a
