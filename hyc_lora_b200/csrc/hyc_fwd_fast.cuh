@@ -77,23 +77,6 @@ struct PackAcc {
       else w1 += bits << pack_shift<BITS>(s, e);
     }
   }
-  // the same from four fp32 pairs: one packed multiply-add per pair
-  __device__ __forceinline__ void add_pairs(const f32x2 (&f)[4], float inv, int s) {
-    const float magic = kRoundMagic + static_cast<float>(BITS == 8 ? 128 : CodeTraits<BITS>::kOff);
-    const f32x2 inv2 = f2_make(inv, inv), magic2 = f2_make(magic, magic);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float lo, hi;
-      f2_split(f2_fma(f[e], inv2, magic2), lo, hi);
-      if (e < 2) {
-        w0 += __float_as_uint(lo) << pack_shift<BITS>(s, 2 * e);
-        w0 += __float_as_uint(hi) << pack_shift<BITS>(s, 2 * e + 1);
-      } else {
-        w1 += __float_as_uint(lo) << pack_shift<BITS>(s, 2 * e);
-        w1 += __float_as_uint(hi) << pack_shift<BITS>(s, 2 * e + 1);
-      }
-    }
-  }
   __device__ __forceinline__ uint2 done() const {
     return BITS == 8 ? make_uint2(w0 ^ 0x80808080u, w1 ^ 0x80808080u) : make_uint2(w0, w1);
   }

@@ -264,7 +264,7 @@ __device__ __forceinline__ void warp_row_plain(const WarpFwdArgs& a, const Packe
 
 // NK: 0 compress only, 1 RMSNorm (plain or Gemma), 2 LayerNorm;  NG: 16-byte register groups per lane
 // (units per lane x segments)
-template <int BITS, int NK, int NG, bool GROUP, bool PAIRS>
+template <int BITS, int NK, int NG, bool GROUP>
 __global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_n_warp_kernel(const __grid_constant__ WarpFwdArgs a) {
   using C = CodeTraits<BITS>;
   constexpr int NSEG = C::kSeg;
@@ -371,26 +371,11 @@ __global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_
       for (int r = 0; r < NG; ++r) forget_unpacked(raw[r]);
     }
     float ss = 0.f;
-    f32x2 ss2 = f2_make(0.f, 0.f);
-    const f32x2 mean2 = f2_make(mean, mean);
     __nv_bfloat162 am2 = __float2bfloat162_rn(0.f);
     float ginv[GROUP ? NG : 1];
 #pragma unroll
     for (int r = 0; r < NG; ++r) {
-      if (NORM && PAIRS) {
-        // packed fp32 pairs: two fused multiply-adds per issue slot
-        f32x2 f[4];
-        unpack_bf16x8_pairs(raw[r], f);
-        if (ln) {
-          if ((lane + 32 * (r / NSEG)) < U) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { const f32x2 c = f2_sub(f[e], mean2); ss2 = f2_fma(c, c, ss2); }
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) ss2 = f2_fma(f[e], f[e], ss2);
-        }
-      } else if (NORM) {
+      if (NORM) {
         float f[8];
         unpack_bf16x8(raw[r], f);
         if (ln) {
@@ -415,11 +400,6 @@ __global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_
     if constexpr (GROUP) group_scales<BITS, NG>(ginv, p.scales + row * G, segw, U, lane);
     float rstd = 0.f;
     if (NORM) {
-      if (PAIRS) {
-        float lo, hi;
-        f2_split(ss2, lo, hi);
-        ss = lo + hi;
-      }
       // the zeroed outlier channels still belong to the row statistics
 #pragma unroll
       for (int q = 0; q < kWarpOutPerLane; ++q)
@@ -451,38 +431,6 @@ __global__ void __launch_bounds__(kWarpKernelThreads, kWarpKernelCtasPerSm) fwd_
 #pragma unroll
         for (int s = 0; s < NSEG; ++s) {
           const int col = s * segw + (u << 3);
-          if (PAIRS) {
-            f32x2 f[4];
-            unpack_bf16x8_pairs(raw[iu * NSEG + s], f);
-            if (NORM) {
-              const ulonglong2 w0 = *reinterpret_cast<const ulonglong2*>(wsm + ((col >> 3) << 2));
-              const ulonglong2 w1 = *reinterpret_cast<const ulonglong2*>(wsm + (D >> 1) + ((col >> 3) << 2));
-              const f32x2 wv[4] = {w0.x, w0.y, w1.x, w1.y};
-              const f32x2 rstd2 = f2_make(rstd, rstd);
-              uint32_t y[4];
-              if (ln) {
-                const ulonglong2 b0 = *reinterpret_cast<const ulonglong2*>(bsm + ((col >> 3) << 2));
-                const ulonglong2 b1 = *reinterpret_cast<const ulonglong2*>(bsm + (D >> 1) + ((col >> 3) << 2));
-                const f32x2 bv[4] = {b0.x, b0.y, b1.x, b1.y};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float lo, hi;
-                  f2_split(f2_fma(f2_mul(f2_sub(f[e], mean2), rstd2), wv[e], bv[e]), lo, hi);
-                  y[e] = pack_bf16x2(lo, hi);
-                }
-              } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float lo, hi;
-                  f2_split(f2_mul(f2_mul(f[e], rstd2), wv[e]), lo, hi);
-                  y[e] = pack_bf16x2(lo, hi);
-                }
-              }
-              *reinterpret_cast<uint4*>(yrow + col) = make_uint4(y[0], y[1], y[2], y[3]);
-            }
-            acc.add_pairs(f, GROUP ? ginv[iu * NSEG + s] : inv_row, s);
-            continue;
-          }
           float f[8];
           unpack_bf16x8(raw[iu * NSEG + s], f);
           if (NORM) {
@@ -957,9 +905,7 @@ int launch_fwd_warp_bits(const WarpFwdArgs& a, const WarpPlan& w, bool norm, cud
           return HYC_ERR_SHAPE;                                                                 \
         }                                                                                       \
       } else {                                                                                  \
-        /* packed fp32 pairs where they measured faster: group scales (65536 x 4096: 0.225 against */   \
-        /* 0.235 ms); with one scale per row the scalar form is (0.220 against 0.242 ms)           */   \
-        auto kern = fwd_n_warp_kernel<BITS, NK, NG, GROUP, GROUP>;                              \
+        auto kern = fwd_n_warp_kernel<BITS, NK, NG, GROUP>;                              \
         int rc = set_smem(kern, w.total);                                                       \
         if (rc) return rc;                                                                      \
         kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                        \
