@@ -78,8 +78,10 @@ __device__ __forceinline__ uint32_t f2_to_bf16x2(f32x2 v, f32x2& rounded) {
   return b;
 }
 
+// (decompress needs nothing row-wide: it rebuilds and stores one segment's chunk at a time -- with two or four
+// segments that is 64 or 32 fp32 values in flight instead of 128, and two CTAs share an SM)
 template <int BITS, int OP, int CH, bool GROUP>
-__global__ void __launch_bounds__(kChunkBwdWarps * 32, 1)
+__global__ void __launch_bounds__(kChunkBwdWarps * 32, (OP == kChunkDecompress && BITS < 8) ? 2 : 1)
 bwd_n_chunk_kernel(const __grid_constant__ ChunkBwdArgs a, const __grid_constant__ CUtensorMap dy_map,
                    const __grid_constant__ CUtensorMap out_map) {
   using C = CodeTraits<BITS>;
@@ -172,9 +174,8 @@ bwd_n_chunk_kernel(const __grid_constant__ ChunkBwdArgs a, const __grid_constant
     const float rstd = rstd_nxt, mean = mean_nxt;
     if (row + stride < rows) fetch(row + stride);
     // ---- rebuild the lane's share: dequantise, rotate back, round to bf16
-    f32x2 v[NSEG][CH / 2];
-#pragma unroll
-    for (int s = 0; s < NSEG; ++s) {
+    f32x2 v[NORMB ? NSEG : 1][CH / 2];
+    auto rebuild = [&](int s, f32x2 (&vs)[CH / 2]) {
       const float scs = __fmul_rn(sc[s], rs);                 // exact: rs is a power of two
       const f32x2 sc2 = f2_make(scs, scs);
 #pragma unroll
@@ -182,22 +183,39 @@ bwd_n_chunk_kernel(const __grid_constant__ ChunkBwdArgs a, const __grid_constant
         f32x2 f[8];
         chunk_dequant16<BITS>(cw[i], s, sc2, f);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[s][8 * i + e] = f[e];
+        for (int e = 0; e < 8; ++e) vs[8 * i + e] = f[e];
       }
-      rotate_chunk<CH>(v[s], p.rotate, lane);
-    }
-    // the result slot is free once the previous row's store has read it
-    if (lane == 0 && stored) bulk_wait_read();
-    __syncwarp();
-#pragma unroll
-    for (int s = 0; s < NSEG; ++s)
+      rotate_chunk<CH>(vs, p.rotate, lane);
+    };
+    auto to_slot = [&](int s, f32x2 (&vs)[CH / 2]) {
 #pragma unroll
       for (int j = 0; j < NPC; ++j) {
         uint32_t b[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) b[e] = f2_to_bf16x2(v[s][4 * j + e], v[s][4 * j + e]);
+        for (int e = 0; e < 4; ++e) b[e] = f2_to_bf16x2(vs[4 * j + e], vs[4 * j + e]);
         *reinterpret_cast<uint4*>(oslot + swz_piece(static_cast<uint32_t>(s * segw + lane * CH + 8 * j))) = make_uint4(b[0], b[1], b[2], b[3]);
       }
+    };
+    if (NORMB) {
+#pragma unroll
+      for (int s = 0; s < NSEG; ++s) rebuild(s, v[s]);
+    } else {
+      rebuild(0, v[0]);
+    }
+    // the result slot is free once the previous row's store has read it
+    if (lane == 0 && stored) bulk_wait_read();
+    __syncwarp();
+    if (NORMB) {
+#pragma unroll
+      for (int s = 0; s < NSEG; ++s) to_slot(s, v[s]);
+    } else {
+      to_slot(0, v[0]);
+#pragma unroll
+      for (int s = 1; s < NSEG; ++s) {
+        rebuild(s, v[0]);
+        to_slot(s, v[0]);
+      }
+    }
     __syncwarp();
     if (!NORMB) {
       // ---- decompress: the stored originals take the outlier channels' places, the row leaves
@@ -343,7 +361,7 @@ inline ChunkBwdPlan plan_chunk_bwd(const hyc_packed* q, bool norm) {
   w.off_slots = take(w.slot_bytes * kChunkBwdWarps * (norm ? 3 : 1), 1024);
   w.total = off + 1024;
   if (w.total > kSmemPerCtaMax) return w;
-  long long grid = sm_count();
+  long long grid = static_cast<long long>(sm_count()) * ((norm || q->bits == 8) ? 1 : 2);
   const long long need = (q->rows + kChunkBwdWarps - 1) / kChunkBwdWarps;
   if (grid > need) grid = need;
   w.grid = static_cast<int>(grid);
