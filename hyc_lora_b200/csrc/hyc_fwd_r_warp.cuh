@@ -133,22 +133,49 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
     }
     float ss = 0.f;
     uint32_t mine = 0;
+    if (!lrs) {
+      // no low-rank part: the values compared with the threshold are the staged bf16 values themselves, so the
+      // count runs on packed pairs (|x| > thr gives 1.0 or 0.0 per half; a lane counts at most 128: exact in bf16)
+      const __nv_bfloat162 thr2 = __float2bfloat162_rn(thr);
+      __nv_bfloat162 cnt2 = __float2bfloat162_rn(0.f);
 #pragma unroll 2
-    for (int iu = 0; iu < upl; ++iu) {
-      const int u = lane + 32 * iu;
-      if (u < U) {
+      for (int iu = 0; iu < upl; ++iu) {
+        const int u = lane + 32 * iu;
+        if (u < U) {
 #pragma unroll
-        for (int s = 0; s < NSEG; ++s) {
-          const int col = s * segw + (u << 3);
-          float f[8];
-          load8<XT>(xs, col, f);
-          if (NORM) {
+          for (int s = 0; s < NSEG; ++s) {
+            const uint4 w = *reinterpret_cast<const uint4*>(xs + s * segw + (u << 3));
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { const float c = ln ? f[e] - mean : f[e]; ss = fmaf(c, c, ss); }
+            for (int e = 0; e < 4; ++e) cnt2 = __hadd2(cnt2, __hgt2(__habs2(h[e]), thr2));
+            if (NORM) {
+              float f[8];
+              unpack_bf16x8(w, f);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) { const float c = ln ? f[e] - mean : f[e]; ss = fmaf(c, c, ss); }
+            }
           }
-          r_residual8<XT>(f, lrs, col);
+        }
+      }
+      mine = static_cast<uint32_t>(__bfloat162float(__low2bfloat16(cnt2)) + __bfloat162float(__high2bfloat16(cnt2)));
+    } else {
+#pragma unroll 2
+      for (int iu = 0; iu < upl; ++iu) {
+        const int u = lane + 32 * iu;
+        if (u < U) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) mine += fabsf(f[e]) > thr ? 1u : 0u;
+          for (int s = 0; s < NSEG; ++s) {
+            const int col = s * segw + (u << 3);
+            float f[8];
+            load8<XT>(xs, col, f);
+            if (NORM) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) { const float c = ln ? f[e] - mean : f[e]; ss = fmaf(c, c, ss); }
+            }
+            r_residual8<XT>(f, lrs, col);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) mine += fabsf(f[e]) > thr ? 1u : 0u;
+          }
         }
       }
     }
