@@ -782,6 +782,31 @@ def run_case(args):
     from hyc_lora_b200.operators import compress_function as cf
     torch.cuda.set_device(0)
     rows = args.rows
+    if args.case == "step_kernels":
+        # GPU time per kernel of the 7B-shaped training step (eager, torch.profiler / CUPTI), `--step-layers` decoder layers
+        import collections
+        from torch.profiler import ProfilerActivity, profile
+        from hyc_lora_b200.hosts.step import build_trainer
+        layers = args.step_layers or 8
+        tr = build_trainer("llama2_7b", layers=layers, compress=True, outlier_mode="channel", rotate=256)
+        ids = synthetic.token_ids(3, 4, 512, 32000).cuda()
+        for _ in range(3):
+            tr.step(ids)
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(2):
+                tr.step(ids)
+            torch.cuda.synchronize()
+        agg = collections.defaultdict(lambda: [0.0, 0])
+        for e in prof.events():
+            if e.device_type == torch.autograd.DeviceType.CUDA:
+                agg[e.name][0] += e.device_time
+                agg[e.name][1] += 1
+        total = sum(v[0] for v in agg.values())
+        rows_ = [{"kernel": k[:100], "ms_per_step": round(v[0] / 2e3, 3), "launches_per_step": v[1] // 2,
+                  "share": round(v[0] / total, 4)} for k, v in sorted(agg.items(), key=lambda kv: -kv[1][0])[:40]]
+        print(json.dumps({"case": args.case, "layers": layers, "gpu_ms_per_step": round(total / 2e3, 2), "kernels": rows_}))
+        return
     if args.case == "mlp_sites":
         # the three one-pass kernels of the gated MLP's sites on bf16 [rows, cols] tensors, `launches` rounds
         cols = args.cols
