@@ -788,8 +788,11 @@ def run_case(args):
         from torch.profiler import ProfilerActivity, profile
         from hyc_lora_b200.hosts.step import build_trainer
         layers = args.step_layers or 8
-        tr = build_trainer("llama2_7b", layers=layers, compress=True, outlier_mode="channel", rotate=256)
-        ids = synthetic.token_ids(3, 4, 512, 32000).cuda()
+        mistral = args.step_config == "mistral_7b"
+        bits, ratio, rotate = (2, 0.02, 0) if mistral else (4, 0.01, 256)
+        tr = build_trainer(args.step_config, layers=layers, compress=True, outlier_mode="channel", bits=bits,
+                           outlier_ratio=ratio, rotate=rotate)
+        ids = synthetic.token_ids(3, 2 if mistral else 4, 2048 if mistral else 512, 32000).cuda()
         for _ in range(3):
             tr.step(ids)
         torch.cuda.synchronize()
