@@ -147,8 +147,13 @@ class Attention(nn.Module):
         b, s, _ = x.shape
         c = self.c
         hd = c.hidden // c.heads
-        v = self.v_proj(x).view(b, s, c.kv_heads, hd).transpose(1, 2)
-        q, k = _rope(self.q_proj(x), self.k_proj(x), c.rope_theta, c.heads, c.kv_heads)
+        # the three projections read the same x: their input gradients travel back along one carry and
+        # are summed by the GEMMs that make them
+        v, carry = self.v_proj(x, carry=x)
+        q, carry = self.q_proj(x, carry=carry)
+        k, carry = self.k_proj(x, carry=carry)
+        v = v.view(b, s, c.kv_heads, hd).transpose(1, 2)
+        q, k = _rope(q, k, c.rope_theta, c.heads, c.kv_heads)
         q, k = q.transpose(1, 2), k.transpose(1, 2)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=c.kv_heads != c.heads)
         return self.o_proj(o.transpose(1, 2).reshape(b, s, c.heads * hd))
@@ -164,7 +169,9 @@ class MLP(nn.Module):
         self.hadamard = LlamaHadamard()
 
     def forward(self, x):
-        return self.down_proj(self.hadamard(self.act_fn(self.gate_proj(x)), self.up_proj(x)))
+        gate, carry = self.gate_proj(x, carry=x)
+        up, carry = self.up_proj(x, carry=carry)
+        return self.down_proj(self.hadamard(self.act_fn(gate), up))
 
 
 class DecoderLayer(nn.Module):

@@ -74,17 +74,37 @@ def nf4_dequantize(codes: torch.Tensor, absmax: torch.Tensor, shape) -> torch.Te
     return out.view(shape)
 
 
-class _FrozenNF4LinearFunc(torch.autograd.Function):
-    """y = x W^T with W rebuilt from 4-bit storage; backward rebuilds W again and returns dX only."""
+def _into_carry(carry_grad, grad_out, weight, shape):
+    """``carry_grad += grad_out @ weight`` in the GEMM's epilogue, or the plain product where no gradient
+    has been carried this far.  The carried buffer is owned by the chain (each link hands it to exactly one
+    other link), so it is updated in place."""
+    g2 = grad_out.reshape(-1, grad_out.shape[-1]).to(weight.dtype)
+    if carry_grad is None or not carry_grad.is_contiguous() or carry_grad.dtype != weight.dtype:
+        out = (g2 @ weight).view(shape)
+        return out if carry_grad is None else carry_grad + out
+    carry_grad.view(-1, carry_grad.shape[-1]).addmm_(g2, weight)
+    return carry_grad
+
+
+class _FrozenLinearFunc(torch.autograd.Function):
+    """``y = x W^T`` for a frozen W (rebuilt from 4-bit storage in forward and again in backward, or a
+    frozen bf16 parameter); nothing is saved.  ``carry`` is a tensor of x's shape that is handed through
+    unchanged: the gradient with respect to x is not returned for ``x`` but added, by the GEMM that makes
+    it, to the gradient that arrives for the carried tensor.  A host strings the projections that read one
+    activation along one carry that starts at the activation itself, and the sum of their input gradients
+    costs no elementwise kernel."""
 
     @staticmethod
-    def forward(ctx, x, layer):
-        ctx.layer = layer
-        return x @ layer.dequantized().t()
+    def forward(ctx, x, carry, layer):
+        ctx.layer, ctx.shape = layer, carry.shape
+        ctx.set_materialize_grads(False)
+        return x @ layer.dense_weight().t(), carry
 
     @staticmethod
-    def backward(ctx, grad_out):
-        return grad_out @ ctx.layer.dequantized(), None
+    def backward(ctx, grad_out, carry_grad):
+        if grad_out is None:
+            return None, carry_grad, None
+        return None, _into_carry(carry_grad, grad_out, ctx.layer.dense_weight(), ctx.shape), None
 
 
 class FrozenLinear(nn.Module):
@@ -110,9 +130,15 @@ class FrozenLinear(nn.Module):
     def dequantized(self) -> torch.Tensor:
         return nf4_dequantize(self.codes, self.absmax, (self.out_features, self.in_features))
 
-    def forward(self, x):
+    def dense_weight(self) -> torch.Tensor:
+        return self.dequantized() if self.quant == "nf4" else self.weight
+
+    def forward(self, x, carry=None):
+        """``carry=None``: x W^T.  With a carry (see ``_FrozenLinearFunc``): (x W^T, the carry handed on)."""
+        if carry is not None:
+            return _FrozenLinearFunc.apply(x, carry, self)
         if self.quant == "nf4":
-            return _FrozenNF4LinearFunc.apply(x, self)
+            return _FrozenLinearFunc.apply(x, x, self)[0]
         return nn.functional.linear(x, self.weight)
 
 
@@ -155,15 +181,29 @@ class LoRALinear(nn.Module):
         nn.init.zeros_(self.lora_B.weight)
         self.scaling = alpha / r
 
-    def forward(self, x):
+    def forward(self, x, carry=None):
+        """``carry=None``: the adapter's output.  With a carry -- a tensor of x's shape, x itself for the
+        first projection that reads x, the carry the previous one returned for the others -- the result is
+        (output, carry to hand on): the input gradients of the base projection and of ``lora_A`` are added
+        into the gradient that travels back along the carry by the GEMMs that make them, and x receives
+        their sum without an elementwise add."""
         # base + scaling * (A x) B^T with the scale and the add in the GEMM's epilogue (no separate
         # elementwise kernels); lora_A stays a module so that it can be swapped for the compressing linear
         # (the base output is produced 2-D so that the in-place update is not an update through a view,
         # which autograd would undo with full-size copies in backward)
-        base = self.base_layer(x.reshape(-1, x.shape[-1]))
-        h = self.lora_A(x)
+        chain = x if carry is None else carry
+        if torch.is_grad_enabled() and chain.requires_grad:
+            base, chain = self.base_layer(x.reshape(-1, x.shape[-1]), carry=chain)
+            if getattr(self.lora_A, "takes_carry", False):
+                h, chain = self.lora_A(x, carry=chain)
+            else:
+                h = self.lora_A(x)
+        else:
+            base = self.base_layer(x.reshape(-1, x.shape[-1]))
+            h = self.lora_A(x)
         base = _LoraMergeFunc.apply(base, h.reshape(-1, h.shape[-1]), self.lora_B.weight, self.scaling)
-        return base.view(*x.shape[:-1], base.shape[-1])
+        out = base.view(*x.shape[:-1], base.shape[-1])
+        return out if carry is None else (out, chain)
 
 
 def lora_parameters(model: nn.Module):

@@ -207,3 +207,47 @@ def test_rotary_kernel_matches_tensor_ops(hq, hk, hd, s):
         got, want = got.detach().float().cpu(), want.detach().float()
         assert (got - want).abs().max() <= 1e-2 * want.abs().max() + 1e-3
         assert _cos(got, want) > 0.9999
+
+
+@pytest.mark.parametrize("quant", ["nf4", "bf16"])
+def test_input_gradients_summed_along_the_carry(quant):
+    """Projections that read one activation hand a carry from one to the next; the gradient that reaches
+    the activation must be the sum of every base and LoRA-A input gradient (worked out here with plain
+    products in fp32), and the LoRA gradients must not depend on whether a carry was used."""
+    from hyc_lora_b200.hosts.lora import LoRALinear
+    from hyc_lora_b200.hosts.replace import replace_module, uniform_config
+    torch.manual_seed(5)
+    mods = torch.nn.ModuleList(LoRALinear(1024, o, r=16, quant=quant, device="cuda") for o in (1024, 512, 256))
+    _train_b(mods)
+    assert replace_module(mods, uniform_config(sub_outlier_bit=8), dict(outlier_mode="channel")) == 3
+    x0 = torch.randn(2, 64, 1024, device="cuda", dtype=torch.bfloat16)
+    gy = [torch.randn(2, 64, m.base_layer.out_features, device="cuda", dtype=torch.bfloat16) for m in mods]
+
+    def run(chained):
+        for m in mods:
+            m.zero_grad(set_to_none=True)
+        x = x0.clone().requires_grad_(True)
+        xa = x * 1.0                                   # a non-leaf activation, as in a host
+        carry, ys = xa, []
+        for m in mods:
+            if chained:
+                y, carry = m(xa, carry=carry)
+            else:
+                y = m(xa)
+            ys.append(y)
+        torch.autograd.backward(ys, gy)
+        return x.grad.float(), [m.lora_A.weight.grad.clone() for m in mods], [m.lora_B.weight.grad.clone() for m in mods]
+
+    for _ in range(3):                                 # calibration calls, then the steady state
+        gx_c, ga_c, gb_c = run(True)
+    gx_u, ga_u, gb_u = run(False)
+    want = torch.zeros_like(gx_c)
+    for m, g in zip(mods, gy):
+        w = m.base_layer.dense_weight().float()
+        gh = (g.float().reshape(-1, g.shape[-1]) @ m.lora_B.weight.float()) * m.scaling
+        want += (g.float().reshape(-1, g.shape[-1]) @ w + gh.to(torch.bfloat16).float() @ m.lora_A.weight.float()).view(want.shape)
+    scale = want.abs().max().item()
+    assert (gx_c - want).abs().max().item() < 2e-2 * scale
+    assert (gx_u - want).abs().max().item() < 3e-2 * scale
+    for a, b in zip(ga_c + gb_c, ga_u + gb_u):
+        assert torch.equal(a, b)
