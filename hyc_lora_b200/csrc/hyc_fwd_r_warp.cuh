@@ -206,6 +206,7 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
       if (over && p.status) atomicOr(p.status, kStatusPoolOverflow);
     }
     const bool extract = !over;              // a row that does not fit the pool is quantised whole
+    const float thr_row = extract ? thr : __int_as_float(0x7f800000);   // nothing exceeds +inf
     uint32_t at = base + incl - mine;        // where this lane's entries go
     // ---- pass 2: norm output, codes, outlier entries
     unsigned char* codes_row = p.codes + row * cb;
@@ -214,7 +215,11 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
     for (int iu = 0; iu < upl; ++iu) {
       const int u = lane + 32 * iu;
       if (u < U) {
+        // 2- and 4-bit codes: clamp, rounding and offset on packed bf16 pairs; 8-bit codes do not fit bf16's
+        // eight significant bits and keep the fp32 form
+        constexpr bool kPairs = BITS < 8;
         RPack<BITS> acc;
+        RPackPairs<BITS> accp;
         bool ok = true;
         uint32_t flags = 0;
 #pragma unroll
@@ -239,19 +244,34 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
           r_residual8<XT>(v, lrs, col);
           RScale8 sc;
           r_scale8(sc, csc, crcp, D, col, sc_row, rc_row);
+          float q[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const bool out = extract && fabsf(v[e]) > thr;
-            if (out) flags |= 1u << (s * 8 + e);
+            const bool out = fabsf(v[e]) > thr_row;
             // what is quantised at an outlier's slot is x - x * mask as in the reference: 0, or NaN for an
             // infinite input (the unit is then redone with the division sequence, which keeps the NaN)
-            float q = r_quotient(out ? v[e] - v[e] : v[e], sc.sc[e], sc.rc[e], ok);
-            q = bf16_round(q);
-            acc.add(q, s, e);
+            float vq = v[e];
+            if (out) {
+              flags |= 1u << (s * 8 + e);
+              vq = vq - vq;
+            }
+            if (kPairs) {
+              q[e] = r_quotient_plain(vq, sc.sc[e], sc.rc[e]);
+            } else {
+              q[e] = bf16_round(r_quotient(vq, sc.sc[e], sc.rc[e], ok));
+              acc.add(q[e], s, e);
+            }
+          }
+          if (kPairs) {
+            accp.add(q[0], q[2], s, 0);
+            accp.add(q[1], q[3], s, 1);
+            accp.add(q[4], q[6], s, 4);
+            accp.add(q[5], q[7], s, 5);
           }
         }
-        uint2 packed = acc.done();
-        if (!ok) packed = r_unit_exact<XT, BITS>(xs, lrs, csc, sc_row, segw, u, extract ? thr : __int_as_float(0x7f800000));
+        if (kPairs) ok = accp.ok();
+        uint2 packed = kPairs ? accp.done() : acc.done();
+        if (!ok) packed = r_unit_exact<XT, BITS>(xs, lrs, csc, sc_row, segw, u, thr_row);
         *reinterpret_cast<uint2*>(codes_row + (u << 3)) = packed;
         // the unit's outliers, values read again from the staged row
         while (flags) {
