@@ -16,6 +16,8 @@
 // Arithmetic per element is that of fwd_r_fast_kernel (hyc_fwd_r_fast.cuh), whose helpers are used here:
 // codes and the outlier set are identical.
 #pragma once
+#include <type_traits>
+
 #include "hyc_fwd_r_fast.cuh"
 #include "hyc_fwd_warp.cuh"
 
@@ -211,10 +213,21 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
     // ---- pass 2: norm output, codes, outlier entries
     unsigned char* codes_row = p.codes + row * cb;
     XT* yrow = NORM ? a.y + row * a.row_stride : nullptr;
+    // The loop is compiled once per combination of three launch-wide facts -- a low-rank row is staged, the
+    // scale is per channel, every lane owns a unit in every round -- so that no test of them (a branch and a
+    // reconvergence point each, per segment) is left between the loads and the arithmetic of a unit: the
+    // compiler then overlaps the segments of a unit.  Each fact is passed as 0 (known false), 1 (known true) or
+    // 2 (left to a test at run time).
+    auto pass2 = [&](auto has_lr, auto has_csc, auto full_rounds) {
+      constexpr int kLr = decltype(has_lr)::value, kCsc = decltype(has_csc)::value;
+      const __nv_bfloat16* const lrs_c = kLr == 0 ? nullptr : lrs;
+      const __nv_bfloat16* const csc_c = kCsc == 0 ? nullptr : csc;
+      if (kLr == 1) __builtin_assume(lrs_c != nullptr);
+      if (kCsc == 1) __builtin_assume(csc_c != nullptr);
 #pragma unroll 2
     for (int iu = 0; iu < upl; ++iu) {
       const int u = lane + 32 * iu;
-      if (u < U) {
+      if (decltype(full_rounds)::value == 1 || u < U) {
         // 2- and 4-bit codes: clamp, rounding and offset on packed bf16 pairs; 8-bit codes do not fit bf16's
         // eight significant bits and keep the fp32 form
         constexpr bool kPairs = BITS < 8;
@@ -241,9 +254,9 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
             }
             store8<XT>(yrow, col, y);
           }
-          r_residual8<XT>(v, lrs, col);
+          r_residual8<XT>(v, lrs_c, col);
           RScale8 sc;
-          r_scale8(sc, csc, crcp, D, col, sc_row, rc_row);
+          r_scale8(sc, csc_c, crcp, D, col, sc_row, rc_row);
           float q[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
@@ -271,7 +284,7 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
         }
         if (kPairs) ok = accp.ok();
         uint2 packed = kPairs ? accp.done() : acc.done();
-        if (!ok) packed = r_unit_exact<XT, BITS>(xs, lrs, csc, sc_row, segw, u, thr_row);
+        if (!ok) packed = r_unit_exact<XT, BITS>(xs, lrs_c, csc_c, sc_row, segw, u, thr_row);
         *reinterpret_cast<uint2*>(codes_row + (u << 3)) = packed;
         // the unit's outliers, values read again from the staged row
         while (flags) {
@@ -279,10 +292,22 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
           flags &= flags - 1;
           const int col = (b >> 3) * segw + (u << 3) + (b & 7);
           float x = __bfloat162float(xs[col]);
-          if (lrs) x = bf16_round(x - __bfloat162float(lrs[col]));
+          if (lrs_c) x = bf16_round(x - __bfloat162float(lrs_c[col]));
           p.pool[at++] = (float_to_bf16_bits(x) << 16) | static_cast<uint32_t>(col);
         }
       }
+    }
+    };
+    using K0 = std::integral_constant<int, 0>;
+    using K1 = std::integral_constant<int, 1>;
+    using K2 = std::integral_constant<int, 2>;
+    const bool full = (U & 31) == 0;
+    if (lrs) {
+      if (per_channel) { if (full) pass2(K1(), K1(), K1()); else pass2(K1(), K1(), K2()); }
+      else { if (full) pass2(K1(), K0(), K1()); else pass2(K1(), K0(), K2()); }
+    } else {
+      if (per_channel) { if (full) pass2(K0(), K1(), K1()); else pass2(K0(), K1(), K2()); }
+      else { if (full) pass2(K0(), K0(), K1()); else pass2(K0(), K0(), K2()); }
     }
     __syncwarp();   // every lane is done with the slot
     const long long next = row + stride;
