@@ -62,7 +62,8 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
   const XT* xs = reinterpret_cast<const XT*>(slot);
   const __nv_bfloat16* lrs = p.lowrank ? reinterpret_cast<const __nv_bfloat16*>(slot + a.off_lr) : nullptr;
   const bool per_channel = p.scale_kind == kScaleChannel;
-  __nv_bfloat16* csc = per_channel ? reinterpret_cast<__nv_bfloat16*>(smem + a.off_csc) : nullptr;
+  // per-channel scales and their reciprocals as fp32 tables (the two halves of each group of 8 apart)
+  float* csc = per_channel ? reinterpret_cast<float*>(smem + a.off_csc) : nullptr;
   float* crcp = per_channel ? reinterpret_cast<float*>(smem + a.off_crcp) : nullptr;
   float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
   float* bsm = reinterpret_cast<float*>(smem + a.off_bsm);
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
   if (lane == 0 && row < rows) issue(row);
   if (per_channel) {
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
-      csc[c] = p.scale[c];
+      csc[split_index(c, D)] = __bfloat162float(p.scale[c]);
       crcp[split_index(c, D)] = r_safe_rcp(__bfloat162float(p.scale[c]));
     }
   }
@@ -221,7 +222,7 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
     auto pass2 = [&](auto has_lr, auto has_csc, auto full_rounds) {
       constexpr int kLr = decltype(has_lr)::value, kCsc = decltype(has_csc)::value;
       const __nv_bfloat16* const lrs_c = kLr == 0 ? nullptr : lrs;
-      const __nv_bfloat16* const csc_c = kCsc == 0 ? nullptr : csc;
+      const float* const csc_c = kCsc == 0 ? nullptr : csc;
       if (kLr == 1) __builtin_assume(lrs_c != nullptr);
       if (kCsc == 1) __builtin_assume(csc_c != nullptr);
 #pragma unroll 2
@@ -256,7 +257,13 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
           }
           r_residual8<XT>(v, lrs_c, col);
           RScale8 sc;
-          r_scale8(sc, csc_c, crcp, D, col, sc_row, rc_row);
+          if (csc_c) {
+            load8_split(csc_c, D, col, sc.sc);
+            load8_split(crcp, D, col, sc.rc);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { sc.sc[e] = sc_row; sc.rc[e] = rc_row; }
+          }
           float q[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
@@ -284,16 +291,16 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
         }
         if (kPairs) ok = accp.ok();
         uint2 packed = kPairs ? accp.done() : acc.done();
-        if (!ok) packed = r_unit_exact<XT, BITS>(xs, lrs_c, csc_c, sc_row, segw, u, thr_row);
+        if (!ok) packed = r_unit_exact<XT, BITS>(xs, lrs_c, csc_c ? p.scale : nullptr, sc_row, segw, u, thr_row);
         *reinterpret_cast<uint2*>(codes_row + (u << 3)) = packed;
         // the unit's outliers, values read again from the staged row
         while (flags) {
           const int b = __ffs(flags) - 1;
           flags &= flags - 1;
           const int col = (b >> 3) * segw + (u << 3) + (b & 7);
-          float x = __bfloat162float(xs[col]);
-          if (lrs_c) x = bf16_round(x - __bfloat162float(lrs_c[col]));
-          p.pool[at++] = (float_to_bf16_bits(x) << 16) | static_cast<uint32_t>(col);
+          uint32_t vbits = reinterpret_cast<const uint16_t*>(xs)[col];   // the staged bf16 value as it is
+          if (lrs_c) vbits = float_to_bf16_bits(bf16_round(__bfloat162float(xs[col]) - __bfloat162float(lrs_c[col])));
+          p.pool[at++] = (vbits << 16) | static_cast<uint32_t>(col);
         }
       }
     }
@@ -338,7 +345,7 @@ inline RWarpPlan plan_r_warp(const hyc_packed* q, const hyc_dense* x, bool norm,
   if (D > 4096) return w;
   uint32_t off = 64 * 8;
   auto take = [&](uint32_t bytes) { uint32_t o = off; off = align_up(off + bytes, 16); return o; };
-  if (q->scale_kind == HYC_SCALE_CHANNEL) { w.off_csc = take(D * 2); w.off_crcp = take(D * 4); }
+  if (q->scale_kind == HYC_SCALE_CHANNEL) { w.off_csc = take(D * 4); w.off_crcp = take(D * 4); }
   if (norm) w.off_wsm = take(D * 4);
   if (ln) w.off_bsm = take(D * 4);
   off = align_up(off, 128);
