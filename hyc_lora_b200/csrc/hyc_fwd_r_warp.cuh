@@ -62,7 +62,8 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
   const XT* xs = reinterpret_cast<const XT*>(slot);
   const __nv_bfloat16* lrs = p.lowrank ? reinterpret_cast<const __nv_bfloat16*>(slot + a.off_lr) : nullptr;
   const bool per_channel = p.scale_kind == kScaleChannel;
-  // per-channel scales and their reciprocals as fp32 tables (the two halves of each group of 8 apart)
+  // per-channel scales, negated (the form the quotient's remainder step takes), and their reciprocals as fp32
+  // tables (the two halves of each group of 8 apart)
   float* csc = per_channel ? reinterpret_cast<float*>(smem + a.off_csc) : nullptr;
   float* crcp = per_channel ? reinterpret_cast<float*>(smem + a.off_crcp) : nullptr;
   float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
@@ -83,7 +84,7 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
   if (lane == 0 && row < rows) issue(row);
   if (per_channel) {
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
-      csc[split_index(c, D)] = __bfloat162float(p.scale[c]);
+      csc[split_index(c, D)] = -__bfloat162float(p.scale[c]);
       crcp[split_index(c, D)] = r_safe_rcp(__bfloat162float(p.scale[c]));
     }
   }
@@ -141,6 +142,8 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
       // count runs on packed pairs (|x| > thr gives 1.0 or 0.0 per half; a lane counts at most 128: exact in bf16)
       const __nv_bfloat162 thr2 = __float2bfloat162_rn(thr);
       __nv_bfloat162 cnt2 = __float2bfloat162_rn(0.f);
+      const f32x2 mean2 = f2_make(mean, mean);
+      f32x2 ss2 = 0ull;
 #pragma unroll 2
       for (int iu = 0; iu < upl; ++iu) {
         const int u = lane + 32 * iu;
@@ -152,13 +155,22 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
 #pragma unroll
             for (int e = 0; e < 4; ++e) cnt2 = __hadd2(cnt2, __hgt2(__habs2(h[e]), thr2));
             if (NORM) {
-              float f[8];
-              unpack_bf16x8(w, f);
+              // the sum of squares as two partial sums, two channels per instruction
+              f32x2 f2[4];
+              unpack_bf16x8_pairs(w, f2);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) { const float c = ln ? f[e] - mean : f[e]; ss = fmaf(c, c, ss); }
+              for (int i = 0; i < 4; ++i) {
+                const f32x2 c = ln ? f2_sub(f2[i], mean2) : f2[i];
+                ss2 = f2_fma(c, c, ss2);
+              }
             }
           }
         }
+      }
+      {
+        float lo, hi;
+        f2_split(ss2, lo, hi);
+        ss = lo + hi;
       }
       mine = static_cast<uint32_t>(__bfloat162float(__low2bfloat16(cnt2)) + __bfloat162float(__high2bfloat16(cnt2)));
     } else {
@@ -250,37 +262,50 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
 #pragma unroll
               for (int e = 0; e < 8; ++e) y[e] = (v[e] - mean) * rstd * wv[e] + bv[e];
             } else {
+              const f32x2 rstd2 = f2_make(rstd, rstd);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) y[e] = v[e] * rstd * wv[e];
+              for (int i = 0; i < 4; ++i) {
+                const f32x2 t = f2_mul(f2_make(v[2 * i], v[2 * i + 1]), rstd2);
+                f2_split(f2_mul(t, f2_make(wv[2 * i], wv[2 * i + 1])), y[2 * i], y[2 * i + 1]);
+              }
             }
             store8<XT>(yrow, col, y);
           }
           r_residual8<XT>(v, lrs_c, col);
-          RScale8 sc;
+          RScale8 sc;   // sc.sc: minus the scale
           if (csc_c) {
             load8_split(csc_c, D, col, sc.sc);
             load8_split(crcp, D, col, sc.rc);
           } else {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { sc.sc[e] = sc_row; sc.rc[e] = rc_row; }
+            for (int e = 0; e < 8; ++e) { sc.sc[e] = -sc_row; sc.rc[e] = rc_row; }
           }
-          float q[8];
+          float q[8], vq[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const bool out = fabsf(v[e]) > thr_row;
             // what is quantised at an outlier's slot is x - x * mask as in the reference: 0, or NaN for an
             // infinite input (the unit is then redone with the division sequence, which keeps the NaN)
-            float vq = v[e];
+            vq[e] = v[e];
             if (out) {
               flags |= 1u << (s * 8 + e);
-              vq = vq - vq;
+              vq[e] = vq[e] - vq[e];
             }
-            if (kPairs) {
-              q[e] = r_quotient_plain(vq, sc.sc[e], sc.rc[e]);
-            } else {
-              q[e] = bf16_round(r_quotient(vq, sc.sc[e], sc.rc[e], ok));
-              acc.add(q[e], s, e);
-            }
+          }
+          // the correctly rounded quotient (r_quotient_plain) of two channels per instruction
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const f32x2 v2 = f2_make(vq[2 * i], vq[2 * i + 1]);
+            const f32x2 rc2 = f2_make(sc.rc[2 * i], sc.rc[2 * i + 1]);
+            const f32x2 q0 = f2_mul(v2, rc2);
+            const f32x2 rem = f2_fma(q0, f2_make(sc.sc[2 * i], sc.sc[2 * i + 1]), v2);
+            const f32x2 q2 = f2_fma(rem, rc2, q0);
+            accp.check(q2);
+            f2_split(q2, q[2 * i], q[2 * i + 1]);
+          }
+          if (!kPairs) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc.add(bf16_round(q[e]), s, e);
           }
           if (kPairs) {
             accp.add(q[0], q[2], s, 0);
@@ -289,7 +314,7 @@ __global__ void __launch_bounds__(kRWarpThreadsMax, 1) fwd_r_warp_kernel(const _
             accp.add(q[5], q[7], s, 5);
           }
         }
-        if (kPairs) ok = accp.ok();
+        ok = accp.ok();
         uint2 packed = kPairs ? accp.done() : acc.done();
         if (!ok) packed = r_unit_exact<XT, BITS>(xs, lrs_c, csc_c ? p.scale : nullptr, sc_row, segw, u, thr_row);
         *reinterpret_cast<uint2*>(codes_row + (u << 3)) = packed;
