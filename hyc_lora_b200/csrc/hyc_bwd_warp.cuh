@@ -14,6 +14,8 @@
 #pragma once
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "hyc_bwd_fast.cuh"
 #include "hyc_fwd_warp.cuh"
 
@@ -90,6 +92,47 @@ __device__ __forceinline__ void warp_rebuild8(const uint2& cw, int s, float sc, 
   if (ROUND) round_bf16x8(f);
 }
 
+// The same values as four fp32 pairs (channels 2i, 2i + 1 of the group), not rotated, rounded to bf16: two
+// channels per instruction on the packed fp32 pipe.
+template <int BITS>
+__device__ __forceinline__ void warp_rebuild8_pairs(const uint2& cw, int s, f32x2 sc2, f32x2 (&f)[4]) {
+  using C = CodeTraits<BITS>;
+  uint32_t w[2] = {cw.x, cw.y};
+  float bias;
+  if (BITS == 8) {
+    w[0] ^= 0x80808080u; w[1] ^= 0x80808080u;  // two's complement -> offset 128
+    bias = 8388608.f + 128.f;
+  } else {
+    const uint32_t m = 0x01010101u * C::kMask;
+    w[0] = (w[0] >> (s * BITS)) & m;
+    w[1] = (w[1] >> (s * BITS)) & m;
+    bias = 8388608.f + static_cast<float>(C::kOff);
+  }
+  const f32x2 bias2 = f2_make(bias, bias);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const f32x2 lo = f2_make(__uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7650)),
+                             __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7651)));
+    const f32x2 hi = f2_make(__uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7652)),
+                             __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7653)));
+    const f32x2 a = f2_mul(f2_sub(lo, bias2), sc2), b = f2_mul(f2_sub(hi, bias2), sc2);
+    float a0, a1, b0, b1;
+    f2_split(a, a0, a1);
+    f2_split(b, b0, b1);
+    const uint32_t pa = pack_bf16x2(a0, a1), pb = pack_bf16x2(b0, b1);
+    f[2 * i] = f2_make(__uint_as_float(pa << 16), __uint_as_float(pa & 0xffff0000u));
+    f[2 * i + 1] = f2_make(__uint_as_float(pb << 16), __uint_as_float(pb & 0xffff0000u));
+  }
+}
+
+// the 8 table entries of load8_split as four pairs
+__device__ __forceinline__ void load8_split_pairs(const float* table, int D, int col, f32x2 (&f)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(table + ((col >> 3) << 2));
+  const float4 b = *reinterpret_cast<const float4*>(table + (D >> 1) + ((col >> 3) << 2));
+  f[0] = f2_make(a.x, a.y); f[1] = f2_make(a.z, a.w);
+  f[2] = f2_make(b.x, b.y); f[3] = f2_make(b.z, b.w);
+}
+
 // ------------------------------------------------------------------ decompress
 
 template <int BITS, int NG, bool ROT>
@@ -162,6 +205,7 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
   c.init(a, smem);
   const int D = c.D;
   const int upl = (c.U + 31) >> 5;
+  const bool full = (c.U & 31) == 0;
   const uint32_t cb = static_cast<uint32_t>(D) * BITS / 8;
   if (c.lane == 0 && c.row < c.rows) warp_issue_row(a, c.slot, c.bar, c.row, cb, false, true, D);
   float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
@@ -203,32 +247,76 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
     //   c1 = mean_d(x-hat * w dy) = rstd * (S1 - mean * S2) / D,   S1 = sum x * w dy,  S2 = sum w dy,
     // so the pass accumulates S1 and S2 from the rebuilt x itself (two fused multiply-adds per element).
     float s1 = 0.f, s2 = 0.f;
-#pragma unroll 2
-    for (int iu = 0; iu < upl; ++iu) {
-      const int u = c.lane + 32 * iu;
-      const bool live = u < c.U;
-      const uint2 cw = live ? *reinterpret_cast<const uint2*>(c.slot + (u << 3)) : make_uint2(0u, 0u);
-#pragma unroll
-      for (int s = 0; s < NSEG; ++s) {
-        const int col = s * c.segw + (u << 3);
-        float f[8];
-        warp_rebuild8<BITS, ROT, true>(cw, s, p.group ? __ldg(sc_row + (min(col, D - 8) >> 7)) : sc_tok, p.rotate, c.lane, f);
-        if (live) {
-          if (ROT) {
-            const uint32_t m = mask8(omask, col);
-            if (m) zero_masked(f, m);
-          }
-          float gv[8], wv[8];
-          load8<__nv_bfloat16>(gs, col, gv);
-          load8_split(wsm, D, col, wv);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float wd = wv[e] * gv[e];
-            s1 = fmaf(f[e], wd, s1);
-            s2 += wd;
+    if (ROT) {
+  #pragma unroll 2
+      for (int iu = 0; iu < upl; ++iu) {
+        const int u = c.lane + 32 * iu;
+        const bool live = u < c.U;
+        const uint2 cw = live ? *reinterpret_cast<const uint2*>(c.slot + (u << 3)) : make_uint2(0u, 0u);
+  #pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+          const int col = s * c.segw + (u << 3);
+          float f[8];
+          warp_rebuild8<BITS, ROT, true>(cw, s, p.group ? __ldg(sc_row + (min(col, D - 8) >> 7)) : sc_tok, p.rotate, c.lane, f);
+          if (live) {
+            if (ROT) {
+              const uint32_t m = mask8(omask, col);
+              if (m) zero_masked(f, m);
+            }
+            float gv[8], wv[8];
+            load8<__nv_bfloat16>(gs, col, gv);
+            load8_split(wsm, D, col, wv);
+  #pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float wd = wv[e] * gv[e];
+              s1 = fmaf(f[e], wd, s1);
+              s2 += wd;
+            }
           }
         }
       }
+    } else {
+      // records without rotation: every step of the pass on packed fp32 pairs, compiled per combination of two
+      // launch-wide facts (group scales; every lane owns a unit in every round) so that no test of them sits
+      // between the segments of a unit
+      auto pass1 = [&](auto group_c, auto full_c) {
+        constexpr bool kGroup = decltype(group_c)::value, kFull = decltype(full_c)::value;
+        f32x2 s1p = 0ull, s2p = 0ull;
+        const f32x2 sc_tok2 = f2_make(sc_tok, sc_tok);
+#pragma unroll 2
+        for (int iu = 0; iu < upl; ++iu) {
+          const int u = c.lane + 32 * iu;
+          if (kFull || u < c.U) {
+            const uint2 cw = *reinterpret_cast<const uint2*>(c.slot + (u << 3));
+#pragma unroll
+            for (int s = 0; s < NSEG; ++s) {
+              const int col = s * c.segw + (u << 3);
+              f32x2 sc2 = sc_tok2;
+              if (kGroup) {
+                const float sg = __ldg(sc_row + (col >> 7));
+                sc2 = f2_make(sg, sg);
+              }
+              f32x2 f[4], gv[4], wv[4];
+              warp_rebuild8_pairs<BITS>(cw, s, sc2, f);
+              unpack_bf16x8_pairs(*reinterpret_cast<const uint4*>(gs + col), gv);
+              load8_split_pairs(wsm, D, col, wv);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const f32x2 wd = f2_mul(wv[e], gv[e]);
+                s1p = f2_fma(f[e], wd, s1p);
+                s2p = f2_add(s2p, wd);
+              }
+            }
+          }
+        }
+        float lo, hi;
+        f2_split(s1p, lo, hi);
+        s1 = lo + hi;
+        f2_split(s2p, lo, hi);
+        s2 = lo + hi;
+      };
+      if (p.group) { if (full) pass1(std::true_type(), std::true_type()); else pass1(std::true_type(), std::false_type()); }
+      else { if (full) pass1(std::false_type(), std::true_type()); else pass1(std::false_type(), std::false_type()); }
     }
     // outlier channels: the streamed pass saw the zero their code encodes instead of the stored value
 #pragma unroll
@@ -241,29 +329,67 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
     // ---- pass 2: dx = (w dy - (x-hat * c1 + c2)) * rstd = ka * w dy + kb * x + kc with three row constants
     const float ka = rstd, kb = -rstd * rstd * c1, kc = (mean * rstd * c1 - c2) * rstd;
     __nv_bfloat16* dxrow = a.out1 + row * D;
-#pragma unroll 2
-    for (int iu = 0; iu < upl; ++iu) {
-      const int u = c.lane + 32 * iu;
-      const bool live = u < c.U;
-      const uint2 cw = live ? *reinterpret_cast<const uint2*>(c.slot + (u << 3)) : make_uint2(0u, 0u);
-#pragma unroll
-      for (int s = 0; s < NSEG; ++s) {
-        const int col = s * c.segw + (u << 3);
-        float f[8];
-        warp_rebuild8<BITS, ROT, true>(cw, s, p.group ? __ldg(sc_row + (min(col, D - 8) >> 7)) : sc_tok, p.rotate, c.lane, f);
-        if (live) {
-          if (ROT) {
-            const uint32_t m = mask8(omask, col);
-            if (m) zero_masked(f, m);
+    if (ROT) {
+  #pragma unroll 2
+      for (int iu = 0; iu < upl; ++iu) {
+        const int u = c.lane + 32 * iu;
+        const bool live = u < c.U;
+        const uint2 cw = live ? *reinterpret_cast<const uint2*>(c.slot + (u << 3)) : make_uint2(0u, 0u);
+  #pragma unroll
+        for (int s = 0; s < NSEG; ++s) {
+          const int col = s * c.segw + (u << 3);
+          float f[8];
+          warp_rebuild8<BITS, ROT, true>(cw, s, p.group ? __ldg(sc_row + (min(col, D - 8) >> 7)) : sc_tok, p.rotate, c.lane, f);
+          if (live) {
+            if (ROT) {
+              const uint32_t m = mask8(omask, col);
+              if (m) zero_masked(f, m);
+            }
+            float gv[8], wv[8], d[8];
+            load8<__nv_bfloat16>(gs, col, gv);
+            load8_split(wsm, D, col, wv);
+  #pragma unroll
+            for (int e = 0; e < 8; ++e) d[e] = fmaf(ka, wv[e] * gv[e], fmaf(kb, f[e], kc));
+            store8<__nv_bfloat16>(dxrow, col, d);
           }
-          float gv[8], wv[8], d[8];
-          load8<__nv_bfloat16>(gs, col, gv);
-          load8_split(wsm, D, col, wv);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) d[e] = fmaf(ka, wv[e] * gv[e], fmaf(kb, f[e], kc));
-          store8<__nv_bfloat16>(dxrow, col, d);
         }
       }
+    } else {
+      auto pass2 = [&](auto group_c, auto full_c) {
+        constexpr bool kGroup = decltype(group_c)::value, kFull = decltype(full_c)::value;
+        const f32x2 sc_tok2 = f2_make(sc_tok, sc_tok);
+        const f32x2 ka2 = f2_make(ka, ka), kb2 = f2_make(kb, kb), kc2 = f2_make(kc, kc);
+#pragma unroll 2
+        for (int iu = 0; iu < upl; ++iu) {
+          const int u = c.lane + 32 * iu;
+          if (kFull || u < c.U) {
+            const uint2 cw = *reinterpret_cast<const uint2*>(c.slot + (u << 3));
+#pragma unroll
+            for (int s = 0; s < NSEG; ++s) {
+              const int col = s * c.segw + (u << 3);
+              f32x2 sc2 = sc_tok2;
+              if (kGroup) {
+                const float sg = __ldg(sc_row + (col >> 7));
+                sc2 = f2_make(sg, sg);
+              }
+              f32x2 f[4], gv[4], wv[4];
+              warp_rebuild8_pairs<BITS>(cw, s, sc2, f);
+              unpack_bf16x8_pairs(*reinterpret_cast<const uint4*>(gs + col), gv);
+              load8_split_pairs(wsm, D, col, wv);
+              uint32_t o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float lo, hi;
+                f2_split(f2_fma(ka2, f2_mul(wv[e], gv[e]), f2_fma(kb2, f[e], kc2)), lo, hi);
+                o[e] = pack_bf16x2(lo, hi);
+              }
+              *reinterpret_cast<uint4*>(dxrow + col) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      };
+      if (p.group) { if (full) pass2(std::true_type(), std::true_type()); else pass2(std::true_type(), std::false_type()); }
+      else { if (full) pass2(std::false_type(), std::true_type()); else pass2(std::false_type(), std::false_type()); }
     }
     __syncwarp();   // every lane is done with the slot; the vector stores come before the outlier channels' results
     const long long next = row + c.stride;

@@ -183,7 +183,11 @@ int hyc_norm_bwd(const hyc_packed* saved, const hyc_norm_bwd_args* g, void* stre
     // frozen norm weight (the adapter case), bf16 gradient, no rotation: one warp per row (a rotated record
     // would be rotated back in both of that kernel's passes; the shuffle pipe is its bound, so it stays on
     // the kernel below, which rotates once and keeps the row in registers)
-    const WarpBwdPlan wp = plan_warp_bwd(saved, nullptr, true, true, kNormBwdWarpThreads, 1);
+    // twenty warps where their slots fit the shared memory (2- and 4-bit codes of 4096 channels), else sixteen
+    // or twelve (8-bit codes: 12 KB per row)
+    WarpBwdPlan wp = plan_warp_bwd(saved, nullptr, true, true, kNormBwdWarpThreads, 1);
+    if (!wp.ok) wp = plan_warp_bwd(saved, nullptr, true, true, 512, 1);
+    if (!wp.ok) wp = plan_warp_bwd(saved, nullptr, true, true, 384, 1);
     if (wp.ok) {
       WarpBwdArgs wa;
       fill_warp_bwd(&wa, wp, saved, nullptr);
