@@ -78,7 +78,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // (lower + upper, lower - upper).  The normalisation 1 / sqrt(n) is a power of two: the caller folds it
 // into the scale, exactly.
 template <int CH>
-__device__ __forceinline__ void rotate_chunk(f32x2 (&v)[CH / 2], int n, int lane) {
+__device__ __forceinline__ void rotate_chunk_n(f32x2 (&v)[CH / 2], int n, int lane) {
   // stride 1: inside a pair
 #pragma unroll
   for (int i = 0; i < CH / 2; ++i) {
@@ -115,6 +115,16 @@ __device__ __forceinline__ void rotate_chunk(f32x2 (&v)[CH / 2], int n, int lane
       }
     }
   }
+}
+
+// The common block sizes with the size known to the compiler: the tests of `n` before every stage then fold away,
+// and the stages of a chunk (and the chunks of the segments around the call) become one stretch of code that the
+// compiler schedules as a whole.
+template <int CH>
+__device__ __forceinline__ void rotate_chunk(f32x2 (&v)[CH / 2], int n, int lane) {
+  if (n == 256) rotate_chunk_n<CH>(v, 256, lane);
+  else if (n == 64) rotate_chunk_n<CH>(v, 64, lane);
+  else rotate_chunk_n<CH>(v, n, lane);
 }
 
 // Outlier channels of one record (`chan`: the list in shared memory; lane l looks after entries l, l + 32, ...):
