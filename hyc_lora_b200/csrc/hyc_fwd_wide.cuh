@@ -18,6 +18,7 @@
 // at a named barrier (bar.sync id, 32 * WPR) for the row's absmax and around the staged row; whether a bounded
 // wait ran out is decided for the whole group at once, so no warp can be left waiting at such a barrier.
 #pragma once
+#include <type_traits>
 #include "hyc_fwd_chunk.cuh"
 
 namespace hyc {
@@ -239,6 +240,10 @@ fwd_n_wide_kernel(const __grid_constant__ WideArgs a, const __grid_constant__ CU
   uint32_t ph = 0;        // product: parity of both barriers; else: parity of slot 0's (slot 1 flips one row later)
   int st = 0;
   int rp = 0;             // which half of `red` the next absmax exchange uses
+  // the row loop is compiled a second time with the rotation block of 64 known: the butterfly stages then carry no
+  // test of it, and the segments of a row overlap
+  auto row_loop = [&](auto rot_c) {
+    const int nrot = decltype(rot_c)::value >= 0 ? decltype(rot_c)::value : p.rotate;
   for (; row < rows; row += stride) {
     // ---- wait for the row (both operands); the group decides together whether a wait ran out
     bool ok;
@@ -333,7 +338,7 @@ fwd_n_wide_kernel(const __grid_constant__ WideArgs a, const __grid_constant__ CU
       }
     }
     // ---- the record of x (x2), from the registers
-    wide_unpack_rotate<NSEG, CH>(raw, v, p.rotate, lane);
+    wide_unpack_rotate<NSEG, CH>(raw, v, nrot, lane);
     wide_scale_pack<BITS, CH, GROUP, WPR>(p, v, row, glane, active, red + rp * WPR, group, wig, lane);
     rp ^= 1;
     if (ACT || PROD) {
@@ -367,6 +372,9 @@ fwd_n_wide_kernel(const __grid_constant__ WideArgs a, const __grid_constant__ CU
       st ^= 1;
     }
   }
+  };
+  if (p.rotate == 64) row_loop(std::integral_constant<int, 64>());     // what rows of 11 008 and 14 336 channels use
+  else row_loop(std::integral_constant<int, -1>());
   // no tensor store of this thread may still be reading shared memory when the CTA leaves
   if ((ACT || PROD) && leader) bulk_wait_all();
 }
