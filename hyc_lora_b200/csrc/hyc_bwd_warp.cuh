@@ -93,9 +93,9 @@ __device__ __forceinline__ void warp_rebuild8(const uint2& cw, int s, float sc, 
 }
 
 // The same values as four fp32 pairs (channels 2i, 2i + 1 of the group), not rotated, rounded to bf16: two
-// channels per instruction on the packed fp32 pipe.
+// channels per instruction on the packed fp32 pipe.  `sc`: the scale of each pair's channels.
 template <int BITS>
-__device__ __forceinline__ void warp_rebuild8_pairs(const uint2& cw, int s, f32x2 sc2, f32x2 (&f)[4]) {
+__device__ __forceinline__ void warp_rebuild8_pairs(const uint2& cw, int s, const f32x2 (&sc)[4], f32x2 (&f)[4]) {
   using C = CodeTraits<BITS>;
   uint32_t w[2] = {cw.x, cw.y};
   float bias;
@@ -115,7 +115,7 @@ __device__ __forceinline__ void warp_rebuild8_pairs(const uint2& cw, int s, f32x
                              __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7651)));
     const f32x2 hi = f2_make(__uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7652)),
                              __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7653)));
-    const f32x2 a = f2_mul(f2_sub(lo, bias2), sc2), b = f2_mul(f2_sub(hi, bias2), sc2);
+    const f32x2 a = f2_mul(f2_sub(lo, bias2), sc[2 * i]), b = f2_mul(f2_sub(hi, bias2), sc[2 * i + 1]);
     float a0, a1, b0, b1;
     f2_split(a, a0, a1);
     f2_split(b, b0, b1);
@@ -195,8 +195,16 @@ constexpr int kNormBwdWarpThreads = 640;    // 20 warps, one CTA per SM: the slo
 // Two passes over the row (the two row sums, then the result) read the codes and the gradient row from
 // the warp's slot both times, in short rolled loops, instead of holding them in registers: few registers,
 // twenty warps per SM to cover the arithmetic latencies, and the slot goes back to the copy engine when
-// the row is done (the other warps keep the memory system busy meanwhile).
-template <int BITS, bool ROT, bool LN>
+// the row is done (the other warps keep the memory system busy meanwhile).  Every step of both passes runs on
+// packed fp32 pairs, and the loops are compiled per launch-wide fact (which kind of scale; every lane owns a
+// unit in every round), so that no test of those sits between the segments of a unit.
+//
+// REF: a reference-mode record without a low-rank part.  Its values are (code - offset) * static scale rounded
+// to bf16 (per channel: an fp32 table in shared memory; per token / per tensor: one scale per row); the row's
+// element outliers (their code is the zero code, so the streamed passes see exactly 0 there) come from the pool
+// and are put right by the lanes, entry by entry, after each pass -- the place the outlier channels' stored
+// originals take in a channel-mode record.
+template <int BITS, bool REF, bool LN>
 __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel(const __grid_constant__ WarpBwdArgs a) {
   constexpr int NSEG = 8 / BITS;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -209,119 +217,114 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
   const uint32_t cb = static_cast<uint32_t>(D) * BITS / 8;
   if (c.lane == 0 && c.row < c.rows) warp_issue_row(a, c.slot, c.bar, c.row, cb, false, true, D);
   float* wsm = reinterpret_cast<float*>(smem + a.off_wsm);
-  uint32_t* omask = reinterpret_cast<uint32_t*>(smem + a.off_chan2);   // ROT: one bit per channel, 1 = outlier channel
+  float* csc = reinterpret_cast<float*>(smem + a.off_chan2);   // REF, per-channel scale: fp32 table (split halves)
+  const bool per_channel = REF && p.scale_kind == kScaleChannel;
   const float plus = a.kind == HYC_NORM_RMS_GEMMA ? 1.f : 0.f;
-  for (int j = threadIdx.x; j < c.k; j += blockDim.x) c.chan[j] = max(0, min(D - 1, p.channels[j]));
-  if (ROT)
-    for (int i = threadIdx.x; i < (D >> 5); i += blockDim.x) omask[i] = 0u;
-  for (int ch = threadIdx.x; ch < D; ch += blockDim.x)
+  if (!REF)
+    for (int j = threadIdx.x; j < c.k; j += blockDim.x) c.chan[j] = max(0, min(D - 1, p.channels[j]));
+  for (int ch = threadIdx.x; ch < D; ch += blockDim.x) {
     wsm[split_index(ch, D)] = (a.param_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.weight)[ch])
                                             : static_cast<const float*>(a.weight)[ch]) + plus;
-  __syncthreads();
-  if (ROT) {
-    for (int j = threadIdx.x; j < c.k; j += blockDim.x) atomicOr(&omask[c.chan[j] >> 5], 1u << (c.chan[j] & 31));
-    __syncthreads();
+    if (per_channel) csc[split_index(ch, D)] = __bfloat162float(p.scale[ch]);
   }
-  c.lanes_channels();
-  const int G = p.group ? (D >> 7) : 1;
+  __syncthreads();
+  if (!REF) c.lanes_channels();
+  const int G = (!REF && p.group) ? (D >> 7) : 1;
   const float inv_d = 1.0f / static_cast<float>(D);
   const __nv_bfloat16* gs = reinterpret_cast<const __nv_bfloat16*>(c.slot + a.off_g);
+  // 0: one scale per row; 1: one per 128 channels (channel mode); 2: one per channel (reference mode)
+  const int scale_mode = REF ? (per_channel ? 2 : 0) : (p.group ? 1 : 0);
   for (; c.row < c.rows; c.row += c.stride, c.ph ^= 1u) {
     const long long row = c.row;
     const float rstd = __ldg(a.rstd + row);
     const float mean = LN ? __ldg(a.mean + row) : 0.f;
     float ov[kWarpOutPerLane];
-#pragma unroll
-    for (int q = 0; q < kWarpOutPerLane; ++q)
-      ov[q] = c.oc[q] >= 0 ? __bfloat162float(p.out_value[row * c.k + c.lane + 32 * q]) : 0.f;
+    uint2 meta = make_uint2(0u, 0u);
     const float* sc_row = p.scales + row * G;
-    const float sc_tok = p.group ? 0.f : __ldg(sc_row);
+    float sc_tok = 0.f;
+    if (REF) {
+      meta = p.row_meta[row];
+      if (!per_channel) sc_tok = __bfloat162float(p.scale[p.scale_kind == kScaleToken ? row % p.seq : 0]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < kWarpOutPerLane; ++q)
+        ov[q] = c.oc[q] >= 0 ? __bfloat162float(p.out_value[row * c.k + c.lane + 32 * q]) : 0.f;
+      sc_tok = p.group ? 0.f : __ldg(sc_row);
+    }
     if (!mbar_wait_bounded(c.bar, c.ph, a.wait_cycles)) {
       if (c.lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
       return;
     }
     float gq[kWarpOutPerLane];
+    if (!REF) {
 #pragma unroll
-    for (int q = 0; q < kWarpOutPerLane; ++q) gq[q] = c.oc[q] >= 0 ? __bfloat162float(gs[c.oc[q]]) : 0.f;
+      for (int q = 0; q < kWarpOutPerLane; ++q) gq[q] = c.oc[q] >= 0 ? __bfloat162float(gs[c.oc[q]]) : 0.f;
+    }
+    // the values of one register group and what goes with them: x-hat, the gradient, the norm weight
+    auto group_operands = [&](auto mode_c, const uint2& cw, int s, int col, f32x2 (&f)[4], f32x2 (&gv)[4], f32x2 (&wv)[4]) {
+      constexpr int kMode = decltype(mode_c)::value;
+      f32x2 sc4[4];
+      if (kMode == 2) {
+        load8_split_pairs(csc, D, col, sc4);
+      } else {
+        const float sg = kMode == 1 ? __ldg(sc_row + (col >> 7)) : sc_tok;
+        sc4[0] = sc4[1] = sc4[2] = sc4[3] = f2_make(sg, sg);
+      }
+      warp_rebuild8_pairs<BITS>(cw, s, sc4, f);
+      unpack_bf16x8_pairs(*reinterpret_cast<const uint4*>(gs + col), gv);
+      load8_split_pairs(wsm, D, col, wv);
+    };
     // ---- pass 1: the two row sums.  With x-hat = (x - mean) * rstd the first one is
     //   c1 = mean_d(x-hat * w dy) = rstd * (S1 - mean * S2) / D,   S1 = sum x * w dy,  S2 = sum w dy,
     // so the pass accumulates S1 and S2 from the rebuilt x itself (two fused multiply-adds per element).
     float s1 = 0.f, s2 = 0.f;
-    if (ROT) {
-  #pragma unroll 2
+    auto pass1 = [&](auto mode_c, auto full_c) {
+      f32x2 s1p = 0ull, s2p = 0ull;
+#pragma unroll 2
       for (int iu = 0; iu < upl; ++iu) {
         const int u = c.lane + 32 * iu;
-        const bool live = u < c.U;
-        const uint2 cw = live ? *reinterpret_cast<const uint2*>(c.slot + (u << 3)) : make_uint2(0u, 0u);
-  #pragma unroll
-        for (int s = 0; s < NSEG; ++s) {
-          const int col = s * c.segw + (u << 3);
-          float f[8];
-          warp_rebuild8<BITS, ROT, true>(cw, s, p.group ? __ldg(sc_row + (min(col, D - 8) >> 7)) : sc_tok, p.rotate, c.lane, f);
-          if (live) {
-            if (ROT) {
-              const uint32_t m = mask8(omask, col);
-              if (m) zero_masked(f, m);
-            }
-            float gv[8], wv[8];
-            load8<__nv_bfloat16>(gs, col, gv);
-            load8_split(wsm, D, col, wv);
-  #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float wd = wv[e] * gv[e];
-              s1 = fmaf(f[e], wd, s1);
-              s2 += wd;
+        if (decltype(full_c)::value || u < c.U) {
+          const uint2 cw = *reinterpret_cast<const uint2*>(c.slot + (u << 3));
+#pragma unroll
+          for (int s = 0; s < NSEG; ++s) {
+            f32x2 f[4], gv[4], wv[4];
+            group_operands(mode_c, cw, s, s * c.segw + (u << 3), f, gv, wv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const f32x2 wd = f2_mul(wv[e], gv[e]);
+              s1p = f2_fma(f[e], wd, s1p);
+              s2p = f2_add(s2p, wd);
             }
           }
         }
       }
+      float lo, hi;
+      f2_split(s1p, lo, hi);
+      s1 = lo + hi;
+      f2_split(s2p, lo, hi);
+      s2 = lo + hi;
+    };
+    using M0 = std::integral_constant<int, 0>;
+    using M1 = std::integral_constant<int, 1>;
+    using M2 = std::integral_constant<int, 2>;
+    using T = std::true_type;
+    using F = std::false_type;
+    if (scale_mode == 0) { if (full) pass1(M0(), T()); else pass1(M0(), F()); }
+    else if (REF) { if (full) pass1(M2(), T()); else pass1(M2(), F()); }
+    else { if (full) pass1(M1(), T()); else pass1(M1(), F()); }
+    // what the streamed pass saw as the zero of its code: the outlier channels' stored originals, or the row's
+    // element outliers from the pool
+    if (REF) {
+      for (uint32_t j = c.lane; j < meta.y; j += 32) {
+        const uint32_t e = p.pool[meta.x + j];
+        const int col = static_cast<int>(e & 0xffffu);
+        s1 = fmaf(bf16_bits_to_float(e >> 16), wsm[split_index(col, D)] * __bfloat162float(gs[col]), s1);
+      }
     } else {
-      // records without rotation: every step of the pass on packed fp32 pairs, compiled per combination of two
-      // launch-wide facts (group scales; every lane owns a unit in every round) so that no test of them sits
-      // between the segments of a unit
-      auto pass1 = [&](auto group_c, auto full_c) {
-        constexpr bool kGroup = decltype(group_c)::value, kFull = decltype(full_c)::value;
-        f32x2 s1p = 0ull, s2p = 0ull;
-        const f32x2 sc_tok2 = f2_make(sc_tok, sc_tok);
-#pragma unroll 2
-        for (int iu = 0; iu < upl; ++iu) {
-          const int u = c.lane + 32 * iu;
-          if (kFull || u < c.U) {
-            const uint2 cw = *reinterpret_cast<const uint2*>(c.slot + (u << 3));
 #pragma unroll
-            for (int s = 0; s < NSEG; ++s) {
-              const int col = s * c.segw + (u << 3);
-              f32x2 sc2 = sc_tok2;
-              if (kGroup) {
-                const float sg = __ldg(sc_row + (col >> 7));
-                sc2 = f2_make(sg, sg);
-              }
-              f32x2 f[4], gv[4], wv[4];
-              warp_rebuild8_pairs<BITS>(cw, s, sc2, f);
-              unpack_bf16x8_pairs(*reinterpret_cast<const uint4*>(gs + col), gv);
-              load8_split_pairs(wsm, D, col, wv);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const f32x2 wd = f2_mul(wv[e], gv[e]);
-                s1p = f2_fma(f[e], wd, s1p);
-                s2p = f2_add(s2p, wd);
-              }
-            }
-          }
-        }
-        float lo, hi;
-        f2_split(s1p, lo, hi);
-        s1 = lo + hi;
-        f2_split(s2p, lo, hi);
-        s2 = lo + hi;
-      };
-      if (p.group) { if (full) pass1(std::true_type(), std::true_type()); else pass1(std::true_type(), std::false_type()); }
-      else { if (full) pass1(std::false_type(), std::true_type()); else pass1(std::false_type(), std::false_type()); }
+      for (int q = 0; q < kWarpOutPerLane; ++q)
+        if (c.oc[q] >= 0) s1 = fmaf(ov[q], wsm[split_index(c.oc[q], D)] * gq[q], s1);
     }
-    // outlier channels: the streamed pass saw the zero their code encodes instead of the stored value
-#pragma unroll
-    for (int q = 0; q < kWarpOutPerLane; ++q)
-      if (c.oc[q] >= 0) s1 = fmaf(ov[q], wsm[split_index(c.oc[q], D)] * gq[q], s1);
     s1 = warp_sum(s1);
     s2 = warp_sum(s2);
     const float c1 = rstd * (s1 - mean * s2) * inv_d;
@@ -329,78 +332,54 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
     // ---- pass 2: dx = (w dy - (x-hat * c1 + c2)) * rstd = ka * w dy + kb * x + kc with three row constants
     const float ka = rstd, kb = -rstd * rstd * c1, kc = (mean * rstd * c1 - c2) * rstd;
     __nv_bfloat16* dxrow = a.out1 + row * D;
-    if (ROT) {
-  #pragma unroll 2
+    auto pass2 = [&](auto mode_c, auto full_c) {
+      const f32x2 ka2 = f2_make(ka, ka), kb2 = f2_make(kb, kb), kc2 = f2_make(kc, kc);
+#pragma unroll 2
       for (int iu = 0; iu < upl; ++iu) {
         const int u = c.lane + 32 * iu;
-        const bool live = u < c.U;
-        const uint2 cw = live ? *reinterpret_cast<const uint2*>(c.slot + (u << 3)) : make_uint2(0u, 0u);
-  #pragma unroll
-        for (int s = 0; s < NSEG; ++s) {
-          const int col = s * c.segw + (u << 3);
-          float f[8];
-          warp_rebuild8<BITS, ROT, true>(cw, s, p.group ? __ldg(sc_row + (min(col, D - 8) >> 7)) : sc_tok, p.rotate, c.lane, f);
-          if (live) {
-            if (ROT) {
-              const uint32_t m = mask8(omask, col);
-              if (m) zero_masked(f, m);
+        if (decltype(full_c)::value || u < c.U) {
+          const uint2 cw = *reinterpret_cast<const uint2*>(c.slot + (u << 3));
+#pragma unroll
+          for (int s = 0; s < NSEG; ++s) {
+            const int col = s * c.segw + (u << 3);
+            f32x2 f[4], gv[4], wv[4];
+            group_operands(mode_c, cw, s, col, f, gv, wv);
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float lo, hi;
+              f2_split(f2_fma(ka2, f2_mul(wv[e], gv[e]), f2_fma(kb2, f[e], kc2)), lo, hi);
+              o[e] = pack_bf16x2(lo, hi);
             }
-            float gv[8], wv[8], d[8];
-            load8<__nv_bfloat16>(gs, col, gv);
-            load8_split(wsm, D, col, wv);
-  #pragma unroll
-            for (int e = 0; e < 8; ++e) d[e] = fmaf(ka, wv[e] * gv[e], fmaf(kb, f[e], kc));
-            store8<__nv_bfloat16>(dxrow, col, d);
+            *reinterpret_cast<uint4*>(dxrow + col) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         }
       }
-    } else {
-      auto pass2 = [&](auto group_c, auto full_c) {
-        constexpr bool kGroup = decltype(group_c)::value, kFull = decltype(full_c)::value;
-        const f32x2 sc_tok2 = f2_make(sc_tok, sc_tok);
-        const f32x2 ka2 = f2_make(ka, ka), kb2 = f2_make(kb, kb), kc2 = f2_make(kc, kc);
-#pragma unroll 2
-        for (int iu = 0; iu < upl; ++iu) {
-          const int u = c.lane + 32 * iu;
-          if (kFull || u < c.U) {
-            const uint2 cw = *reinterpret_cast<const uint2*>(c.slot + (u << 3));
-#pragma unroll
-            for (int s = 0; s < NSEG; ++s) {
-              const int col = s * c.segw + (u << 3);
-              f32x2 sc2 = sc_tok2;
-              if (kGroup) {
-                const float sg = __ldg(sc_row + (col >> 7));
-                sc2 = f2_make(sg, sg);
-              }
-              f32x2 f[4], gv[4], wv[4];
-              warp_rebuild8_pairs<BITS>(cw, s, sc2, f);
-              unpack_bf16x8_pairs(*reinterpret_cast<const uint4*>(gs + col), gv);
-              load8_split_pairs(wsm, D, col, wv);
-              uint32_t o[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float lo, hi;
-                f2_split(f2_fma(ka2, f2_mul(wv[e], gv[e]), f2_fma(kb2, f[e], kc2)), lo, hi);
-                o[e] = pack_bf16x2(lo, hi);
-              }
-              *reinterpret_cast<uint4*>(dxrow + col) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-      };
-      if (p.group) { if (full) pass2(std::true_type(), std::true_type()); else pass2(std::true_type(), std::false_type()); }
-      else { if (full) pass2(std::false_type(), std::true_type()); else pass2(std::false_type(), std::false_type()); }
+    };
+    if (scale_mode == 0) { if (full) pass2(M0(), T()); else pass2(M0(), F()); }
+    else if (REF) { if (full) pass2(M2(), T()); else pass2(M2(), F()); }
+    else { if (full) pass2(M1(), T()); else pass2(M1(), F()); }
+    __syncwarp();   // the vector stores come before the results at the outliers (other lanes)
+    if (REF) {
+      for (uint32_t j = c.lane; j < meta.y; j += 32) {
+        const uint32_t e = p.pool[meta.x + j];
+        const int col = static_cast<int>(e & 0xffffu);
+        dxrow[col] = __float2bfloat16_rn(fmaf(ka, wsm[split_index(col, D)] * __bfloat162float(gs[col]),
+                                              fmaf(kb, bf16_bits_to_float(e >> 16), kc)));
+      }
+      __syncwarp();   // every lane is done with the slot
     }
-    __syncwarp();   // every lane is done with the slot; the vector stores come before the outlier channels' results
     const long long next = row + c.stride;
     if (c.lane == 0 && next < c.rows) {
       fence_proxy_async();
       warp_issue_row(a, c.slot, c.bar, next, cb, false, true, D);
     }
+    if (!REF) {
 #pragma unroll
-    for (int q = 0; q < kWarpOutPerLane; ++q) {
-      if (c.oc[q] >= 0)
-        dxrow[c.oc[q]] = __float2bfloat16_rn(fmaf(ka, wsm[split_index(c.oc[q], D)] * gq[q], fmaf(kb, ov[q], kc)));
+      for (int q = 0; q < kWarpOutPerLane; ++q) {
+        if (c.oc[q] >= 0)
+          dxrow[c.oc[q]] = __float2bfloat16_rn(fmaf(ka, wsm[split_index(c.oc[q], D)] * gq[q], fmaf(kb, ov[q], kc)));
+      }
     }
   }
 }
@@ -421,13 +400,17 @@ inline WarpBwdPlan plan_warp_bwd(const hyc_packed* q, const hyc_packed* q2, bool
   WarpBwdPlan w;
   memset(&w, 0, sizeof(w));
   static const bool off_env = getenv("HYC_BWD_WARP") && getenv("HYC_BWD_WARP")[0] == '0';
-  if (off_env || q->mode != HYC_MODE_N || (q2 && q2->mode != HYC_MODE_N)) return w;
+  // reference-mode records: the norm backward only (want_w), without a low-rank part, columns that fit 16 bits
+  const bool ref = q->mode == HYC_MODE_R;
+  if (off_env || (ref && (!want_w || q2 || q->lowrank || q->seq <= 0 || q->cols > 65535)) ||
+      (!ref && q->mode != HYC_MODE_N) || (q2 && q2->mode != HYC_MODE_N))
+    return w;
   if (q->bits != 2 && q->bits != 4 && q->bits != 8) return w;
-  if (q->n_channels > 32 * kWarpOutPerLane || (q2 && q2->n_channels > 32 * kWarpOutPerLane)) return w;
+  if (!ref && (q->n_channels > 32 * kWarpOutPerLane || (q2 && q2->n_channels > 32 * kWarpOutPerLane))) return w;
   if (g_tune_threads || g_tune_stages || g_tune_ctas) return w;
   const int D = q->cols, nseg = 8 / q->bits;
-  if (q->rotate && (q->rotate > 256 || (D / nseg) % 256 != 0)) return w;
-  if (q->group && (D / nseg) % 128 != 0) return w;
+  if (!ref && q->rotate && (q->rotate > 256 || (D / nseg) % 256 != 0)) return w;
+  if (!ref && q->group && (D / nseg) % 128 != 0) return w;
   const int U = D / nseg / 8;
   const int upl = (U + 31) / 32;
   int ng = nseg;
@@ -437,9 +420,10 @@ inline WarpBwdPlan plan_warp_bwd(const hyc_packed* q, const hyc_packed* q2, bool
   w.ng = ng;
   uint32_t off = 64 * 8;
   auto take = [&](uint32_t bytes) { uint32_t o = off; off = align_up(off + bytes, 16); return o; };
-  w.off_chan = take((q->n_channels > 0 ? q->n_channels : 1) * 4);
-  // second channel list (product), or the outlier-channel bitmap of the rotating norm backward
-  w.off_chan2 = take(want_w ? static_cast<uint32_t>(D) / 8u : (q2 && q2->n_channels > 0 ? q2->n_channels : 1) * 4);
+  w.off_chan = take((!ref && q->n_channels > 0 ? q->n_channels : 1) * 4);
+  // second channel list (product), or the per-channel scale table of a reference-mode record (fp32 [D])
+  w.off_chan2 = take(ref ? (q->scale_kind == HYC_SCALE_CHANNEL ? static_cast<uint32_t>(D) * 4u : 16u)
+                         : (q2 && q2->n_channels > 0 ? q2->n_channels : 1) * 4);
   if (want_w) w.off_wsm = take(D * 4);
   off = align_up(off, 128);
   w.off_slots = off;

@@ -3,7 +3,7 @@
 
 namespace hyc {
 int launch_norm_bwd_warp(const WarpBwdArgs& a, const WarpBwdPlan& w, cudaStream_t stream) {
-  const bool rot = a.p.rotate != 0;
+  const bool ref = a.p.mode == HYC_MODE_R;
   const bool ln = a.kind == HYC_NORM_LAYER;
 #define HYC_K(B, NGV, RT, LNV)                                                                   \
   {                                                                                              \
@@ -14,7 +14,7 @@ int launch_norm_bwd_warp(const WarpBwdArgs& a, const WarpBwdPlan& w, cudaStream_
   }
 #define HYC_L(B, NGV)                                                                            \
   {                                                                                              \
-    if (rot) { if (ln) HYC_K(B, NGV, true, true) else HYC_K(B, NGV, true, false) }               \
+    if (ref) { if (ln) HYC_K(B, NGV, true, true) else HYC_K(B, NGV, true, false) }               \
     else { if (ln) HYC_K(B, NGV, false, true) else HYC_K(B, NGV, false, false) }                 \
   }
   HYC_WARP_BWD_DISPATCH(a.p.bits, w.ng, HYC_L)

@@ -383,6 +383,35 @@ def test_norm_backward_matches_oracle(pk, kind, mode, bits, gdtype, d, rotate):
     assert dw2 is None and _rel_err(dx2, oc.norm_backward(xh, dy, w, mean_o, rstd_o, kind)[0]) < 1e-2
 
 
+@pytest.mark.parametrize("kind,bits,method,d", [
+    ("rms", 4, "per-channel", 4096), ("rms", 2, "per-channel", 2048), ("ln", 8, "per-channel", 1024),
+    ("rms", 4, "per-token", 768), ("ln", 2, "per-token", 4096), ("rms_gemma", 8, "per-tensor", 768),
+    ("ln", 4, "per-tensor", 3072)])
+def test_reference_mode_norm_backward_one_warp_per_row(pk, kind, bits, method, d):
+    """Frozen norm weight, bf16 gradient, reference-mode record without a low-rank part: the warp-per-row
+    kernel (static scales per channel / token / tensor, the row's element outliers put right from the pool
+    after each pass).  Checked element by element, the outlier positions on their own as well."""
+    b, s = 5, 67
+    x, _ = synthetic.roundtrip_activation(b, s, d, planted=6, gain=20.0, dtype=torch.bfloat16, salt=d + bits)
+    w = synthetic.norm_weight(d, 0.1, dtype=torch.float32)
+    dy = torch.randn(b, s, d, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16)
+    thr, L, R, scale = oc.r_calibrate(x, 0.02, 1.0, bits, method, 0)
+    c = oc.r_compress(x, thr, scale, bits, 1.0)
+    xh = oc.r_decompress(c)
+    p = pk.compress_r(x.to(DEV), thr.to(DEV), scale.to(DEV), bits, outlier_ratio=0.05)
+    assert int(p.pool_used.item()) > 0 and not p.overflowed()
+    _, mean_o, rstd_o = oc.norm_forward(x, w, torch.zeros(d), 1e-5, kind)
+    for compat in (True, False):
+        dx_o = oc.norm_backward(xh, dy, w, mean_o, rstd_o, kind, ref_compat_c2=compat)[0].float()
+        dx = pk.norm_bwd(p, dy.to(DEV), w.to(DEV), rstd_o.to(DEV), None if mean_o is None else mean_o.to(DEV), kind,
+                         ref_compat_c2=compat)[0].float().cpu()
+        tol = 1.6e-2 * dx_o.abs() + 2e-3 * dx_o.abs().max()
+        assert ((dx - dx_o).abs() <= tol).all()
+        out = (x.float().abs() > thr.float()).reshape(dx.shape)          # the element outliers
+        assert out.any() and ((dx - dx_o).abs()[out] <= tol[out]).all()
+    assert not p.wait_expired()
+
+
 @pytest.mark.parametrize("op,mode,bits,gdtype,d,rotate", [
     ("silu", "N", 4, torch.bfloat16, 11008, 256), ("silu", "R", 8, torch.bfloat16, 1024, 0),
     ("gelu", "R", 4, torch.float32, 3072, 0), ("gelu", "N", 4, torch.bfloat16, 3072, 0),
