@@ -135,29 +135,47 @@ __device__ __forceinline__ void load8_split_pairs(const float* table, int D, int
 
 // ------------------------------------------------------------------ decompress
 
-template <int BITS, int NG, bool ROT>
+// KIND 0: channel-mode record; 1: rotated channel-mode record; 2: reference-mode record without a low-rank part
+// (static scales: an fp32 table per channel, or one per row; the row's element outliers -- stored values with
+// their columns in the pool -- overwrite the zeros their codes gave, as the outlier channels' originals do).
+template <int BITS, int NG, int KIND>
 __global__ void __launch_bounds__(kWarpKernelThreads, 2) decompress_n_warp_kernel(const __grid_constant__ WarpBwdArgs a) {
   using Ctx = WarpRowCtx<BITS, NG>;
   constexpr int NSEG = Ctx::NSEG, UPL = Ctx::UPL;
+  constexpr bool ROT = KIND == 1, REF = KIND == 2;
   extern __shared__ __align__(128) unsigned char smem[];
   const PackedDev& p = a.p;
   Ctx c;
   c.init(a, smem);
   const uint32_t cb = static_cast<uint32_t>(c.D) * BITS / 8;
   if (c.lane == 0 && c.row < c.rows) warp_issue_row(a, c.slot, c.bar, c.row, cb, false, false, c.D);
-  for (int j = threadIdx.x; j < c.k; j += blockDim.x) c.chan[j] = max(0, min(c.D - 1, p.channels[j]));
+  float* csc = reinterpret_cast<float*>(smem + a.off_chan2);   // REF, per-channel scale: fp32 table (split halves)
+  const bool per_channel = REF && p.scale_kind == kScaleChannel;
+  if (REF) {
+    if (per_channel)
+      for (int ch = threadIdx.x; ch < c.D; ch += blockDim.x) csc[split_index(ch, c.D)] = __bfloat162float(p.scale[ch]);
+  } else {
+    for (int j = threadIdx.x; j < c.k; j += blockDim.x) c.chan[j] = max(0, min(c.D - 1, p.channels[j]));
+  }
   __syncthreads();
-  c.lanes_channels();
-  const int G = p.group ? (c.D >> 7) : 1;
+  if (!REF) c.lanes_channels();
+  const int G = (!REF && p.group) ? (c.D >> 7) : 1;
   for (; c.row < c.rows; c.row += c.stride, c.ph ^= 1u) {
     const long long row = c.row;
     // the stored originals of the outlier channels, fetched before the wait
     __nv_bfloat16 ov[kWarpOutPerLane];
-#pragma unroll
-    for (int q = 0; q < kWarpOutPerLane; ++q)
-      ov[q] = c.oc[q] >= 0 ? p.out_value[row * c.k + c.lane + 32 * q] : __float2bfloat16_rn(0.f);
+    uint2 meta = make_uint2(0u, 0u);
     const float* sc_row = p.scales + row * G;
-    const float sc_tok = p.group ? 0.f : __ldg(sc_row);
+    float sc_tok = 0.f;
+    if (REF) {
+      meta = p.row_meta[row];
+      if (!per_channel) sc_tok = __bfloat162float(p.scale[p.scale_kind == kScaleToken ? row % p.seq : 0]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < kWarpOutPerLane; ++q)
+        ov[q] = c.oc[q] >= 0 ? p.out_value[row * c.k + c.lane + 32 * q] : __float2bfloat16_rn(0.f);
+      sc_tok = p.group ? 0.f : __ldg(sc_row);
+    }
     if (!mbar_wait_bounded(c.bar, c.ph, a.wait_cycles)) {
       if (c.lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
       return;
@@ -177,14 +195,31 @@ __global__ void __launch_bounds__(kWarpKernelThreads, 2) decompress_n_warp_kerne
     for (int r = 0; r < NG; ++r) {
       const int col = c.col(r);
       float f[8];
-      const float sc = p.group ? __ldg(sc_row + (min(col, c.D - 8) >> 7)) : sc_tok;
-      warp_rebuild8<BITS, ROT, false>(cw[r / NSEG], r % NSEG, sc, p.rotate, c.lane, f);
+      if (REF) {
+        dequant8<BITS>(cw[r / NSEG], r % NSEG, per_channel ? 1.f : sc_tok, f);
+        if (per_channel) {
+          float sc[8];
+          load8_split(csc, c.D, min(col, c.D - 8), sc);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] *= sc[e];
+        }
+      } else {
+        const float sc = p.group ? __ldg(sc_row + (min(col, c.D - 8) >> 7)) : sc_tok;
+        warp_rebuild8<BITS, ROT, false>(cw[r / NSEG], r % NSEG, sc, p.rotate, c.lane, f);
+      }
       if (c.live(r)) store8<__nv_bfloat16>(orow, col, f);
     }
-    __syncwarp();   // the vector stores come before the originals of the outlier channels
+    __syncwarp();   // the vector stores come before the stored originals (other lanes)
+    if (REF) {
+      for (uint32_t j = c.lane; j < meta.y; j += 32) {
+        const uint32_t e = p.pool[meta.x + j];
+        reinterpret_cast<uint16_t*>(orow)[e & 0xffffu] = static_cast<uint16_t>(e >> 16);
+      }
+    } else {
 #pragma unroll
-    for (int q = 0; q < kWarpOutPerLane; ++q)
-      if (c.oc[q] >= 0) orow[c.oc[q]] = ov[q];
+      for (int q = 0; q < kWarpOutPerLane; ++q)
+        if (c.oc[q] >= 0) orow[c.oc[q]] = ov[q];
+    }
   }
 }
 
@@ -400,9 +435,9 @@ inline WarpBwdPlan plan_warp_bwd(const hyc_packed* q, const hyc_packed* q2, bool
   WarpBwdPlan w;
   memset(&w, 0, sizeof(w));
   static const bool off_env = getenv("HYC_BWD_WARP") && getenv("HYC_BWD_WARP")[0] == '0';
-  // reference-mode records: the norm backward only (want_w), without a low-rank part, columns that fit 16 bits
+  // reference-mode records: decompress and the norm backward, without a low-rank part, columns that fit 16 bits
   const bool ref = q->mode == HYC_MODE_R;
-  if (off_env || (ref && (!want_w || q2 || q->lowrank || q->seq <= 0 || q->cols > 65535)) ||
+  if (off_env || (ref && (want_w != grad || q2 || q->lowrank || q->seq <= 0 || q->cols > 65535)) ||
       (!ref && q->mode != HYC_MODE_N) || (q2 && q2->mode != HYC_MODE_N))
     return w;
   if (q->bits != 2 && q->bits != 4 && q->bits != 8) return w;

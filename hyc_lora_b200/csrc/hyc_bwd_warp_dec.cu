@@ -3,16 +3,21 @@
 
 namespace hyc {
 int launch_decompress_warp(const WarpBwdArgs& a, const WarpBwdPlan& w, cudaStream_t stream) {
-  const bool rot = a.p.rotate != 0;
+  const bool rot = a.p.rotate != 0, ref = a.p.mode == HYC_MODE_R;
 #define HYC_L(B, NGV)                                                                            \
   {                                                                                              \
-    if (rot) {                                                                                   \
-      auto kern = decompress_n_warp_kernel<B, NGV, true>;                                        \
+    if (ref) {                                                                                   \
+      auto kern = decompress_n_warp_kernel<B, NGV, 2>;                                           \
+      int rc = set_smem(kern, w.total);                                                          \
+      if (rc) return rc;                                                                         \
+      kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                  \
+    } else if (rot) {                                                                            \
+      auto kern = decompress_n_warp_kernel<B, NGV, 1>;                                           \
       int rc = set_smem(kern, w.total);                                                          \
       if (rc) return rc;                                                                         \
       kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                  \
     } else {                                                                                     \
-      auto kern = decompress_n_warp_kernel<B, NGV, false>;                                       \
+      auto kern = decompress_n_warp_kernel<B, NGV, 0>;                                           \
       int rc = set_smem(kern, w.total);                                                          \
       if (rc) return rc;                                                                         \
       kern<<<w.grid, w.threads, w.total, stream>>>(a); HYC_LAUNCHED();                  \
