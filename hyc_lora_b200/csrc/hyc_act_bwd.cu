@@ -1,5 +1,6 @@
 // Decompress + SiLU / GELU(tanh) / product backward.
 #include "hyc_bwd_fast.cuh"
+#include "hyc_bwd_warp.cuh"
 
 namespace hyc {
 
@@ -125,6 +126,19 @@ int hyc_act_bwd(int op, const hyc_packed* s1, const hyc_packed* s2, const void* 
   }
   if (s1->rows == 0) return HYC_OK;
   const int D = s1->cols;
+  if (!prod && g_dtype == HYC_BF16 && !s1->rotate) {
+    // SiLU / GELU, bf16 gradient, rows of up to 4096 channels without rotation: one warp per row
+    WarpBwdPlan wp = plan_warp_bwd(s1, nullptr, true, false, kNormBwdWarpThreads, 1);
+    if (!wp.ok) wp = plan_warp_bwd(s1, nullptr, true, false, 512, 1);
+    if (!wp.ok) wp = plan_warp_bwd(s1, nullptr, true, false, 384, 1);
+    if (wp.ok) {
+      WarpBwdArgs wa;
+      fill_warp_bwd(&wa, wp, s1, nullptr);
+      wa.g = static_cast<const __nv_bfloat16*>(g);
+      wa.out1 = static_cast<__nv_bfloat16*>(dx1);
+      return launch_act_bwd_warp(wa, wp, op == HYC_ACT_GELU_TANH, stream);
+    }
+  }
   {
     const BwdPlan bp = plan_bwd_fast(s1, prod ? s2 : nullptr, 4, false, 0, 512, 0,
                                      align_up(static_cast<uint32_t>(D) * s1->bits / 8, 128) * (prod ? 2 : 1) +

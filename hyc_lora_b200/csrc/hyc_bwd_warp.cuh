@@ -1,16 +1,19 @@
-// Warp-per-row consumers of a channel-mode record (rows of up to 4096 channels): decompress, and
-// decompress + norm backward with a frozen norm weight and a bf16 gradient.
+// Warp-per-row consumers of a record (rows of up to 4096 channels; channel-mode records, and reference-mode
+// records without a low-rank part): decompress, decompress + norm backward with a frozen norm weight and a bf16
+// gradient, decompress + SiLU / GELU backward with a bf16 gradient.
 //
 // Same walk as the warp-per-row forward kernel: a warp owns its rows; the packed codes (and the gradient
 // row) of a row land in the warp's own shared-memory slot by bulk asynchronous copies on the warp's own
 // mbarrier; reductions are warp shuffles, and there is no CTA barrier in the row loop.  The decompress
 // moves the codes into registers and hands the slot straight back to the copy engine; the norm backward
-// makes its two passes (the two row sums, then the result) over the slot itself and rebuilds the values
-// from the codes in both.  Outlier channels are streamed as the zero their code encodes and put right
-// afterwards by the lanes that look after them (after the inverse rotation they are cleared first, the
-// correction assumes a zero).  Arithmetic per element is that of the CTA-per-row kernels in
-// hyc_bwd_fast.cuh.  (The activation backward stays on those: with its exponentials it is bound by
-// instruction issue, not by the row barrier, and measured faster there.)
+// makes its two passes (the two row sums, then the result) and the activation backward its one pass over the
+// slot itself, in short rolled loops on packed fp32 pairs, and rebuild the values from the codes there.
+// Outliers (the outlier channels of a channel-mode record, the pool entries of a reference-mode row) are
+// streamed as the zero their code encodes and put right afterwards by the lanes that look after them (after the
+// inverse rotation they are cleared first, the correction assumes a zero).  Arithmetic per element is that of
+// the CTA-per-row kernels in hyc_bwd_fast.cuh, which keep the product backward, fp32 gradients, rotated
+// records and wider rows.  (A first warp-per-row activation backward held the whole row in registers, spilled and
+// measured slower than those; the rolled loop over the slot needs few registers.)
 #pragma once
 #include <stdlib.h>
 
@@ -419,6 +422,147 @@ __global__ void __launch_bounds__(kNormBwdWarpThreads, 1) norm_bwd_n_warp_kernel
   }
 }
 
+// ------------------------------------------------------------------ activation backward (SiLU / GELU)
+
+__device__ __forceinline__ float ex2_approx(float x) {   // what __expf evaluates after its scaling by log2(e)
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// silu'(x) * g for two channels: silu_grad_f's formula on packed fp32 pairs (the exponential and the reciprocal
+// stay one channel at a time: they run on the special-function unit)
+__device__ __forceinline__ f32x2 silu_grad_times_pairs(f32x2 x2, f32x2 g2) {
+  const f32x2 one2 = f2_make(1.f, 1.f);
+  float t0, t1;
+  f2_split(f2_mul(x2, f2_make(-1.4426950408889634f, -1.4426950408889634f)), t0, t1);
+  float d0, d1;
+  f2_split(f2_add(f2_make(ex2_approx(t0), ex2_approx(t1)), one2), d0, d1);
+  const f32x2 s2 = f2_make(__fdividef(1.f, d0), __fdividef(1.f, d1));
+  return f2_mul(f2_mul(s2, f2_fma(x2, f2_sub(one2, s2), one2)), g2);
+}
+
+// dx = act'(x-hat) * g for bf16 gradients, rows of up to 4096 channels, records without rotation (channel mode)
+// or reference-mode records without a low-rank part.  One pass over the warp's slot (codes + gradient row) in a
+// short rolled loop, twenty warps per SM; the outliers are put right afterwards as in the norm backward.
+template <int BITS, bool REF, bool GELU>
+__global__ void __launch_bounds__(kNormBwdWarpThreads, 1) act_bwd_n_warp_kernel(const __grid_constant__ WarpBwdArgs a) {
+  constexpr int NSEG = 8 / BITS;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const PackedDev& p = a.p;
+  WarpRowCtx<BITS, NSEG> c;
+  c.init(a, smem);
+  const int D = c.D;
+  const int upl = (c.U + 31) >> 5;
+  const bool full = (c.U & 31) == 0;
+  const uint32_t cb = static_cast<uint32_t>(D) * BITS / 8;
+  if (c.lane == 0 && c.row < c.rows) warp_issue_row(a, c.slot, c.bar, c.row, cb, false, true, D);
+  float* csc = reinterpret_cast<float*>(smem + a.off_chan2);   // REF, per-channel scale: fp32 table (split halves)
+  const bool per_channel = REF && p.scale_kind == kScaleChannel;
+  if (REF) {
+    if (per_channel)
+      for (int ch = threadIdx.x; ch < D; ch += blockDim.x) csc[split_index(ch, D)] = __bfloat162float(p.scale[ch]);
+  } else {
+    for (int j = threadIdx.x; j < c.k; j += blockDim.x) c.chan[j] = max(0, min(D - 1, p.channels[j]));
+  }
+  __syncthreads();
+  if (!REF) c.lanes_channels();
+  const int G = (!REF && p.group) ? (D >> 7) : 1;
+  const __nv_bfloat16* gs = reinterpret_cast<const __nv_bfloat16*>(c.slot + a.off_g);
+  const int scale_mode = REF ? (per_channel ? 2 : 0) : (p.group ? 1 : 0);
+  auto grad_of = [&](float x) { return GELU ? gelu_tanh_grad_f(x) : silu_grad_f(x); };
+  for (; c.row < c.rows; c.row += c.stride, c.ph ^= 1u) {
+    const long long row = c.row;
+    float ov[kWarpOutPerLane];
+    uint2 meta = make_uint2(0u, 0u);
+    const float* sc_row = p.scales + row * G;
+    float sc_tok = 0.f;
+    if (REF) {
+      meta = p.row_meta[row];
+      if (!per_channel) sc_tok = __bfloat162float(p.scale[p.scale_kind == kScaleToken ? row % p.seq : 0]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < kWarpOutPerLane; ++q)
+        ov[q] = c.oc[q] >= 0 ? __bfloat162float(p.out_value[row * c.k + c.lane + 32 * q]) : 0.f;
+      sc_tok = p.group ? 0.f : __ldg(sc_row);
+    }
+    if (!mbar_wait_bounded(c.bar, c.ph, a.wait_cycles)) {
+      if (c.lane == 0 && p.status) atomicOr(p.status, kStatusWaitExpired);
+      return;
+    }
+    float gq[kWarpOutPerLane];
+    if (!REF) {
+#pragma unroll
+      for (int q = 0; q < kWarpOutPerLane; ++q) gq[q] = c.oc[q] >= 0 ? __bfloat162float(gs[c.oc[q]]) : 0.f;
+    }
+    __nv_bfloat16* dxrow = a.out1 + row * D;
+    auto pass = [&](auto mode_c, auto full_c) {
+      constexpr int kMode = decltype(mode_c)::value;
+#pragma unroll 2
+      for (int iu = 0; iu < upl; ++iu) {
+        const int u = c.lane + 32 * iu;
+        if (decltype(full_c)::value || u < c.U) {
+          const uint2 cw = *reinterpret_cast<const uint2*>(c.slot + (u << 3));
+#pragma unroll
+          for (int s = 0; s < NSEG; ++s) {
+            const int col = s * c.segw + (u << 3);
+            f32x2 sc4[4], f[4], gv[4];
+            if (kMode == 2) {
+              load8_split_pairs(csc, D, col, sc4);
+            } else {
+              const float sg = kMode == 1 ? __ldg(sc_row + (col >> 7)) : sc_tok;
+              sc4[0] = sc4[1] = sc4[2] = sc4[3] = f2_make(sg, sg);
+            }
+            warp_rebuild8_pairs<BITS>(cw, s, sc4, f);
+            unpack_bf16x8_pairs(*reinterpret_cast<const uint4*>(gs + col), gv);
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float lo, hi;
+              if (GELU) {
+                float x0, x1, g0, g1;
+                f2_split(f[e], x0, x1);
+                f2_split(gv[e], g0, g1);
+                lo = gelu_tanh_grad_f(x0) * g0;
+                hi = gelu_tanh_grad_f(x1) * g1;
+              } else {
+                f2_split(silu_grad_times_pairs(f[e], gv[e]), lo, hi);
+              }
+              o[e] = pack_bf16x2(lo, hi);
+            }
+            *reinterpret_cast<uint4*>(dxrow + col) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+    };
+    using M0 = std::integral_constant<int, 0>;
+    using M1 = std::integral_constant<int, 1>;
+    using M2 = std::integral_constant<int, 2>;
+    if (scale_mode == 0) { if (full) pass(M0(), std::true_type()); else pass(M0(), std::false_type()); }
+    else if (REF) { if (full) pass(M2(), std::true_type()); else pass(M2(), std::false_type()); }
+    else { if (full) pass(M1(), std::true_type()); else pass(M1(), std::false_type()); }
+    __syncwarp();   // the vector stores come before the results at the outliers (other lanes)
+    if (REF) {
+      for (uint32_t j = c.lane; j < meta.y; j += 32) {
+        const uint32_t e = p.pool[meta.x + j];
+        const int col = static_cast<int>(e & 0xffffu);
+        dxrow[col] = __float2bfloat16_rn(grad_of(bf16_bits_to_float(e >> 16)) * __bfloat162float(gs[col]));
+      }
+      __syncwarp();   // every lane is done with the slot
+    }
+    const long long next = row + c.stride;
+    if (c.lane == 0 && next < c.rows) {
+      fence_proxy_async();
+      warp_issue_row(a, c.slot, c.bar, next, cb, false, true, D);
+    }
+    if (!REF) {
+#pragma unroll
+      for (int q = 0; q < kWarpOutPerLane; ++q)
+        if (c.oc[q] >= 0) dxrow[c.oc[q]] = __float2bfloat16_rn(grad_of(ov[q]) * gq[q]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ host: eligibility and launch
 
 struct WarpBwdPlan {
@@ -435,9 +579,9 @@ inline WarpBwdPlan plan_warp_bwd(const hyc_packed* q, const hyc_packed* q2, bool
   WarpBwdPlan w;
   memset(&w, 0, sizeof(w));
   static const bool off_env = getenv("HYC_BWD_WARP") && getenv("HYC_BWD_WARP")[0] == '0';
-  // reference-mode records: decompress and the norm backward, without a low-rank part, columns that fit 16 bits
+  // reference-mode records: the single-record consumers, without a low-rank part, columns that fit 16 bits
   const bool ref = q->mode == HYC_MODE_R;
-  if (off_env || (ref && (want_w != grad || q2 || q->lowrank || q->seq <= 0 || q->cols > 65535)) ||
+  if (off_env || (ref && (q2 || q->lowrank || q->seq <= 0 || q->cols > 65535)) ||
       (!ref && q->mode != HYC_MODE_N) || (q2 && q2->mode != HYC_MODE_N))
     return w;
   if (q->bits != 2 && q->bits != 4 && q->bits != 8) return w;
@@ -501,5 +645,6 @@ inline void fill_warp_bwd(WarpBwdArgs* a, const WarpBwdPlan& w, const hyc_packed
 
 int launch_decompress_warp(const WarpBwdArgs& a, const WarpBwdPlan& w, cudaStream_t stream);
 int launch_norm_bwd_warp(const WarpBwdArgs& a, const WarpBwdPlan& w, cudaStream_t stream);
+int launch_act_bwd_warp(const WarpBwdArgs& a, const WarpBwdPlan& w, bool gelu, cudaStream_t stream);
 
 }  // namespace hyc

@@ -416,7 +416,12 @@ def test_reference_mode_norm_backward_one_warp_per_row(pk, kind, bits, method, d
     ("silu", "N", 4, torch.bfloat16, 11008, 256), ("silu", "R", 8, torch.bfloat16, 1024, 0),
     ("gelu", "R", 4, torch.float32, 3072, 0), ("gelu", "N", 4, torch.bfloat16, 3072, 0),
     ("product", "N", 4, torch.bfloat16, 11008, 0), ("product", "R", 4, torch.bfloat16, 1024, 0),
-    ("product", "N", 2, torch.float32, 1024, 256)])
+    ("product", "N", 2, torch.float32, 1024, 256),
+    # bf16 gradients, rows of up to 4096 channels without rotation: the warp-per-row kernel (whole and ragged
+    # rounds of units, channel-mode and reference-mode records)
+    ("silu", "N", 4, torch.bfloat16, 4096, 0), ("silu", "N", 2, torch.bfloat16, 768, 0),
+    ("gelu", "N", 8, torch.bfloat16, 2048, 0), ("silu", "R", 4, torch.bfloat16, 4096, 0),
+    ("gelu", "R", 2, torch.bfloat16, 768, 0), ("silu", "R", 8, torch.bfloat16, 3072, 0)])
 def test_activation_backward_matches_oracle(pk, op, mode, bits, gdtype, d, rotate):
     b, s = 2, 23
     x1, _ = synthetic.roundtrip_activation(b, s, d, planted=6, gain=4.0, dtype=torch.bfloat16, salt=d)
