@@ -80,7 +80,10 @@ __device__ __forceinline__ uint32_t f2_to_bf16x2(f32x2 v, f32x2& rounded) {
 
 // (decompress needs nothing row-wide: it rebuilds and stores one segment's chunk at a time -- with two or four
 // segments that is 64 or 32 fp32 values in flight instead of 128, and two CTAs share an SM)
-template <int BITS, int OP, int CH, bool GROUP>
+// RN: the rotation block when the kernel is compiled for one (256: no test of the block size in front of the
+// butterfly stages), or 0: the record's own, read at run time.  The launcher takes RN = 256 for long inputs only:
+// inside a training step a launch starts with cold instruction caches, where the smaller code counts for more.
+template <int BITS, int OP, int CH, bool GROUP, int RN = 0>
 __global__ void __launch_bounds__(kChunkBwdWarps * 32, (OP == kChunkDecompress && BITS < 8) ? 2 : 1)
 bwd_n_chunk_kernel(const __grid_constant__ ChunkBwdArgs a, const __grid_constant__ CUtensorMap dy_map,
                    const __grid_constant__ CUtensorMap out_map) {
@@ -185,7 +188,7 @@ bwd_n_chunk_kernel(const __grid_constant__ ChunkBwdArgs a, const __grid_constant
 #pragma unroll
         for (int e = 0; e < 8; ++e) vs[8 * i + e] = f[e];
       }
-      rotate_chunk<CH>(vs, p.rotate, lane);
+      rotate_chunk<CH>(vs, RN ? RN : p.rotate, lane);
     };
     auto to_slot = [&](int s, f32x2 (&vs)[CH / 2]) {
 #pragma unroll
@@ -369,15 +372,24 @@ inline ChunkBwdPlan plan_chunk_bwd(const hyc_packed* q, bool norm) {
   return w;
 }
 
+constexpr long long kChunkBwdLongRows = 8192;   // from here on the kernel compiled for the block of 256 is taken
+
 template <int BITS, int CH>
 int launch_bwd_chunk_one(const ChunkBwdArgs& a, const ChunkBwdPlan& w, int op, const CUtensorMap& dy_map,
                          const CUtensorMap& out_map, cudaStream_t stream) {
 #define HYC_CB_LAUNCH(OP, GROUP)                                                                \
   {                                                                                             \
-    auto kern = bwd_n_chunk_kernel<BITS, OP, CH, GROUP>;                                        \
-    int rc = set_smem(kern, w.total);                                                           \
-    if (rc) return rc;                                                                          \
-    kern<<<w.grid, kChunkBwdWarps * 32, w.total, stream>>>(a, dy_map, out_map); HYC_LAUNCHED(); \
+    if (!GROUP && a.p.rotate == 256 && a.p.rows >= kChunkBwdLongRows) {                         \
+      auto kern = bwd_n_chunk_kernel<BITS, OP, CH, false, 256>;                                 \
+      int rc = set_smem(kern, w.total);                                                         \
+      if (rc) return rc;                                                                        \
+      kern<<<w.grid, kChunkBwdWarps * 32, w.total, stream>>>(a, dy_map, out_map); HYC_LAUNCHED(); \
+    } else {                                                                                    \
+      auto kern = bwd_n_chunk_kernel<BITS, OP, CH, GROUP>;                                      \
+      int rc = set_smem(kern, w.total);                                                         \
+      if (rc) return rc;                                                                        \
+      kern<<<w.grid, kChunkBwdWarps * 32, w.total, stream>>>(a, dy_map, out_map); HYC_LAUNCHED(); \
+    }                                                                                           \
   }
 #define HYC_CB_OP(OP) if (a.p.group) HYC_CB_LAUNCH(OP, true) else HYC_CB_LAUNCH(OP, false)
   if (op == kChunkNormBwdLn) { HYC_CB_OP(kChunkNormBwdLn) }

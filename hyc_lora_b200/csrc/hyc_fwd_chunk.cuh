@@ -78,7 +78,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // (lower + upper, lower - upper).  The normalisation 1 / sqrt(n) is a power of two: the caller folds it
 // into the scale, exactly.
 template <int CH>
-__device__ __forceinline__ void rotate_chunk_n(f32x2 (&v)[CH / 2], int n, int lane) {
+__device__ __forceinline__ void rotate_chunk(f32x2 (&v)[CH / 2], int n, int lane) {
   // stride 1: inside a pair
 #pragma unroll
   for (int i = 0; i < CH / 2; ++i) {
@@ -115,16 +115,6 @@ __device__ __forceinline__ void rotate_chunk_n(f32x2 (&v)[CH / 2], int n, int la
       }
     }
   }
-}
-
-// The common block sizes with the size known to the compiler: the tests of `n` before every stage then fold away,
-// and the stages of a chunk (and the chunks of the segments around the call) become one stretch of code that the
-// compiler schedules as a whole.
-template <int CH>
-__device__ __forceinline__ void rotate_chunk(f32x2 (&v)[CH / 2], int n, int lane) {
-  if (n == 256) rotate_chunk_n<CH>(v, 256, lane);
-  else if (n == 64) rotate_chunk_n<CH>(v, 64, lane);
-  else rotate_chunk_n<CH>(v, n, lane);
 }
 
 // Outlier channels of one record (`chan`: the list in shared memory; lane l looks after entries l, l + 32, ...):
@@ -243,7 +233,11 @@ __device__ __forceinline__ void chunk_scale_pack(const PackedDev& p, const f32x2
 
 // NK: 0 compress only, 1 RMSNorm (plain or Gemma), 2 LayerNorm;  CH: channels of a segment per lane;
 // DUAL: a second record (a.p2, with its own outlier channels) takes the compressed norm output.
-template <int BITS, int NK, int CH, bool GROUP, bool DUAL, int WARPS>
+// RN: the rotation block when the kernel is compiled for one (256: the butterfly stages then carry no test of the
+// block size and are one stretch of code), or 0: the record's own, read at run time.  Only the many-warps build
+// for long inputs exists with RN = 256: inside a training step a launch starts with cold instruction caches, and
+// there the smaller code of the few-warps build counts for more.
+template <int BITS, int NK, int CH, bool GROUP, bool DUAL, int WARPS, int RN = 0>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 fwd_n_chunk_kernel(const __grid_constant__ ChunkFwdArgs a, const __grid_constant__ CUtensorMap in_map,
                    const __grid_constant__ CUtensorMap y_map) {
@@ -335,7 +329,7 @@ fwd_n_chunk_kernel(const __grid_constant__ ChunkFwdArgs a, const __grid_constant
         mbar_expect_tx(bar, row_bytes + a.tx_pad);
         tensor_load_row(slot, &in_map, next, bar);
       }
-      chunk_unpack_rotate<NSEG, CH>(raw, v, p.rotate, lane);
+      chunk_unpack_rotate<NSEG, CH>(raw, v, RN ? RN : p.rotate, lane);
     } else {
       // ---- statistics of the norm (the zeroed outlier channels still belong to them)
       float mean = 0.f;
@@ -432,7 +426,7 @@ fwd_n_chunk_kernel(const __grid_constant__ ChunkFwdArgs a, const __grid_constant
             for (int e = 0; e < 4; ++e) v[s][4 * j + e] = f[e];
           }
         }
-        if (FUSE) rotate_chunk<CH>(v[s], p.rotate, lane);
+        if (FUSE) rotate_chunk<CH>(v[s], RN ? RN : p.rotate, lane);
         else if (s + 1 < NSEG) asm volatile("" ::: "memory");
       }
       // the vector stores wrote the norm of the zeroed value at the outlier channels: order them before the
@@ -460,7 +454,7 @@ fwd_n_chunk_kernel(const __grid_constant__ ChunkFwdArgs a, const __grid_constant
         for (int s = 0; s < NSEG; ++s)
 #pragma unroll
           for (int j = 0; j < NPC; ++j) forget_unpacked(raw[s][j]);
-        chunk_unpack_rotate<NSEG, CH>(raw, v, p.rotate, lane);
+        chunk_unpack_rotate<NSEG, CH>(raw, v, RN ? RN : p.rotate, lane);
       }
     }
     // ---- the record of the row itself, from the registers
@@ -473,7 +467,7 @@ fwd_n_chunk_kernel(const __grid_constant__ ChunkFwdArgs a, const __grid_constant
       chunk_take_outliers(a.p2, chan2, slot, row, lane, ov2);
       __syncwarp();
       chunk_load<NSEG, CH>(slot, segw, lane, raw);
-      chunk_unpack_rotate<NSEG, CH>(raw, v, p.rotate, lane);
+      chunk_unpack_rotate<NSEG, CH>(raw, v, RN ? RN : p.rotate, lane);
       chunk_scale_pack<BITS, CH, GROUP>(a.p2, v, row, lane);
     }
     if (NORM) {
@@ -588,7 +582,12 @@ int launch_fwd_chunk_one(const ChunkFwdArgs& a, const ChunkPlan& w, bool norm, c
 #define HYC_CHUNK_LAUNCH(NK, GROUP, DUAL)                                                       \
   {                                                                                             \
     if (w.warps == kChunkWarpsFew) HYC_CHUNK_LAUNCH_W(NK, GROUP, DUAL, kChunkWarpsFew)          \
-    else HYC_CHUNK_LAUNCH_W(NK, GROUP, DUAL, kChunkWarpsMany)                                   \
+    else if (!DUAL && a.p.rotate == 256) {                                                      \
+      auto kern = fwd_n_chunk_kernel<BITS, NK, CH, GROUP, false, kChunkWarpsMany, 256>;         \
+      int rc = set_smem(kern, w.total);                                                         \
+      if (rc) return rc;                                                                        \
+      kern<<<w.grid, kChunkWarpsMany * 32, w.total, stream>>>(a, in_map, y_map); HYC_LAUNCHED(); \
+    } else HYC_CHUNK_LAUNCH_W(NK, GROUP, DUAL, kChunkWarpsMany)                                 \
   }
 #define HYC_CHUNK_NK(NK)                                                                        \
   if (a.p.group) {                                                                              \

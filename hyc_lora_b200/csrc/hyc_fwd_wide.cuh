@@ -174,7 +174,11 @@ __device__ __forceinline__ void wide_unpack_rotate(const uint4 (&raw)[NSEG][CH /
 __device__ __forceinline__ float act_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float act_gelu(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
 
-template <int BITS, int OP, int CH, bool GROUP, int WPR>
+// RN: the rotation block when the kernel is compiled for one (64, what rows of 11 008 and 14 336 channels use:
+// the butterfly stages then carry no test of the block size and the segments of a row overlap), or -1: the
+// record's own, read at run time.  Two kernels rather than two loops in one: a launch inside a training step
+// starts with cold instruction caches, and code that is not run still costs there.
+template <int BITS, int OP, int CH, bool GROUP, int WPR, int RN>
 __global__ void __launch_bounds__(kWideWarps * 32, 1)
 fwd_n_wide_kernel(const __grid_constant__ WideArgs a, const __grid_constant__ CUtensorMap in_map,
                   const __grid_constant__ CUtensorMap in2_map, const __grid_constant__ CUtensorMap y_map) {
@@ -240,10 +244,7 @@ fwd_n_wide_kernel(const __grid_constant__ WideArgs a, const __grid_constant__ CU
   uint32_t ph = 0;        // product: parity of both barriers; else: parity of slot 0's (slot 1 flips one row later)
   int st = 0;
   int rp = 0;             // which half of `red` the next absmax exchange uses
-  // the row loop is compiled a second time with the rotation block of 64 known: the butterfly stages then carry no
-  // test of it, and the segments of a row overlap
-  auto row_loop = [&](auto rot_c) {
-    const int nrot = decltype(rot_c)::value >= 0 ? decltype(rot_c)::value : p.rotate;
+  const int nrot = RN >= 0 ? RN : p.rotate;
   for (; row < rows; row += stride) {
     // ---- wait for the row (both operands); the group decides together whether a wait ran out
     bool ok;
@@ -372,9 +373,6 @@ fwd_n_wide_kernel(const __grid_constant__ WideArgs a, const __grid_constant__ CU
       st ^= 1;
     }
   }
-  };
-  if (p.rotate == 64) row_loop(std::integral_constant<int, 64>());     // what rows of 11 008 and 14 336 channels use
-  else row_loop(std::integral_constant<int, -1>());
   // no tensor store of this thread may still be reading shared memory when the CTA leaves
   if ((ACT || PROD) && leader) bulk_wait_all();
 }
@@ -433,10 +431,17 @@ int launch_wide_op(const WideArgs& a, const WidePlan& w, const CUtensorMap& in_m
                    const CUtensorMap& y_map, cudaStream_t stream) {
 #define HYC_WIDE_LAUNCH(GROUP, WPR)                                                             \
   {                                                                                             \
-    auto kern = fwd_n_wide_kernel<BITS, OP, 128 * BITS / 8, GROUP, WPR>;                        \
-    int rc = set_smem(kern, w.total);                                                           \
-    if (rc) return rc;                                                                          \
-    kern<<<w.grid, kWideWarps * 32, w.total, stream>>>(a, in_map, in2_map, y_map); HYC_LAUNCHED(); \
+    if (a.p.rotate == 64) {                                                                     \
+      auto kern = fwd_n_wide_kernel<BITS, OP, 128 * BITS / 8, GROUP, WPR, 64>;                  \
+      int rc = set_smem(kern, w.total);                                                         \
+      if (rc) return rc;                                                                        \
+      kern<<<w.grid, kWideWarps * 32, w.total, stream>>>(a, in_map, in2_map, y_map); HYC_LAUNCHED(); \
+    } else {                                                                                    \
+      auto kern = fwd_n_wide_kernel<BITS, OP, 128 * BITS / 8, GROUP, WPR, -1>;                  \
+      int rc = set_smem(kern, w.total);                                                         \
+      if (rc) return rc;                                                                        \
+      kern<<<w.grid, kWideWarps * 32, w.total, stream>>>(a, in_map, in2_map, y_map); HYC_LAUNCHED(); \
+    }                                                                                           \
   }
 #define HYC_WIDE_WPR(GROUP)                                                                     \
   switch (w.wpr) {                                                                              \
