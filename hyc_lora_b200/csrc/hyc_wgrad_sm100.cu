@@ -740,7 +740,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) lora_wgrad_ws_kernel(const __gr
 // of the side partials, and writes the row.
 __global__ void wgrad_finish_kernel(const float* __restrict__ partials, int splits, const float* __restrict__ side,
                                     int slices, const int* __restrict__ channels, int k, int rank, int D, int rotate,
-                                    const __nv_bfloat16* __restrict__ colscale, float* __restrict__ out) {
+                                    const __nv_bfloat16* __restrict__ colscale, float* __restrict__ out,
+                                    __nv_bfloat16* __restrict__ out_bf16) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* rowbuf = reinterpret_cast<float*>(smem_raw);
   const int n = blockIdx.x;
@@ -772,6 +773,14 @@ __global__ void wgrad_finish_kernel(const float* __restrict__ partials, int spli
     }
   }
   __syncthreads();
+  if (out_bf16) {   // the caller's parameter dtype: rounded here instead of by a kernel of its own
+    __nv_bfloat16* dst = out_bf16 + static_cast<long long>(n) * D + d0;
+    for (int c = threadIdx.x << 2; c < len; c += blockDim.x << 2) {
+      const float4 v = *reinterpret_cast<const float4*>(rowbuf + c);
+      *reinterpret_cast<uint2*>(dst + c) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    }
+    return;
+  }
   float* dst = out + static_cast<long long>(n) * D + d0;
   for (int c = threadIdx.x << 2; c < len; c += blockDim.x << 2)
     *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(rowbuf + c);
@@ -1002,20 +1011,27 @@ int64_t hyc_lora_wgrad_scratch_floats(const hyc_packed* saved, int32_t rank) {
 
 int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, float* out, float* partials,
                    void* stream_) {
+  return hyc_lora_wgrad_to(saved, grad, rank, out, HYC_F32, partials, stream_);
+}
+
+int hyc_lora_wgrad_to(const hyc_packed* saved, const void* grad, int32_t rank, void* out, int32_t out_dtype,
+                      float* partials, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int rc = wgrad_check(saved, rank);
   if (rc != HYC_OK) return rc;
+  if (out_dtype != HYC_F32 && out_dtype != HYC_BF16) return HYC_ERR_DTYPE;
+  const size_t out_elem = out_dtype == HYC_F32 ? sizeof(float) : sizeof(__nv_bfloat16);
   const bool ref = saved->mode == HYC_MODE_R;
   if (!saved->codes || !grad || !out || !partials) return HYC_ERR_NULL;
   if (ref ? (!saved->scale || !saved->pool || !saved->row_meta) : !saved->scales) return HYC_ERR_NULL;
   if (!ref && saved->n_channels > 0 && (!saved->channels || !saved->out_value)) return HYC_ERR_NULL;
   const int D = saved->cols;
   if ((reinterpret_cast<uintptr_t>(grad) & 15u) || (reinterpret_cast<uintptr_t>(saved->codes) & 15u) ||
-      (reinterpret_cast<uintptr_t>(partials) & 15u))
+      (reinterpret_cast<uintptr_t>(partials) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u))
     return HYC_ERR_ALIGN;
   const long long slab = static_cast<long long>(rank) * D;
   if (saved->rows == 0) {
-    if (cudaMemsetAsync(out, 0, slab * sizeof(float), stream) != cudaSuccess) return HYC_ERR_CUDA;
+    if (cudaMemsetAsync(out, 0, slab * out_elem, stream) != cudaSuccess) return HYC_ERR_CUDA;
     return HYC_OK;
   }
   WgradPlan pl;
@@ -1104,7 +1120,10 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
         return HYC_ERR_CUDA;
     wgrad_finish_kernel<<<dim3(rank, parts), 256, sm, stream>>>(partials, splits, side, pl.side_slices, saved->channels,
                                                                pl.side_slices > 0 ? k : 0, rank, D,
-                                                               ref ? 0 : saved->rotate, colscale, out); HYC_LAUNCHED();
+                                                               ref ? 0 : saved->rotate, colscale,
+                                                               out_dtype == HYC_F32 ? static_cast<float*>(out) : nullptr,
+                                                               out_dtype == HYC_BF16 ? static_cast<__nv_bfloat16*>(out) : nullptr);
+    HYC_LAUNCHED();
   }
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;
 }

@@ -60,7 +60,8 @@ class EfficientMemoryLinearFunc(torch.autograd.Function):
             elif ctx.needs_input_grad[0]:
                 grad_input = grad_output.to(w.dtype) @ w
             if ctx.needs_input_grad[1]:
-                grad_weight = _pk.lora_wgrad(packed, grad_output).to(w.dtype)
+                out_dtype = w.dtype if w.dtype in (torch.bfloat16, torch.float32) else torch.float32
+                grad_weight = _pk.lora_wgrad(packed, grad_output, out_dtype=out_dtype).to(w.dtype)
             if ctx.use_bias and ctx.needs_input_grad[2]:
                 grad_bias = grad_output.to(torch.bfloat16).sum(0)
         grads = [grad_input, grad_weight, grad_bias] + [None] * (8 + ctx.n_extra)

@@ -462,6 +462,9 @@ def test_lora_weight_gradient_from_codes(pk, rows, d, bits, group, rotate, rank,
     assert _cos(dw, want) > 0.9999 and _rel_err(dw, want) < 1e-2
     lib_path = pk.lora_wgrad(p, g.to(DEV), force_library=True)
     assert _cos(dw, lib_path) > 0.9999
+    # the result in the weight's dtype straight from the kernel that finishes the sums: the same sums, rounded once
+    dwb = pk.lora_wgrad(p, g.to(DEV), out_dtype=torch.bfloat16)
+    assert dwb.dtype == torch.bfloat16 and torch.equal(dwb, dw.to(torch.bfloat16))
     assert not p.wait_expired()
 
 
