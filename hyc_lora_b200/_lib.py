@@ -105,8 +105,8 @@ SYMBOLS = {
     "hyc_select_channels": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "hyc_lora_wgrad_scratch_floats": (C.c_int64, [C.POINTER(HycPacked), C.c_int32]),
     "hyc_lora_wgrad": (C.c_int, [C.POINTER(HycPacked), C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
-    "hyc_lora_wgrad_to": (C.c_int, [C.POINTER(HycPacked), C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p,
-                                    C.c_void_p]),
+    "hyc_lora_wgrad_to": (C.c_int, [C.POINTER(HycPacked), C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
+                                    C.c_void_p, C.c_void_p]),
     "hyc_softmax_compact": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(HycSparseRows), C.c_void_p]),
     "hyc_softmax_expand": (C.c_int, [C.POINTER(HycSparseRows), C.c_void_p, C.c_void_p]),
     "hyc_softmax_bwd": (C.c_int, [C.POINTER(HycSparseRows), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),

@@ -741,7 +741,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) lora_wgrad_ws_kernel(const __gr
 __global__ void wgrad_finish_kernel(const float* __restrict__ partials, int splits, const float* __restrict__ side,
                                     int slices, const int* __restrict__ channels, int k, int rank, int D, int rotate,
                                     const __nv_bfloat16* __restrict__ colscale, float* __restrict__ out,
-                                    __nv_bfloat16* __restrict__ out_bf16) {
+                                    __nv_bfloat16* __restrict__ out_bf16, int accumulate) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* rowbuf = reinterpret_cast<float*>(smem_raw);
   const int n = blockIdx.x;
@@ -773,17 +773,30 @@ __global__ void wgrad_finish_kernel(const float* __restrict__ partials, int spli
     }
   }
   __syncthreads();
+  // `accumulate`: the result is added to what `out` holds (the sum in fp32, rounded once) -- a gradient buffer that
+  // collects several backward passes
   if (out_bf16) {   // the caller's parameter dtype: rounded here instead of by a kernel of its own
     __nv_bfloat16* dst = out_bf16 + static_cast<long long>(n) * D + d0;
     for (int c = threadIdx.x << 2; c < len; c += blockDim.x << 2) {
-      const float4 v = *reinterpret_cast<const float4*>(rowbuf + c);
+      float4 v = *reinterpret_cast<const float4*>(rowbuf + c);
+      if (accumulate) {
+        const uint2 old = *reinterpret_cast<const uint2*>(dst + c);
+        v.x += __uint_as_float(old.x << 16); v.y += __uint_as_float(old.x & 0xffff0000u);
+        v.z += __uint_as_float(old.y << 16); v.w += __uint_as_float(old.y & 0xffff0000u);
+      }
       *reinterpret_cast<uint2*>(dst + c) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
     }
     return;
   }
   float* dst = out + static_cast<long long>(n) * D + d0;
-  for (int c = threadIdx.x << 2; c < len; c += blockDim.x << 2)
-    *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(rowbuf + c);
+  for (int c = threadIdx.x << 2; c < len; c += blockDim.x << 2) {
+    float4 v = *reinterpret_cast<const float4*>(rowbuf + c);
+    if (accumulate) {
+      const float4 old = *reinterpret_cast<const float4*>(dst + c);
+      v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+    }
+    *reinterpret_cast<float4*>(dst + c) = v;
+  }
 }
 
 // Reference mode: the scale of every row as fp32 (per-token scale: by sequence position; per-tensor: the one
@@ -1011,11 +1024,11 @@ int64_t hyc_lora_wgrad_scratch_floats(const hyc_packed* saved, int32_t rank) {
 
 int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, float* out, float* partials,
                    void* stream_) {
-  return hyc_lora_wgrad_to(saved, grad, rank, out, HYC_F32, partials, stream_);
+  return hyc_lora_wgrad_to(saved, grad, rank, out, HYC_F32, 0, partials, stream_);
 }
 
 int hyc_lora_wgrad_to(const hyc_packed* saved, const void* grad, int32_t rank, void* out, int32_t out_dtype,
-                      float* partials, void* stream_) {
+                      int32_t accumulate, float* partials, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int rc = wgrad_check(saved, rank);
   if (rc != HYC_OK) return rc;
@@ -1031,7 +1044,7 @@ int hyc_lora_wgrad_to(const hyc_packed* saved, const void* grad, int32_t rank, v
     return HYC_ERR_ALIGN;
   const long long slab = static_cast<long long>(rank) * D;
   if (saved->rows == 0) {
-    if (cudaMemsetAsync(out, 0, slab * out_elem, stream) != cudaSuccess) return HYC_ERR_CUDA;
+    if (!accumulate && cudaMemsetAsync(out, 0, slab * out_elem, stream) != cudaSuccess) return HYC_ERR_CUDA;
     return HYC_OK;
   }
   WgradPlan pl;
@@ -1122,7 +1135,8 @@ int hyc_lora_wgrad_to(const hyc_packed* saved, const void* grad, int32_t rank, v
                                                                pl.side_slices > 0 ? k : 0, rank, D,
                                                                ref ? 0 : saved->rotate, colscale,
                                                                out_dtype == HYC_F32 ? static_cast<float*>(out) : nullptr,
-                                                               out_dtype == HYC_BF16 ? static_cast<__nv_bfloat16*>(out) : nullptr);
+                                                               out_dtype == HYC_BF16 ? static_cast<__nv_bfloat16*>(out) : nullptr,
+                                                               accumulate != 0);
     HYC_LAUNCHED();
   }
   return cudaGetLastError() == cudaSuccess ? HYC_OK : HYC_ERR_CUDA;

@@ -7,7 +7,10 @@ a view into it), so the exchange is a few large all-reduces that NCCL can run th
 buffer is cut into buckets (64 MB by default) and a bucket's all-reduce is enqueued, asynchronously,
 the moment backward has accumulated the last gradient that lives in it, so the exchange of the later
 layers' gradients runs under the backward pass of the earlier ones; ``comm_dtype=torch.bfloat16``
-halves the bytes on the wire (the sum is then a bf16 sum).  Nothing else on the compression path
+halves the bytes on the wire (the sum is then a bf16 sum).  With ``fused_accumulate=True`` every parameter carries a
+``hyc_grad_sink`` callable: a producer that can add its gradient into ``param.grad`` itself (in a GEMM epilogue,
+in the kernel that finishes the LoRA-A weight gradient) does so and calls the sink, which counts the parameter in
+for its bucket exactly as the accumulation hook would.  Nothing else on the compression path
 communicates: every kernel is rank-local and calibration state stays per rank, as in the reference
 (its DDP comes implicitly from the HF Trainer)."""
 from __future__ import annotations
@@ -20,7 +23,7 @@ import torch.distributed as dist
 
 class FlatGradSync:
     def __init__(self, params: Iterable[torch.nn.Parameter], average: bool = True, dtype=None, overlap: bool = False,
-                 bucket_bytes: int = 64 << 20, comm_dtype=None):
+                 bucket_bytes: int = 64 << 20, comm_dtype=None, fused_accumulate: bool = False):
         self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
         if not self.params:
             raise ValueError("no trainable parameters to synchronise")
@@ -52,6 +55,12 @@ class FlatGradSync:
         if self.overlap:
             for i, p in enumerate(self.params):
                 p.register_post_accumulate_grad_hook(lambda _p, i=i: self._ready(i))
+        # fused_accumulate: producers that know how (the LoRA-A weight gradient kernel, the LoRA-B GEMM of the host's
+        # adapter) add their gradient straight into the parameter's view of the flat buffer and call the sink
+        # instead of handing the engine a tensor to add -- one elementwise kernel less per parameter and step
+        if fused_accumulate and self._views:
+            for i, p in enumerate(self.params):
+                p.hyc_grad_sink = (lambda i=i: self._ready(i)) if self.overlap else (lambda: None)
 
     def _active(self) -> bool:
         return dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1

@@ -160,6 +160,13 @@ class _LoraMergeFunc(torch.autograd.Function):
         grad = grad.contiguous()
         # beta = 0: the first argument only gives shape and dtype, its contents are not read
         grad_h = torch.addmm(torch.empty_like(h), grad, weight_b, beta=0, alpha=ctx.scaling)
+        sink = getattr(weight_b, "hyc_grad_sink", None)
+        if sink is not None and weight_b.grad is not None and weight_b.grad.dtype == grad.dtype:
+            # the owner of the gradient buffer asked for it (ddp.FlatGradSync(fused_accumulate=True)): the GEMM
+            # adds into the buffer (beta = 1), which is the engine's accumulation step without a kernel of its own
+            weight_b.grad.addmm_(grad.t(), h, alpha=ctx.scaling)
+            sink()
+            return grad, grad_h, None, None
         grad_b = torch.addmm(torch.empty_like(weight_b), grad.t(), h, beta=0, alpha=ctx.scaling)
         return grad, grad_h, grad_b, None
 

@@ -27,7 +27,7 @@ class Trainer:
     def __init__(self, model, lr: float = 1e-4):
         self.model = model
         self.params = lora_parameters(model)
-        self.sync = FlatGradSync(self.params, overlap=True)
+        self.sync = FlatGradSync(self.params, overlap=True, fused_accumulate=True)
         self.opt = torch.optim.AdamW(self.params, lr=lr, fused=True, capturable=True)
         self.graph = None
         self.static_ids = None

@@ -10,7 +10,10 @@ Beyond the reference: ``EfficientMemoryLinear.forward(x, carry=t)`` also hands t
 shape) through unchanged, and backward adds ``dX`` into the gradient that arrives for it -- in the epilogue
 of the GEMM that makes ``dX`` -- instead of returning it for ``x``.  A host that strings the projections
 reading one activation along one such carry, starting at the activation itself, gets the sum of their
-input gradients without elementwise adds."""
+input gradients without elementwise adds.  And a weight that carries a ``hyc_grad_sink`` callable (set by the
+owner of its gradient buffer, ``ddp.FlatGradSync(fused_accumulate=True)``) has its gradient added into
+``weight.grad`` by the kernel that finishes the sums; backward then returns no gradient for it and calls the
+sink."""
 import torch
 
 from .. import packed as _pk
@@ -60,8 +63,16 @@ class EfficientMemoryLinearFunc(torch.autograd.Function):
             elif ctx.needs_input_grad[0]:
                 grad_input = grad_output.to(w.dtype) @ w
             if ctx.needs_input_grad[1]:
-                out_dtype = w.dtype if w.dtype in (torch.bfloat16, torch.float32) else torch.float32
-                grad_weight = _pk.lora_wgrad(packed, grad_output, out_dtype=out_dtype).to(w.dtype)
+                sink = getattr(w, "hyc_grad_sink", None)
+                if sink is not None and w.grad is not None and w.grad.dtype == w.dtype:
+                    # the owner of the gradient buffer asked for it (see ddp.FlatGradSync): the kernel that finishes
+                    # the sums adds them into ``w.grad`` -- the engine's accumulation step without a kernel of its
+                    # own -- and the owner is told that this gradient is in
+                    _pk.lora_wgrad(packed, grad_output, accumulate_into=w.grad)
+                    sink()
+                else:
+                    out_dtype = w.dtype if w.dtype in (torch.bfloat16, torch.float32) else torch.float32
+                    grad_weight = _pk.lora_wgrad(packed, grad_output, out_dtype=out_dtype).to(w.dtype)
             if ctx.use_bias and ctx.needs_input_grad[2]:
                 grad_bias = grad_output.to(torch.bfloat16).sum(0)
         grads = [grad_input, grad_weight, grad_bias] + [None] * (8 + ctx.n_extra)

@@ -576,9 +576,11 @@ def lora_wgrad_supported(p: Packed, rank: int) -> bool:
 
 
 def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False, path: str = "auto",
-               out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+               out_dtype: torch.dtype = torch.float32, accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``dW[r, D] = sum_t G[t, r] * X_hat[t, d]`` from the packed input, summed in fp32 and returned in
     ``out_dtype`` (fp32, or bf16: the LoRA-A weight's dtype, rounded once by the kernel that finishes the sums).
+    ``accumulate_into``: a contiguous fp32 / bf16 ``[r, D]`` tensor (a gradient buffer) that the result is added
+    to -- by the finishing kernel where the tensor-core route runs, else by one add -- and that is returned.
 
     The packed codes go to the dequant-fused tcgen05 kernel (the reconstruction never touches HBM).  Channel
     mode: the outlier channels' columns, the skinny product ``G^T @ out_value``, come from extra thread blocks
@@ -601,21 +603,32 @@ def lora_wgrad(p: Packed, grad_output: torch.Tensor, force_library: bool = False
         path = "library" if p.mode == "R" else "tensor"
     if force_library or path == "library" or not lora_wgrad_supported(p, rank):
         xh = decompress(p).reshape(p.rows, p.cols)
+        if accumulate_into is not None:
+            return accumulate_into.add_(g.t() @ xh)
         return (g.t() @ xh).to(out_dtype)
     rec = p.record()
     need = lib.hyc_lora_wgrad_scratch_floats(C.byref(rec), rank)
     if need < 0:
         check(int(need), "hyc_lora_wgrad_scratch_floats")
     # a low-rank part is added in fp32 below: the kernel's own result stays fp32 then
-    direct = out_dtype == torch.bfloat16 and not (p.mode == "R" and p.lowrank is not None)
-    out = torch.empty((rank, p.cols), dtype=torch.bfloat16 if direct else torch.float32, device=g.device)
+    lowrank = p.mode == "R" and p.lowrank is not None
+    sink = accumulate_into if (accumulate_into is not None and not lowrank and accumulate_into.is_contiguous()
+                               and accumulate_into.shape == (rank, p.cols) and accumulate_into.data_ptr() % 16 == 0
+                               and accumulate_into.dtype in (torch.float32, torch.bfloat16)) else None
+    direct = out_dtype == torch.bfloat16 and not lowrank
+    out = sink if sink is not None else torch.empty((rank, p.cols), dtype=torch.bfloat16 if direct else torch.float32,
+                                                    device=g.device)
     partials = torch.empty(need, dtype=torch.float32, device=g.device)
-    check(lib.hyc_lora_wgrad_to(C.byref(rec), _ptr(g), rank, _ptr(out), _dtype_code(out), _ptr(partials), _stream()),
-          "hyc_lora_wgrad_to")
-    if p.mode == "R" and p.lowrank is not None:
+    check(lib.hyc_lora_wgrad_to(C.byref(rec), _ptr(g), rank, _ptr(out), _dtype_code(out), int(sink is not None),
+                                _ptr(partials), _stream()), "hyc_lora_wgrad_to")
+    if sink is not None:
+        return sink
+    if lowrank:
         # the low-rank rows repeat for every batch element: contract them with the batch sum of the gradient
         gsum = g.view(-1, p.seq, rank).sum(dim=0, dtype=torch.float32).to(torch.bfloat16)
         out.addmm_(gsum.t().float(), p.lowrank.float())
+    if accumulate_into is not None:
+        return accumulate_into.add_(out.view_as(accumulate_into))
     return out.to(out_dtype)
 
 

@@ -254,9 +254,10 @@ int hyc_lora_wgrad(const hyc_packed* saved, const void* grad, int32_t rank, floa
 /* The same with the result written in `out_dtype` (HYC_F32 or HYC_BF16; 16-byte aligned [rank, cols]): the sums
  * are taken in fp32 as above and rounded once, by the kernel that finishes them, to the dtype of the LoRA-A weight
  * -- the `.to(weight dtype)` that follows the contraction in efficient_linear.py:66-67, without a kernel of its
- * own. */
+ * own.  accumulate != 0: the result is added to what `out` holds (in fp32, rounded once) instead of replacing it
+ * -- what the autograd engine does with a second gradient for the same weight, without a kernel of its own. */
 int hyc_lora_wgrad_to(const hyc_packed* saved, const void* grad, int32_t rank, void* out, int32_t out_dtype,
-                      float* partials, void* stream);
+                      int32_t accumulate, float* partials, void* stream);
 
 /* Thresholded ("sparse") copy of attention probabilities, rows x cols with cols <= 65535.
  * Replaces true_compress_softmax / true_decompress_softmax (compress_function.py:264-275: a

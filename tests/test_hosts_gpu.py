@@ -251,3 +251,41 @@ def test_input_gradients_summed_along_the_carry(quant):
     assert (gx_u - want).abs().max().item() < 3e-2 * scale
     for a, b in zip(ga_c + gb_c, ga_u + gb_u):
         assert torch.equal(a, b)
+
+
+def test_gradients_added_into_the_owner_s_buffer_match_the_engine_s_accumulation():
+    """Parameters that carry a ``hyc_grad_sink`` (what ``FlatGradSync(fused_accumulate=True)`` sets) get their
+    gradients added into ``param.grad`` by the producing kernels; the result must be what the autograd engine's own
+    accumulation gives, the sink must be called once per parameter and backward pass, and a second pass must add."""
+    from hyc_lora_b200.ddp import FlatGradSync
+    from hyc_lora_b200.hosts.lora import LoRALinear, lora_parameters
+    from hyc_lora_b200.hosts.replace import replace_module, uniform_config
+    torch.manual_seed(11)
+    mods = torch.nn.ModuleList(LoRALinear(1024, o, r=16, quant="bf16", device="cuda") for o in (1024, 256))
+    _train_b(mods)
+    assert replace_module(mods, uniform_config(sub_outlier_bit=4), dict(outlier_mode="channel", rotate=256)) == 2
+    x0 = torch.randn(2, 64, 1024, device="cuda", dtype=torch.bfloat16)
+    gy = [torch.randn(2, 64, m.base_layer.out_features, device="cuda", dtype=torch.bfloat16) for m in mods]
+
+    def backward_pass():
+        x = x0.clone().requires_grad_(True)
+        torch.autograd.backward([m(x) for m in mods], gy)
+
+    for _ in range(3):                                 # calibration calls, then the steady state
+        mods.zero_grad(set_to_none=True)
+        backward_pass()
+    params = lora_parameters(mods)
+    want = [p.grad.clone() for p in params]
+    sync = FlatGradSync(params, fused_accumulate=True)   # every .grad is now a view of the (zeroed) flat buffer
+    calls = []
+    for i, p in enumerate(params):
+        inner = p.hyc_grad_sink
+        p.hyc_grad_sink = lambda i=i, inner=inner: (calls.append(i), inner())[1]
+    backward_pass()
+    assert sorted(calls) == list(range(len(params)))
+    for p, w in zip(params, want):
+        assert p.grad.data_ptr() >= sync.flat.data_ptr() and torch.equal(p.grad, w)
+    backward_pass()                                     # a second pass adds (one rounding of the fp32 sum)
+    for p, w in zip(params, want):
+        assert (p.grad.float() - 2 * w.float()).abs().max() <= 2e-2 * w.float().abs().max()
+    assert len(calls) == 2 * len(params)

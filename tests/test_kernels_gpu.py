@@ -1210,3 +1210,19 @@ def test_expired_wait_is_reported_and_leaves_the_device_usable(pk):
     assert torch.equal(pk.decompress(p).reshape(rows, d), want)
     assert not p.wait_expired() and pk.poll_status(wait=True) == 0
     assert _lib.lib.hyc_debug_wait(-1, 0) == -2 and _lib.lib.hyc_debug_wait(0, 8) == -2
+
+
+def test_weight_gradient_added_to_a_gradient_buffer(pk):
+    """hyc_lora_wgrad_to with accumulate: what the buffer held plus the fp32 sums, rounded once (bf16 and fp32)."""
+    rows, d, rank = 700, 4096, 16
+    x, _ = synthetic.sweep_activation(rows, d, 0.01, salt=3)
+    g = torch.randn(rows, rank, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
+    ch = oc.n_select_channels(oc.n_channel_scores(x), oc.n_outlier_count(d, 0.01))
+    p = pk.compress_n(x.to(DEV), ch.to(DEV), 4, 0, 256)
+    dw = pk.lora_wgrad(p, g)
+    for dtype in (torch.bfloat16, torch.float32):
+        base = torch.randn(rank, d, device=DEV).to(dtype)
+        buf = base.clone()
+        out = pk.lora_wgrad(p, g, accumulate_into=buf)
+        assert out.data_ptr() == buf.data_ptr()
+        assert torch.equal(buf, (base.float() + dw).to(dtype))
