@@ -52,6 +52,7 @@ class FlatGradSync:
                 start, members = off, []
         self.overlap = bool(overlap) and self._views
         self._pending, self._works, self._launched = [], [], []
+        self._seen = []
         if self.overlap:
             for i, p in enumerate(self.params):
                 p.register_post_accumulate_grad_hook(lambda _p, i=i: self._ready(i))
@@ -69,11 +70,17 @@ class FlatGradSync:
         """Call before backward (overlap mode): every bucket waits for all of its gradients again."""
         self._pending = [len(m) for _, _, m in self.buckets]
         self._launched = [False] * len(self.buckets)
+        self._seen = [False] * len(self.params)
         self._works = []
 
     def _ready(self, i: int):
         if not self._pending or not self._active():
             return
+        # a parameter counts once per backward pass: the accumulation hook may fire for a parameter whose producer
+        # has already reported through the sink (the engine runs the hook even when no gradient tensor arrives)
+        if self._seen[i]:
+            return
+        self._seen[i] = True
         b = self._bucket_of[i]
         self._pending[b] -= 1
         if self._pending[b] == 0 and not self._launched[b]:

@@ -27,16 +27,60 @@ class _Tiny(torch.nn.Module):
         return ((x @ self.base.t() + x @ self.lora_A.t() @ self.lora_B.t()) ** 2).mean()
 
 
-def _worker(rank, world, port, out, overlap=False, comm_dtype=None):
+class _SelfAccumulating(torch.autograd.Function):
+    """h = x W^T whose backward adds the weight gradient into ``W.grad`` itself and reports through the sink --
+    what the LoRA-A weight-gradient kernel and the adapter's LoRA-B GEMM do on the GPU."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return x @ w.t()
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        sink = getattr(w, "hyc_grad_sink", None)
+        if sink is not None and w.grad is not None:
+            w.grad.addmm_(g.t(), x)
+            sink()
+            return g @ w, None
+        return g @ w, g.t() @ x
+
+
+class _TinyFused(_Tiny):
+    def forward(self, x):
+        h = _SelfAccumulating.apply(_SelfAccumulating.apply(x, self.lora_A), self.lora_B)
+        return ((x @ self.base.t() + h) ** 2).mean()
+
+
+def _worker(rank, world, port, out, overlap=False, comm_dtype=None, fused=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from hyc_lora_b200.ddp import FlatGradSync
-    model = _Tiny()
+    model = _TinyFused() if fused else _Tiny()
     # overlap: one bucket per parameter (the buckets go out from the gradient hooks, during backward)
-    sync = FlatGradSync(model.parameters(), overlap=overlap, bucket_bytes=64 if overlap else 64 << 20, comm_dtype=comm_dtype)
-    assert sync.numel() == 4 * 24 * 2 and len(sync.buckets) == (2 if overlap else 1)
+    # (with the producers reporting themselves: one bucket for both parameters, which must not go out early)
+    one_bucket = fused or not overlap
+    sync = FlatGradSync(model.parameters(), overlap=overlap, bucket_bytes=64 << 20 if one_bucket else 64, comm_dtype=comm_dtype,
+                        fused_accumulate=fused)
+    assert sync.numel() == 4 * 24 * 2 and len(sync.buckets) == (1 if one_bucket else 2)
+    reported = set()
+    if fused:
+        # a bucket may go out only when the producers of all its gradients have reported (checked where it is sent:
+        # with an asynchronous all-reduce a bucket that left early could still come out right by timing)
+        params = list(model.parameters())
+        for i, p in enumerate([q for q in params if q.requires_grad]):
+            inner = p.hyc_grad_sink
+            p.hyc_grad_sink = lambda i=i, inner=inner: (reported.add(i), inner())[1]
+        send = sync._launch
+
+        def checked_send(b):
+            assert all(i in reported for i in sync.buckets[b][2]), "bucket sent before its gradients were in"
+            return send(b)
+        sync._launch = checked_send
     x = torch.randn(8, 24, generator=torch.Generator().manual_seed(9))
     for step in range(2):                       # second step: the flat buffer is reused after zero()
+        reported.clear()
         sync.zero()
         loss = model(x[rank * 4:(rank + 1) * 4])
         sync.begin()
@@ -53,12 +97,17 @@ def _worker(rank, world, port, out, overlap=False, comm_dtype=None):
 import pytest
 
 
-@pytest.mark.parametrize("overlap,comm_dtype,atol", [(False, None, 1e-6), (True, None, 1e-6), (True, torch.bfloat16, 2e-3)])
-def test_flat_gradient_allreduce_matches_single_process(overlap, comm_dtype, atol):
+# fused: the producers add their gradients into the flat buffer themselves and report through the sink; the
+# accumulation hook of such a parameter may fire as well, and the parameter must still count once (one bucket holds
+# both parameters in these cases: counted twice, it would go out before the second gradient is in)
+@pytest.mark.parametrize("overlap,comm_dtype,atol,fused", [
+    (False, None, 1e-6, False), (True, None, 1e-6, False), (True, torch.bfloat16, 2e-3, False),
+    (True, None, 1e-6, True), (False, None, 1e-6, True)])
+def test_flat_gradient_allreduce_matches_single_process(overlap, comm_dtype, atol, fused):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out, overlap, comm_dtype)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out, overlap, comm_dtype, fused)) for r in range(2)]
     for p in procs:
         p.start()
     ga, gb = out.get(timeout=120)
